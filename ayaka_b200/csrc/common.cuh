@@ -1,0 +1,88 @@
+// Shared helpers of the sm_100a kernels: element conversion, warp/block reductions,
+// the C ABI's status codes. Every entry point is `extern "C" int ayk_*(..., void* stream)`
+// and returns 0, a positive cudaError_t from the launch, or a negative refusal code below.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define AYK_OK 0
+#define AYK_BAD_ARGUMENT (-1)   // a size or pointer the kernel does not take
+#define AYK_BAD_ALIGNMENT (-2)  // a pointer or stride that breaks a vector or TMA rule
+#define AYK_TOO_LARGE (-3)      // beyond a stated maximum
+#define AYK_DRIVER (-4)         // a driver entry point is missing or failed
+
+#define AYK_API extern "C" __attribute__((visibility("default")))
+
+namespace ayk {
+
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float load(const float* p) { return *p; }
+  static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float load(const __nv_bfloat16* p) {
+    return __bfloat162float(*p);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) {
+    *p = __float2bfloat16_rn(v);
+  }
+};
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p) { return Elem<T>::load(p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v) { Elem<T>::store(p, v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+// tanh-form and erf-form GELU in fp32 (torch's `gelu(approximate="tanh")` and `gelu`).
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float inner = k0 * (x + k1 * x * x * x);
+  return 0.5f * x * (1.f + tanhf(inner));
+}
+__device__ __forceinline__ float gelu_erf(float x) {
+  return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
+}
+
+enum Activation : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_GELU_ERF = 2 };
+
+__device__ __forceinline__ float activate(float x, int act) {
+  if (act == ACT_GELU_TANH) return gelu_tanh(x);
+  if (act == ACT_GELU_ERF) return gelu_erf(x);
+  return x;
+}
+
+inline int launch_status() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? AYK_OK : (int)e;
+}
+
+}  // namespace ayk

@@ -1,0 +1,302 @@
+// C[M,N] = A[M,K] * W[N,K]^T (+ bias, activation, residual) in bfloat16 on the 5th-generation
+// tensor cores: TMA -> shared memory (128-byte swizzle) -> tcgen05.mma with the fp32
+// accumulator in tensor memory -> tcgen05.ld -> epilogue in registers -> global memory.
+//
+// One CTA of 128 threads computes one 128 x BN tile of C. Warp 0's elected thread is the TMA
+// producer, warp 1's the MMA issuer; a ring of STAGES buffers with a full/empty mbarrier pair
+// each decouples them. When the last MMA has been committed all four warps run the epilogue:
+// warp w owns tensor-memory lanes 32w..32w+31, i.e. rows 32w..32w+31 of the tile, and each
+// thread reads its row 32 columns at a time.
+//
+// K is walked in blocks of 64 from 0 upward whatever M and N are, so an output element's
+// accumulation order does not depend on the batch. Tails in M, N and K are zero-filled by
+// TMA and masked at the store. Needs: A and W 16-byte aligned with row strides that are
+// multiples of 8 elements (the caller falls back to the CUDA-core kernel otherwise).
+//
+// Every wait is bounded; a wait that runs out sets *status = AYK_WAIT_TIMEOUT, the CTA skips
+// its stores, drains its copies, frees its tensor memory and returns.
+#include <mutex>
+#include <unordered_map>
+
+#include "tc_common.cuh"
+
+namespace ayk {
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 64;
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;
+
+enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_RESIDUAL_F32 = 2 };
+
+template <int BN, int STAGES>
+struct TcSmem {
+  static constexpr int B_BYTES = BN * TC_BK * 2;
+  static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  // full[STAGES], empty[STAGES], accum, then the tmem slot and the failure flag
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16;
+  static constexpr int DYNAMIC = TOTAL + 1024;  // room to align the base to 1024 bytes
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(128)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const float* __restrict__ bias, void* __restrict__ out, int ldo, int M, int N,
+               int K, int act, int mode, int vec_ok, int* __restrict__ status) {
+  using L = TcSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty = full + STAGES;
+  uint64_t* accum = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * TC_BM;
+  const int num_kb = (K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    *failed = 0;
+    mbar_fence_init();
+    tma_prefetch_map(&map_a);
+    tma_prefetch_map(&map_w);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, BN < 32 ? 32 : BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  int issued = 0;  // k-blocks whose copies the producer has started
+  if (warp == 0 && lane == 0) {
+    for (int kb = 0; kb < num_kb; ++kb) {
+      const int s = kb % STAGES;
+      if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1)) {
+        *failed = 1;
+        break;
+      }
+      uint8_t* a_tile = smem + s * L::STAGE_BYTES;
+      mbar_expect_tx(&full[s], L::STAGE_BYTES);
+      tma_load_2d(a_tile, &map_a, &full[s], kb * TC_BK, m0);
+      tma_load_2d(a_tile + TC_A_BYTES, &map_w, &full[s], kb * TC_BK, n0);
+      issued = kb + 1;
+    }
+  } else if (warp == 1 && lane == 0) {
+    constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
+    bool ok = true;
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int s = kb % STAGES;
+      if (!mbar_wait(&full[s], (kb / STAGES) & 1)) {
+        *failed = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint8_t* a_tile = smem + s * L::STAGE_BYTES;
+      const uint8_t* b_tile = a_tile + TC_A_BYTES;
+#pragma unroll
+      for (int k = 0; k < TC_BK / 16; ++k) {
+        umma_f16(tmem_base, umma_desc_k128(a_tile, k * 32), umma_desc_k128(b_tile, k * 32),
+                 idesc, (kb | k) != 0);
+      }
+      umma_commit(&empty[s]);  // the stage is free once these MMAs have read it
+    }
+    if (ok) umma_commit(accum);
+  }
+
+  // ---- epilogue: all four warps -----------------------------------------------------
+  __syncwarp();
+  bool have = mbar_wait(accum, 0);
+  if (!have) *failed = 1;
+  tc_fence_after();
+  if (have && *failed == 0) {
+    const int m = m0 + warp * 32 + lane;
+    const bool row_ok = m < M;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int n = n0 + c * 32;
+      if (n >= N) break;  // uniform over the CTA
+      uint32_t raw[32];
+      tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), raw);
+      tmem_ld_wait();
+      if (row_ok) {
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        v[j] = __uint_as_float(raw[j]);
+        if (bias != nullptr && n + j < N) v[j] += __ldg(bias + n + j);
+      }
+      const bool full_chunk = n + 32 <= N;
+      if (mode == OUT_BF16) {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = activate(v[j], act);
+        if (vec_ok && full_chunk) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 packed;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+            packed.x = *reinterpret_cast<uint32_t*>(&h0);
+            packed.y = *reinterpret_cast<uint32_t*>(&h1);
+            packed.z = *reinterpret_cast<uint32_t*>(&h2);
+            packed.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(dst + j) = packed;
+          }
+        } else {
+          for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+        }
+      } else {
+        float* dst = reinterpret_cast<float*>(out) + (size_t)m * ldo + n;
+        if (mode == OUT_F32) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = activate(v[j], act);
+        }
+        if (vec_ok && full_chunk) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            if (mode == OUT_RESIDUAL_F32) {
+              const float4 r = *reinterpret_cast<const float4*>(dst + j);
+              o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+            }
+            *reinterpret_cast<float4*>(dst + j) = o;
+          }
+        } else {
+          for (int j = 0; j < 32 && n + j < N; ++j) {
+            dst[j] = mode == OUT_RESIDUAL_F32 ? dst[j] + v[j] : v[j];
+          }
+        }
+      }
+      }  // row_ok
+      __syncwarp();  // the next tcgen05.ld needs the whole warp
+    }
+  }
+
+  // ---- teardown ---------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*failed != 0) {
+    if (warp == 0 && lane == 0) {
+      // copies this thread started may still be landing: wait for each started stage, bounded
+      for (int kb = issued > STAGES ? issued - STAGES : 0; kb < issued; ++kb) {
+        mbar_wait(&full[kb % STAGES], (kb / STAGES) & 1);
+      }
+      atomicExch(status, AYK_WAIT_TIMEOUT);
+    }
+    __syncthreads();
+  }
+  if (warp == 0) tmem_dealloc(tmem_base, BN < 32 ? 32 : BN);
+}
+
+// Tensor maps are cached by what they describe: weights are static and activations live in
+// persistent buffers, so a serving process encodes each map once.
+struct MapKey {
+  const void* base;
+  uint64_t rows, cols, ld;
+  uint32_t box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld &&
+           box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.base;
+    h = h * 1000003u ^ k.rows;
+    h = h * 1000003u ^ k.cols;
+    h = h * 1000003u ^ k.ld;
+    h = h * 1000003u ^ k.box_rows;
+    return h;
+  }
+};
+
+static int cached_map(const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                      uint32_t box_rows, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  const MapKey key{base, rows, cols, ld, box_rows};
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    CUtensorMap map;
+    const int r = make_map_bf16_k64(&map, base, rows, cols, ld, box_rows);
+    if (r != AYK_OK) return r;
+    if (cache.size() > 4096) cache.clear();
+    it = cache.emplace(key, map).first;
+  }
+  *out = it->second;
+  return AYK_OK;
+}
+
+template <int BN, int STAGES>
+int launch_gemm_tc(const void* a, int lda, const void* w, int ldw, const float* bias, void* out,
+                   int ldo, int M, int N, int K, int act, int mode, int* status,
+                   cudaStream_t stream) {
+  using L = TcSmem<BN, STAGES>;
+  CUtensorMap map_a, map_w;
+  int r = cached_map(a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BM, &map_a);
+  if (r != AYK_OK) return r;
+  r = cached_map(w, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN, &map_w);
+  if (r != AYK_OK) return r;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYNAMIC);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const size_t elem = mode == OUT_BF16 ? 2 : 4;
+  const int vec_ok = (((uintptr_t)out % 16) == 0 && ((size_t)ldo * elem) % 16 == 0) ? 1 : 0;
+  const long long gy = (M + TC_BM - 1) / TC_BM;
+  if (gy > 65535) return AYK_TOO_LARGE;
+  dim3 grid((N + BN - 1) / BN, (unsigned)gy);
+  gemm_tc_kernel<BN, STAGES><<<grid, 128, L::DYNAMIC, stream>>>(map_a, map_w, bias, out, ldo, M,
+                                                                N, K, act, mode, vec_ok, status);
+  return launch_status();
+}
+
+}  // namespace ayk
+
+// mode: 0 = bf16 out with activation, 1 = fp32 out with activation, 2 = fp32 out += (residual).
+// tile_n: 64, 128 or 256 (0 = choose). `status` is one device int that a CTA sets to
+// AYK_WAIT_TIMEOUT if a wait ran out; the host reads it when it checks a step.
+AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, const float* bias,
+                             void* out, int ldo, int M, int N, int K, int act, int mode,
+                             int tile_n, int* status, void* stream) {
+  using namespace ayk;
+  if (M == 0 || N == 0) return AYK_OK;
+  if (M < 0 || N < 0 || K < 1 || lda < K || ldw < K || ldo < N || status == nullptr) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (mode < OUT_BF16 || mode > OUT_RESIDUAL_F32 || act < ACT_NONE || act > ACT_GELU_ERF ||
+      (mode == OUT_RESIDUAL_F32 && act != ACT_NONE)) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (((uintptr_t)a % 16) || ((uintptr_t)w % 16) || (lda % 8) || (ldw % 8)) {
+    return AYK_BAD_ALIGNMENT;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  if (tile_n == 0) tile_n = 128;
+  switch (tile_n) {
+    case 64:
+      return launch_gemm_tc<64, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
+    case 128:
+      return launch_gemm_tc<128, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
+    case 256:
+      return launch_gemm_tc<256, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
+    default:
+      return AYK_BAD_ARGUMENT;
+  }
+}

@@ -1,0 +1,139 @@
+"""Compiling the CUDA sources with nvcc, one shared library per ``.cu`` file.
+
+Nothing is compiled at import. A library is built the first time a kernel of it is called
+(so a float32 run never builds the bfloat16 tensor-core kernels) or all at once by
+:func:`build_all`. Libraries are cached beside the sources in ``csrc/_build`` under a name
+that carries a hash of the source, its headers and the flags; when that folder cannot be
+written the cache goes to a per-user folder under the system's temporary directory. While
+nvcc runs, a line goes to standard error every few seconds.
+"""
+
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+from ayaka_b200.errors import BackendError
+
+__all__ = ["CSRC", "build_all", "ensure_built", "library_names"]
+
+CSRC = Path(__file__).resolve().parent.parent / "csrc"
+_FLAGS = (
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--shared", "-Xcompiler", "-fPIC",
+)
+_locks: dict[str, threading.Lock] = {}
+_locks_guard = threading.Lock()
+
+
+def library_names() -> list[str]:
+    """Every ``.cu`` file of the source folder, without its suffix."""
+    return sorted(path.stem for path in CSRC.glob("*.cu"))
+
+
+def _nvcc() -> str | None:
+    found = shutil.which("nvcc")
+    if found:
+        return found
+    for root in (os.environ.get("CUDA_HOME"), os.environ.get("CUDA_PATH"), "/usr/local/cuda"):
+        if root and (Path(root) / "bin" / "nvcc").is_file():
+            return str(Path(root) / "bin" / "nvcc")
+    return None
+
+
+def _digest(name: str) -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(_FLAGS).encode())
+    h.update((CSRC / f"{name}.cu").read_bytes())
+    for header in sorted(CSRC.glob("*.cuh")):
+        h.update(header.name.encode())
+        h.update(header.read_bytes())
+    return h.hexdigest()[:16]
+
+
+def _fallback_dir() -> Path:
+    return Path(tempfile.gettempdir()) / f"ayaka_b200-build-{os.getuid()}"
+
+
+def _writable_build_dir() -> Path:
+    preferred = CSRC / "_build"
+    try:
+        preferred.mkdir(exist_ok=True)
+        probe = preferred / f".write-test-{os.getpid()}-{threading.get_ident()}"
+        probe.write_bytes(b"")
+        probe.unlink()
+        return preferred
+    except OSError:
+        fallback = _fallback_dir()
+        fallback.mkdir(parents=True, exist_ok=True)
+        return fallback
+
+
+def _say(text: str) -> None:
+    print(f"ayaka_b200: {text}", file=sys.stderr, flush=True)
+
+
+def _compile(name: str, filename: str, verbose: bool) -> Path:
+    nvcc = _nvcc()
+    if nvcc is None:
+        raise BackendError(
+            f"the CUDA library of {name}.cu is not built and nvcc was not found; "
+            "this engine has no fallback path")
+    folder = _writable_build_dir()
+    target = folder / filename
+    partial = folder / f".{filename}.{os.getpid()}.{threading.get_ident()}.tmp"
+    command = [nvcc, *_FLAGS, "-I", str(CSRC), "-o", str(partial), str(CSRC / f"{name}.cu")]
+    if verbose:
+        _say(f"compiling {name}.cu for sm_100a ...")
+    started = time.monotonic()
+    process = subprocess.Popen(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                               text=True, cwd=str(folder))
+    finished = threading.Event()
+
+    def heartbeat() -> None:
+        while not finished.wait(10.0):
+            _say(f"still compiling {name}.cu ({time.monotonic() - started:.0f} s)")
+
+    if verbose:
+        threading.Thread(target=heartbeat, daemon=True).start()
+    output, _ = process.communicate()
+    finished.set()
+    if process.returncode != 0:
+        partial.unlink(missing_ok=True)
+        raise BackendError(f"nvcc failed on {name}.cu:\n{output}")
+    os.replace(partial, target)
+    for stale in folder.glob(f"libayk_{name}.*.so"):
+        if stale != target:
+            stale.unlink(missing_ok=True)
+    if verbose:
+        _say(f"compiled {name}.cu in {time.monotonic() - started:.1f} s")
+    return target
+
+
+def ensure_built(name: str, *, verbose: bool = True) -> Path:
+    """Return the path of the shared library of ``csrc/<name>.cu``, compiling it if needed."""
+    if not (CSRC / f"{name}.cu").is_file():
+        raise BackendError(f"no CUDA source {CSRC / (name + '.cu')}")
+    with _locks_guard:
+        lock = _locks.setdefault(name, threading.Lock())
+    with lock:
+        filename = f"libayk_{name}.{_digest(name)}.so"
+        for folder in (CSRC / "_build", _fallback_dir()):
+            if (folder / filename).is_file():
+                return folder / filename
+        return _compile(name, filename, verbose)
+
+
+def build_all(*, verbose: bool = True) -> list[Path]:
+    """Compile every library, several nvcc processes at a time, and return their paths."""
+    names = library_names()
+    with ThreadPoolExecutor(max_workers=max(1, min(os.cpu_count() or 1, len(names)))) as pool:
+        return list(pool.map(lambda name: ensure_built(name, verbose=verbose), names))

@@ -1,0 +1,60 @@
+"""The bfloat16 tensor-core matrix product's Python side: argument rules, the status word."""
+
+from __future__ import annotations
+
+from ctypes import c_int, c_void_p
+
+import torch
+
+from ayaka_b200.errors import BackendError
+from ayaka_b200.kernels.lib import check, library
+
+__all__ = ["check_status", "linear_bf16", "status_word"]
+
+_status: dict[int, torch.Tensor] = {}
+
+#: tile width (columns of the output per CTA) the next calls use; 0 lets the library choose.
+TILE_N = 0
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """One int32 per device that a kernel sets when a bounded wait ran out."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    word = _status.get(index)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", index))
+        _status[index] = word
+    return word
+
+
+def check_status(device: torch.device) -> None:
+    """Read the status word (a device synchronisation) and raise if a kernel gave up."""
+    word = status_word(device)
+    value = int(word.item())
+    if value:
+        word.zero_()
+        check(value, "tensor-core kernel")
+
+
+def usable(a: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether TMA can read these operands: 16-byte aligned, row strides multiples of 8."""
+    return (a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+            and a.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0)
+
+
+def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
+                out: torch.Tensor, rows: int, activation: int, residual: bool,
+                tile_n: int | None = None) -> None:
+    if not usable(a, weight):
+        raise BackendError("linear: operands break the TMA rules (16-byte aligned, row strides "
+                           "multiples of 8 elements)")
+    n, k = weight.shape
+    mode = 2 if residual else (0 if out.dtype == torch.bfloat16 else 1)
+    fn = library("gemm_tc").ayk_gemm_bf16_tc
+    status = fn(c_void_p(a.data_ptr()), c_int(a.stride(0)), c_void_p(weight.data_ptr()),
+                c_int(weight.stride(0)), c_void_p(0 if bias is None else bias.data_ptr()),
+                c_void_p(out.data_ptr()), c_int(out.stride(0)), c_int(rows), c_int(n), c_int(k),
+                c_int(activation), c_int(mode), c_int(TILE_N if tile_n is None else tile_n),
+                c_void_p(status_word(a.device).data_ptr()),
+                c_void_p(torch.cuda.current_stream().cuda_stream))
+    check(status, "linear (tcgen05)")

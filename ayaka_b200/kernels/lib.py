@@ -1,0 +1,50 @@
+"""Loading the CUDA libraries through ctypes and checking what their entry points return."""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+
+from ayaka_b200.errors import BackendError
+from ayaka_b200.kernels.build import ensure_built
+
+__all__ = ["check", "library", "loaded_libraries"]
+
+_REFUSALS = {
+    -1: "an argument the kernel does not take (a size, a stride or a missing pointer)",
+    -2: "a pointer or stride that breaks the kernel's alignment rule",
+    -3: "a size beyond the kernel's stated maximum",
+    -4: "a CUDA driver entry point is missing or failed",
+    -5: "a device-side wait ran out; the kernel gave up and reported it",
+}
+_libraries: dict[str, ctypes.CDLL] = {}
+_guard = threading.Lock()
+
+
+def library(name: str) -> ctypes.CDLL:
+    """The shared library built from ``csrc/<name>.cu``; built on first use, loaded once."""
+    with _guard:
+        found = _libraries.get(name)
+        if found is None:
+            path = ensure_built(name)
+            try:
+                found = ctypes.CDLL(str(path))
+            except OSError as error:
+                raise BackendError(f"cannot load {path}: {error}") from None
+            _libraries[name] = found
+        return found
+
+
+def loaded_libraries() -> list[str]:
+    """Names of the libraries this process has loaded so far."""
+    return sorted(_libraries)
+
+
+def check(status: int, op: str) -> None:
+    """Raise :class:`BackendError` unless an entry point returned 0."""
+    if status == 0:
+        return
+    if status < 0:
+        reason = _REFUSALS.get(status, f"refusal code {status}")
+        raise BackendError(f"{op}: {reason}", context={"op": op, "status": status})
+    raise BackendError(f"{op}: CUDA error {status} at launch", context={"op": op, "status": status})

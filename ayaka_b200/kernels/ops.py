@@ -1,0 +1,251 @@
+"""The kernels as functions over torch tensors.
+
+Every function writes into tensors the caller allocated and launches on torch's current
+CUDA stream. Tensors are on one CUDA device; 2-D tensors may have any row stride but a unit
+stride along the last dimension. Nothing here falls back to torch arithmetic: a missing
+library or a refused argument raises :class:`~ayaka_b200.errors.BackendError`.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from ayaka_b200.errors import BackendError
+from ayaka_b200.kernels.lib import check, library
+
+__all__ = [
+    "ACTIVATIONS",
+    "argmax",
+    "attention",
+    "embed_rows",
+    "kv_store",
+    "layer_norm",
+    "linear",
+]
+
+ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2}
+_TYPE = {torch.float32: 0, torch.bfloat16: 1}
+
+#: Which bfloat16 matrix-product kernel :func:`linear` launches: ``"tcgen05"`` (the tensor
+#: cores, the serving path) or ``"simt"`` (the CUDA-core reference); tests switch it.
+BF16_GEMM = "tcgen05"
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(tensor: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if tensor is None else tensor.data_ptr())
+
+
+def _need(op: str, name: str, tensor: torch.Tensor, dtype: torch.dtype | None = None,
+          ndim: int | None = None) -> None:
+    if not tensor.is_cuda:
+        raise BackendError(f"{op}: {name} must be on a CUDA device, it is on {tensor.device}")
+    if dtype is not None and tensor.dtype != dtype:
+        raise BackendError(f"{op}: {name} must be {dtype}, got {tensor.dtype}")
+    if ndim is not None and tensor.ndim != ndim:
+        raise BackendError(f"{op}: {name} must have {ndim} dimensions, got {tensor.ndim}")
+    if tensor.ndim and tensor.numel() and tensor.stride(-1) != 1:
+        raise BackendError(f"{op}: {name} must have a unit stride along its last dimension")
+
+
+def embed_rows(table: torch.Tensor, index: torch.Tensor, out: torch.Tensor, *,
+               add_table: torch.Tensor | None = None, add_index: torch.Tensor | None = None,
+               bad_index: torch.Tensor) -> None:
+    """``out[i] = table[index[i]] (+ add_table[add_index[i]])`` as fp32 rows.
+
+    ``bad_index`` is one int32 on the device that the kernel sets to 1 if an id is outside
+    its table.
+    """
+    op = "embed_rows"
+    _need(op, "table", table, ndim=2)
+    _need(op, "index", index, torch.int32, 1)
+    _need(op, "out", out, torch.float32, 2)
+    _need(op, "bad_index", bad_index, torch.int32)
+    if table.dtype not in _TYPE or not table.is_contiguous():
+        raise BackendError(f"{op}: table must be contiguous float32 or bfloat16")
+    rows, width = index.shape[0], table.shape[1]
+    if out.shape[0] < rows or out.shape[1] != width:
+        raise BackendError(f"{op}: out {list(out.shape)} does not hold [{rows}, {width}]")
+    if add_table is not None:
+        if add_index is None:
+            raise BackendError(f"{op}: add_table needs add_index")
+        _need(op, "add_table", add_table, table.dtype, 2)
+        _need(op, "add_index", add_index, torch.int32, 1)
+        if add_table.shape[1] != width or add_index.shape[0] != rows or \
+                not add_table.is_contiguous():
+            raise BackendError(f"{op}: add_table/add_index do not match the rows")
+    name = "ayk_embed_rows_f32" if table.dtype == torch.float32 else "ayk_embed_rows_bf16"
+    fn = getattr(library("embed"), name)
+    status = fn(_ptr(table), _ptr(index), c_int(table.shape[0]), _ptr(add_table),
+                _ptr(add_index), c_int(0 if add_table is None else add_table.shape[0]),
+                _ptr(out), c_int(out.stride(0)), c_int(rows), c_int(width), _ptr(bad_index),
+                _stream())
+    check(status, op)
+
+
+def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor | None, eps: float,
+               out: torch.Tensor, *, rows: torch.Tensor | None = None,
+               count: int | None = None) -> None:
+    """LayerNorm of fp32 rows into ``out`` (float32 or bfloat16).
+
+    With ``rows`` (int32), output row ``i`` normalises ``x[rows[i]]``. ``count`` limits the
+    number of output rows (default: all of ``rows`` or of ``x``).
+    """
+    op = "layer_norm"
+    _need(op, "x", x, torch.float32, 2)
+    _need(op, "gamma", gamma, torch.float32, 1)
+    if beta is not None:
+        _need(op, "beta", beta, torch.float32, 1)
+    _need(op, "out", out, ndim=2)
+    if out.dtype not in _TYPE:
+        raise BackendError(f"{op}: out must be float32 or bfloat16, got {out.dtype}")
+    width = x.shape[1]
+    if gamma.shape[0] != width or (beta is not None and beta.shape[0] != width) or \
+            out.shape[1] != width:
+        raise BackendError(f"{op}: widths differ")
+    if rows is not None:
+        _need(op, "rows", rows, torch.int32, 1)
+    n = count if count is not None else (rows.shape[0] if rows is not None else x.shape[0])
+    if n > out.shape[0] or (rows is None and n > x.shape[0]) or \
+            (rows is not None and n > rows.shape[0]):
+        raise BackendError(f"{op}: {n} rows do not fit the tensors")
+    name = "ayk_layer_norm_f32" if out.dtype == torch.float32 else "ayk_layer_norm_bf16"
+    fn = getattr(library("norm"), name)
+    status = fn(_ptr(x), c_int(x.stride(0)), _ptr(rows), _ptr(gamma), _ptr(beta),
+                c_float(eps), _ptr(out), c_int(out.stride(0)), c_int(n), c_int(width), _stream())
+    check(status, op)
+
+
+def linear(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor,
+           *, activation: str = "none", residual: bool = False, rows: int | None = None,
+           kernel: str | None = None) -> None:
+    """``out = act(a @ weight.T + bias)``, or ``out += a @ weight.T + bias`` with ``residual``.
+
+    ``a`` is ``[M, K]``, ``weight`` ``[N, K]`` (both float32, or both bfloat16), ``bias``
+    float32 ``[N]``. ``out`` is ``[M, N]``: float32 always allowed (and required with
+    ``residual``), bfloat16 for bfloat16 inputs. ``rows`` limits M. float32 inputs run on
+    the CUDA cores with fp32 FMA (no reduced-precision matrix mode); bfloat16 inputs on the
+    tensor cores unless ``kernel="simt"``.
+    """
+    op = "linear"
+    _need(op, "a", a, ndim=2)
+    _need(op, "weight", weight, a.dtype, 2)
+    _need(op, "out", out, ndim=2)
+    if a.dtype not in _TYPE or out.dtype not in _TYPE:
+        raise BackendError(f"{op}: float32 and bfloat16 only, got {a.dtype} -> {out.dtype}")
+    if bias is not None:
+        _need(op, "bias", bias, torch.float32, 1)
+    m = a.shape[0] if rows is None else rows
+    n, k = weight.shape
+    if a.shape[1] != k or m > a.shape[0] or m > out.shape[0] or out.shape[1] != n or \
+            (bias is not None and bias.shape[0] != n):
+        raise BackendError(
+            f"{op}: shapes a{list(a.shape)} w{list(weight.shape)} out{list(out.shape)} "
+            f"rows={m} do not fit")
+    if activation not in ACTIVATIONS:
+        raise BackendError(f"{op}: unknown activation {activation!r}")
+    if residual and (out.dtype != torch.float32 or activation != "none"):
+        raise BackendError(f"{op}: a residual sum is float32 and has no activation")
+    if a.dtype == torch.float32 and out.dtype != torch.float32:
+        raise BackendError(f"{op}: float32 inputs give float32 output")
+    which = kernel or (BF16_GEMM if a.dtype == torch.bfloat16 else "simt")
+    if which == "tcgen05" and a.dtype == torch.bfloat16:
+        from ayaka_b200.kernels import gemm_tc
+
+        # operands TMA cannot read (a row stride that is no multiple of 8 elements) go to
+        # the CUDA-core kernel: slower, same result
+        if kernel == "tcgen05" or gemm_tc.usable(a, weight):
+            gemm_tc.linear_bf16(a, weight, bias, out, m, ACTIVATIONS[activation], residual)
+            return
+    fn = library("gemm_simt").ayk_gemm_simt
+    status = fn(_ptr(a), c_int(a.stride(0)), _ptr(weight), c_int(weight.stride(0)), _ptr(bias),
+                _ptr(out), c_int(out.stride(0)), c_int(m), c_int(n), c_int(k),
+                c_int(ACTIVATIONS[activation]), c_int(1 if residual else 0),
+                c_int(_TYPE[a.dtype]), c_int(_TYPE[out.dtype]), _stream())
+    check(status, op)
+
+
+def kv_store(k: torch.Tensor, v: torch.Tensor, slot_mapping: torch.Tensor,
+             k_pages: torch.Tensor, v_pages: torch.Tensor, *, rows: int | None = None) -> None:
+    """Write this step's key and value rows ``[N, kv_heads * head_dim]`` into the pages.
+
+    Pages are ``[page, kv_head, slot, head_dim]``; ``slot_mapping[i] = page * page_size +
+    slot`` or negative for a row that stores nothing. ``k`` and ``v`` share a row stride (they
+    are column ranges of one projection output).
+    """
+    op = "kv_store"
+    _need(op, "k", k, ndim=2)
+    _need(op, "v", v, k.dtype, 2)
+    _need(op, "slot_mapping", slot_mapping, torch.int32, 1)
+    _need(op, "k_pages", k_pages, k.dtype, 4)
+    _need(op, "v_pages", v_pages, k.dtype, 4)
+    if k.dtype not in _TYPE or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+        raise BackendError(f"{op}: contiguous float32 or bfloat16 pages only")
+    _, kv_heads, page_size, head_dim = k_pages.shape
+    n = k.shape[0] if rows is None else rows
+    if k.shape[1] != kv_heads * head_dim or v.shape != k.shape or k.stride(0) != v.stride(0) \
+            or v_pages.shape != k_pages.shape or n > k.shape[0] or n > slot_mapping.shape[0]:
+        raise BackendError(f"{op}: shapes do not fit")
+    fn = library("attention_simt").ayk_kv_store
+    status = fn(_ptr(k), _ptr(v), c_int(k.stride(0)), _ptr(slot_mapping), _ptr(k_pages),
+                _ptr(v_pages), c_int(n), c_int(kv_heads), c_int(head_dim), c_int(page_size),
+                c_int(_TYPE[k.dtype]), _stream())
+    check(status, op)
+
+
+def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+              block_table: torch.Tensor, request_of_row: torch.Tensor, positions: torch.Tensor,
+              out: torch.Tensor, *, num_heads: int, scale: float, window: int = 0,
+              rows: int | None = None) -> None:
+    """Causal attention of query rows over their requests' cached keys and values.
+
+    ``q`` and ``out`` are ``[N, num_heads * head_dim]``; row ``i`` belongs to request
+    ``request_of_row[i]`` (a row of ``block_table``; negative = padding row, output zero) and
+    sits at ``positions[i]``; it sees keys ``max(0, p - window + 1) .. p`` (``window`` 0 = all).
+    The keys of the step's own rows must already be stored.
+    """
+    op = "attention"
+    _need(op, "q", q, ndim=2)
+    _need(op, "out", out, q.dtype, 2)
+    _need(op, "k_pages", k_pages, q.dtype, 4)
+    _need(op, "v_pages", v_pages, q.dtype, 4)
+    _need(op, "block_table", block_table, torch.int32, 2)
+    _need(op, "request_of_row", request_of_row, torch.int32, 1)
+    _need(op, "positions", positions, torch.int32, 1)
+    if q.dtype not in _TYPE or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+        raise BackendError(f"{op}: contiguous float32 or bfloat16 pages only")
+    _, kv_heads, page_size, head_dim = k_pages.shape
+    n = q.shape[0] if rows is None else rows
+    if q.shape[1] != num_heads * head_dim or out.shape[1] != q.shape[1] or n > out.shape[0] \
+            or n > request_of_row.shape[0] or n > positions.shape[0] or \
+            v_pages.shape != k_pages.shape:
+        raise BackendError(f"{op}: shapes do not fit")
+    fn = library("attention_simt").ayk_attention_simt
+    status = fn(_ptr(q), c_int(q.stride(0)), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                c_int(block_table.stride(0)), _ptr(request_of_row), _ptr(positions), _ptr(out),
+                c_int(out.stride(0)), c_int(n), c_int(num_heads), c_int(kv_heads),
+                c_int(head_dim), c_int(page_size), c_float(scale), c_int(window),
+                c_int(_TYPE[q.dtype]), _stream())
+    check(status, op)
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor, *, rows: int | None = None) -> None:
+    """``out[i]`` = the id of row ``i``'s largest logit, the smallest id among equals."""
+    op = "argmax"
+    _need(op, "logits", logits, torch.float32, 2)
+    _need(op, "out", out, torch.int32, 1)
+    n = logits.shape[0] if rows is None else rows
+    if n > out.shape[0] or n > logits.shape[0]:
+        raise BackendError(f"{op}: {n} rows do not fit")
+    status = library("sampling").ayk_argmax(_ptr(logits), c_int(logits.stride(0)), c_int(n),
+                                            c_int(logits.shape[1]), _ptr(out), _stream())
+    check(status, op)
+
+
+_ = ctypes  # keep the import for type names used by callers

@@ -1,0 +1,78 @@
+"""The one model class: a decoder assembled from a :class:`ModelSpec`.
+
+It owns the embedding, the position encoding, one block per layer, the final norm and the
+head, and runs the layers in the order the spec lists. It knows nothing of GPT-2: another
+architecture is another spec.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ayaka_b200.parts.base import BuildContext, CacheNeed, Part, StateNeed, build_part
+from ayaka_b200.parts.context import LayerCache, StepContext
+from ayaka_b200.parts.spec import ModelSpec
+
+__all__ = ["DecoderModel"]
+
+
+class DecoderModel(Part):
+    """Embedding -> runs of blocks -> final norm on the wanted rows -> head (fp32 logits).
+
+    Parameter names: ``embedding.weight``, ``position.*``, ``layers.<i>.<part>.*``,
+    ``final_norm.*`` and, when the head is not tied, ``head.weight``.
+    """
+
+    def __init__(self, spec: ModelSpec, ctx: BuildContext) -> None:
+        super().__init__(ctx)
+        self.spec = spec
+        self.embedding = self.add_child(
+            "embedding", build_part("embedding", spec.embedding.kind, spec.embedding, ctx))
+        self.position = self.add_child(
+            "position", build_part("position", spec.position.kind, spec.position, ctx))
+        layers = Part(ctx)
+        self.add_child("layers", layers)
+        self.blocks: list[Part] = []
+        for index, layer in enumerate(spec.layers):
+            block = build_part("block", layer.block, layer, ctx, self.position)
+            layers.add_child(str(index), block)
+            self.blocks.append(block)
+        self.final_norm = self.add_child(
+            "final_norm", build_part("norm", spec.final_norm.kind, spec.final_norm, ctx))
+        self.head = self.add_child(
+            "head", build_part("head", spec.head.kind, spec.head, ctx, self.embedding))
+        for position, run in enumerate(spec.order):
+            if not 0 <= run.layer < len(self.blocks):
+                raise ValueError(f"order[{position}] names layer {run.layer}, which does not "
+                                 "exist")
+            if run.reads_cache_of is not None and not 0 <= run.reads_cache_of < position:
+                raise ValueError(f"order[{position}] must read the cache of an earlier run")
+
+    def needs(self) -> list[tuple[CacheNeed | None, StateNeed | None]]:
+        """For each run of the order: the pages and the state its mixer asks for."""
+        out = []
+        for run in self.spec.order:
+            mixer = self.blocks[run.layer].mixer  # type: ignore[attr-defined]
+            out.append((mixer.cache_need(), mixer.state_need()))
+        return out
+
+    def forward(self, step: StepContext, caches: list[LayerCache],
+                want_rows: torch.Tensor | None, num_want: int) -> torch.Tensor | None:
+        """Run the step's rows; return fp32 logits ``[num_want, vocab]`` (a view of a
+        persistent buffer) at the rows listed in ``want_rows``, or ``None`` if none is wanted."""
+        spec = self.spec
+        residual = step.workspace.buffer("model.residual", spec.hidden_size, torch.float32)
+        self.embedding.forward(  # type: ignore[attr-defined]
+            step, residual, self.position.added_rows(step))  # type: ignore[attr-defined]
+        for index, run in enumerate(spec.order):
+            self.blocks[run.layer].forward(residual, step, caches[index])  # type: ignore
+        if num_want == 0 or want_rows is None:
+            return None
+        chosen = step.workspace.buffer("model.head_in", spec.hidden_size, self.ctx.dtype,
+                                       rows=num_want)
+        self.final_norm.forward(residual, chosen, count=num_want,  # type: ignore[attr-defined]
+                                rows=want_rows)
+        logits = step.workspace.buffer("model.logits", spec.vocab_size, torch.float32,
+                                       rows=num_want)
+        self.head.forward(chosen, logits, count=num_want)  # type: ignore[attr-defined]
+        return logits[:num_want]

@@ -1,0 +1,50 @@
+"""Arrangements: how one layer wires its norms, its mixer and its feed-forward."""
+
+from __future__ import annotations
+
+import torch
+
+from ayaka_b200.parts.base import BuildContext, Part, build_part, register_part
+from ayaka_b200.parts.context import LayerCache, StepContext
+from ayaka_b200.parts.spec import LayerSpec
+
+__all__ = ["Block", "PreNormBlock"]
+
+
+class Block(Part):
+    """Interface of an arrangement: ``forward(residual, step, cache)`` updates the fp32
+    residual stream ``[N, width]`` in place. ``mixer`` is exposed for the cache planner."""
+
+    mixer: Part
+
+    def forward(self, residual: torch.Tensor, step: StepContext, cache: LayerCache) -> None:
+        raise NotImplementedError
+
+
+@register_part("block", "pre_norm")
+class PreNormBlock(Block):
+    """``x += mixer(norm(x)); x += feed_forward(norm(x))`` — GPT-2's block
+    (``python/ayaka/models/gpt2.py:99-101``). The sums happen in fp32 inside the last matrix
+    product of each half."""
+
+    def __init__(self, spec: LayerSpec, ctx: BuildContext, position: Part | None) -> None:
+        super().__init__(ctx)
+        self.mixer_norm = self.add_child(
+            "mixer_norm", build_part("norm", spec.mixer_norm.kind, spec.mixer_norm, ctx))
+        self.mixer = self.add_child(
+            "mixer", build_part("mixer", spec.mixer.kind, spec.mixer, ctx, position))
+        self.feed_forward_norm = self.add_child(
+            "feed_forward_norm",
+            build_part("norm", spec.feed_forward_norm.kind, spec.feed_forward_norm, ctx))
+        self.feed_forward = self.add_child(
+            "feed_forward",
+            build_part("feed_forward", spec.feed_forward.kind, spec.feed_forward, ctx))
+        self.width = int(spec.mixer_norm.width)  # type: ignore[arg-type]
+
+    def forward(self, residual: torch.Tensor, step: StepContext, cache: LayerCache) -> None:
+        n = step.num_rows
+        hidden = step.workspace.buffer("block.normed", self.width, self.ctx.dtype)
+        self.mixer_norm.forward(residual, hidden, count=n)  # type: ignore[attr-defined]
+        self.mixer.forward(hidden, residual, step, cache)  # type: ignore[attr-defined]
+        self.feed_forward_norm.forward(residual, hidden, count=n)  # type: ignore[attr-defined]
+        self.feed_forward.forward(hidden, residual, step)  # type: ignore[attr-defined]

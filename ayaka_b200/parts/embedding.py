@@ -1,0 +1,104 @@
+"""Token embedding, position encodings and the output head."""
+
+from __future__ import annotations
+
+import torch
+
+from ayaka_b200.kernels import ops
+from ayaka_b200.parts.base import BuildContext, Part, register_part
+from ayaka_b200.parts.context import StepContext
+from ayaka_b200.parts.spec import PartSpec
+
+__all__ = ["LearnedPositions", "LinearHead", "NoPositions", "TokenEmbedding"]
+
+
+class PositionEncoding(Part):
+    """Interface of a position encoding.
+
+    ``added_rows(step)`` returns ``(table, index)`` for an encoding that adds one table row
+    per token to the embedding (fused into the embedding kernel), or ``None``.
+    ``on_query_key(q, k, step)`` lets an encoding change queries and keys in place before the
+    keys are cached (a rotary encoding); the default does nothing.
+    ``max_positions`` bounds a sequence, or is ``None``.
+    """
+
+    max_positions: int | None = None
+
+    def added_rows(self, step: StepContext) -> tuple[torch.Tensor, torch.Tensor] | None:
+        return None
+
+    def on_query_key(self, q: torch.Tensor, k: torch.Tensor, step: StepContext) -> None:
+        return None
+
+
+@register_part("position", "learned")
+class LearnedPositions(PositionEncoding):
+    """A table ``[max_positions, width]`` whose row ``p`` is added to the token at position
+    ``p`` (the reference's ``wpe``, ``python/ayaka/models/gpt2.py:147-149, 175``).
+
+    Spec parameters: ``max_positions``, ``width``.
+    """
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext) -> None:
+        super().__init__(ctx)
+        self.max_positions = int(spec.max_positions)  # type: ignore[arg-type]
+        self.weight = self.add_param(
+            "weight", (self.max_positions, int(spec.width)), "table")  # type: ignore[arg-type]
+
+    def added_rows(self, step: StepContext) -> tuple[torch.Tensor, torch.Tensor]:
+        return self.weight, step.positions
+
+
+@register_part("position", "none")
+class NoPositions(PositionEncoding):
+    """No position signal at all (for toy models in tests)."""
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext) -> None:
+        super().__init__(ctx)
+
+
+@register_part("embedding", "token")
+class TokenEmbedding(Part):
+    """Row gather from ``[vocab_size, width]`` into the fp32 residual stream.
+
+    Spec parameters: ``vocab_size``, ``width``.
+    """
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext) -> None:
+        super().__init__(ctx)
+        self.vocab_size = int(spec.vocab_size)  # type: ignore[arg-type]
+        self.width = int(spec.width)  # type: ignore[arg-type]
+        self.weight = self.add_param("weight", (self.vocab_size, self.width), "table")
+
+    def forward(self, step: StepContext, out: torch.Tensor,
+                added: tuple[torch.Tensor, torch.Tensor] | None) -> None:
+        table, index = added if added is not None else (None, None)
+        ops.embed_rows(self.weight, step.tokens[:step.num_rows], out,
+                       add_table=table,
+                       add_index=None if index is None else index[:step.num_rows],
+                       bad_index=step.bad_index)
+
+
+@register_part("head", "linear")
+class LinearHead(Part):
+    """``logits = hidden @ weight.T`` in fp32, no bias; ``weight`` is the embedding table when
+    tied (``python/ayaka/layers/embedding/token.py:81-100``).
+
+    Spec parameters: ``vocab_size``, ``width``, ``tied`` (bool).
+    """
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext,
+                 embedding: TokenEmbedding | None = None) -> None:
+        super().__init__(ctx)
+        self.vocab_size = int(spec.vocab_size)  # type: ignore[arg-type]
+        self.tied = bool(spec.get("tied", True))
+        if self.tied:
+            if embedding is None:
+                raise ValueError("a tied head needs the embedding it shares")
+            self.weight = embedding.weight  # the same tensor, not declared twice
+        else:
+            self.weight = self.add_param(
+                "weight", (self.vocab_size, int(spec.width)), "matrix")  # type: ignore[arg-type]
+
+    def forward(self, hidden: torch.Tensor, logits: torch.Tensor, *, count: int) -> None:
+        ops.linear(hidden, self.weight, None, logits, rows=count)

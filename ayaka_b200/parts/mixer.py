@@ -1,0 +1,96 @@
+"""Mixers: the parts that let a token see other tokens. Here: causal multi-head attention."""
+
+from __future__ import annotations
+
+import torch
+
+from ayaka_b200.kernels import ops
+from ayaka_b200.parts.base import BuildContext, CacheNeed, Part, StateNeed, register_part
+from ayaka_b200.parts.context import LayerCache, StepContext
+from ayaka_b200.parts.spec import PartSpec
+
+__all__ = ["Attention", "Mixer"]
+
+
+class Mixer(Part):
+    """Interface of a mixer.
+
+    ``cache_need()`` says which paged keys/values the mixer wants (or ``None``);
+    ``state_need()`` which fixed-size per-request state (or ``None``). ``forward`` reads
+    ``hidden`` (``[N, width]`` in the compute dtype: the normalised residual), and **adds**
+    its result to ``residual`` (fp32 ``[N, width]``) in place. It may use ``cache`` as its
+    needs say and ``step.workspace`` for scratch.
+    """
+
+    def cache_need(self) -> CacheNeed | None:
+        return None
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def forward(self, hidden: torch.Tensor, residual: torch.Tensor, step: StepContext,
+                cache: LayerCache) -> None:
+        raise NotImplementedError
+
+
+@register_part("mixer", "attention")
+class Attention(Mixer):
+    """Causal attention with one fused query/key/value projection and an output projection.
+
+    ``qkv = h @ Wqkv.T + b`` with columns ordered queries, keys, values; keys and values go
+    to the cache before attending, so a row sees itself; ``scores = scale * q.k`` over keys
+    ``max(0, p - window + 1) .. p``, softmax and the weighted sum in fp32; then
+    ``residual += o @ Wout.T + b`` (the reference's ``python/ayaka/layers/attention/dense.py:
+    101-125`` and ``python/ayaka/ops/attention.py:15-24, 133-137``).
+
+    Spec parameters: ``width``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale``
+    (the factor on q.k, given by the architecture: this part has no default), ``window``
+    (0 = none), ``bias`` (bool).
+    """
+
+    def __init__(self, spec: PartSpec, ctx: BuildContext, position: Part | None = None) -> None:
+        super().__init__(ctx)
+        self.width = int(spec.width)  # type: ignore[arg-type]
+        self.num_heads = int(spec.num_heads)  # type: ignore[arg-type]
+        self.num_kv_heads = int(spec.num_kv_heads)  # type: ignore[arg-type]
+        self.head_dim = int(spec.head_dim)  # type: ignore[arg-type]
+        self.scale = float(spec.scale)  # type: ignore[arg-type]
+        self.window = int(spec.get("window", 0))  # type: ignore[arg-type]
+        self.position = position
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"num_kv_heads ({self.num_kv_heads}) must divide num_heads "
+                             f"({self.num_heads})")
+        if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
+            raise ValueError(f"head_dim must be a multiple of 16 in [16, 256], got "
+                             f"{self.head_dim}")
+        bias = bool(spec.get("bias", True))
+        self.q_width = self.num_heads * self.head_dim
+        self.kv_width = self.num_kv_heads * self.head_dim
+        out_features = self.q_width + 2 * self.kv_width
+        self.qkv_weight = self.add_param("qkv.weight", (out_features, self.width), "matrix")
+        self.qkv_bias = self.add_param("qkv.bias", (out_features,), "vector") if bias else None
+        self.out_weight = self.add_param("out.weight", (self.width, self.q_width), "matrix")
+        self.out_bias = self.add_param("out.bias", (self.width,), "vector") if bias else None
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(self.num_kv_heads, self.head_dim, self.window)
+
+    def forward(self, hidden: torch.Tensor, residual: torch.Tensor, step: StepContext,
+                cache: LayerCache) -> None:
+        n = step.num_rows
+        group = step.groups[cache.group]  # type: ignore[index]
+        qkv = step.workspace.buffer("attention.qkv", self.q_width + 2 * self.kv_width,
+                                    self.ctx.dtype)
+        ops.linear(hidden, self.qkv_weight, self.qkv_bias, qkv, rows=n)
+        q = qkv[:, :self.q_width]
+        k = qkv[:, self.q_width:self.q_width + self.kv_width]
+        v = qkv[:, self.q_width + self.kv_width:]
+        if self.position is not None:
+            self.position.on_query_key(q, k, step)  # type: ignore[attr-defined]
+        if cache.writes:
+            ops.kv_store(k, v, group.slot_mapping, cache.k_pages, cache.v_pages, rows=n)
+        attended = step.workspace.buffer("attention.out", self.q_width, self.ctx.dtype)
+        ops.attention(q, cache.k_pages, cache.v_pages, group.block_table, step.request_of_row,
+                      step.positions, attended, num_heads=self.num_heads, scale=self.scale,
+                      window=self.window, rows=n)
+        ops.linear(attended, self.out_weight, self.out_bias, residual, residual=True, rows=n)

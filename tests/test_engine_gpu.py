@@ -1,0 +1,179 @@
+"""The engine against the plain implementation under every way of cutting the work, in
+float32 and in bfloat16, on three tiny configurations that differ in every size and option.
+
+A difference that shows in only one way of cutting points at the cache or the batch; the
+failure message names the first wrong position with its page and slot."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import engine_support as es
+from cases import INIT_LOUD, TINY_A, TINY_B, TINY_C, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+LENGTHS = {"A": (5, 17, 32, 9, 100, 128), "B": (1, 64, 130, 200, 47), "C": (70, 33, 250, 2)}
+DTYPES = ("float32", "bfloat16")
+
+
+def sequences_of(name: str) -> dict[str, list[int]]:
+    vocab = CONFIGS[name]["vocab_size"]
+    return {f"{name.lower()}{index}": random_tokens(vocab, length, 100 * ord(name) + index)
+            for index, length in enumerate(LENGTHS[name])}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    """(model folder, float32 state for the plain side, config) per (config, dtype)."""
+    made = {}
+    for name, config in CONFIGS.items():
+        for dtype in DTYPES:
+            folder = tmp_path_factory.mktemp(f"tiny_{name}_{dtype}")
+            made[name, dtype] = (*es.make_model(folder, config, seed=ord(name), init=INIT_LOUD,
+                                                dtype=dtype), config)
+    return made
+
+
+@pytest.fixture(scope="module")
+def expected(models):
+    return {key: es.plain_logits(state, config, sequences_of(key[0]))
+            for key, (_, state, config) in models.items()}
+
+
+def _pages_for(sequences, extra=0):
+    return sum(-(-len(t) // es.PAGE) for t in sequences.values()) + 1 + extra
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_whole_requests(models, expected, name, dtype):
+    folder, _, _ = models[name, dtype]
+    sequences = sequences_of(name)
+    core = es.build_core(folder, dtype, num_blocks=_pages_for(sequences))
+    got = es.replay(core, es.schedule_whole(sequences))
+    es.assert_logits_close(got, expected[name, dtype], dtype, f"whole/{name}")
+    assert core.manager.live_requests() == []
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_last_32_tokens_one_by_one(models, expected, name, dtype):
+    folder, _, _ = models[name, dtype]
+    sequences = sequences_of(name)
+    core = es.build_core(folder, dtype, num_blocks=_pages_for(sequences))
+    got = es.replay(core, es.schedule_tail(sequences, 32))
+    es.assert_logits_close(got, expected[name, dtype], dtype, f"tail/{name}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_portions_of_changing_size(models, expected, name, dtype):
+    folder, _, _ = models[name, dtype]
+    sequences = sequences_of(name)
+    core = es.build_core(folder, dtype, num_blocks=_pages_for(sequences))
+    got = es.replay(core, es.schedule_portions(sequences))
+    es.assert_logits_close(got, expected[name, dtype], dtype, f"portions/{name}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_mixed_batches_with_pages_used_again(models, expected, name, dtype):
+    folder, _, config = models[name, dtype]
+    sequences = sequences_of(name)
+    # every request twice (second copy under another id) so that later ones reuse pages
+    doubled = {**sequences, **{rid + "x": tokens for rid, tokens in sequences.items()}}
+    longest = max(len(t) for t in doubled.values())
+    pool_tokens = 2 * (-(-longest // 64) * 64) + 64
+    steps = es.schedule_mixed(doubled, pool_tokens)
+    assert any(len(step["entries"]) > 1 for step in steps)
+    assert any(len(e["tokens"]) > 1 for step in steps for e in step["entries"]
+               if len(step["entries"]) > 1)
+    peak = es.peak_tokens(steps, doubled)
+    assert peak <= pool_tokens
+    core = es.build_core(folder, dtype, num_blocks=peak // es.PAGE + 1)
+    got = es.replay(core, steps)
+    both = {**expected[name, dtype],
+            **{rid + "x": value for rid, value in expected[name, dtype].items()}}
+    es.assert_logits_close(got, both, dtype, f"mixed/{name}")
+    # pages really were handed out more than once
+    total_pages = sum(-(-len(t) // es.PAGE) for t in doubled.values())
+    assert total_pages > core.manager.pools[0].num_usable
+    assert core.manager.num_free_pages() == core.manager.pools[0].num_usable
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_cutting_does_not_change_the_logits_beyond_rounding(models, dtype):
+    """Whole, tail-decoded and chunked runs of the same request agree far more tightly with
+    each other than bfloat16 agrees with the float64 oracle."""
+    folder, _, _ = models["B", dtype]
+    sequences = {"s": sequences_of("B")["b3"]}
+    runs = []
+    for schedule in (es.schedule_whole, es.schedule_tail, es.schedule_portions):
+        core = es.build_core(folder, dtype, num_blocks=_pages_for(sequences))
+        runs.append(es.replay(core, schedule(sequences))["s"])
+    scale = float(runs[0].abs().max())
+    limit = 1e-5 if dtype == "float32" else 1.5e-2
+    for other in runs[1:]:
+        worst = float((other - runs[0]).abs().max()) / scale
+        es.log_error(f"cut-vs-whole/{dtype}", worst)
+        assert worst <= limit
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_long_decoding_to_the_last_position(models, name, dtype):
+    """Four prompt tokens, then one token a step until the context is full."""
+    folder, state, config = models[name, dtype]
+    length = config["n_positions"]
+    sequences = {"long": random_tokens(config["vocab_size"], length, 7)}
+    core = es.build_core(folder, dtype, num_blocks=_pages_for(sequences))
+    got = es.replay(core, es.schedule_tail(sequences, length - 4))
+    es.assert_logits_close(got, es.plain_logits(state, config, sequences), dtype,
+                           f"long-decode/{name}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_first_tokens_of_a_sequence(models, name, dtype):
+    folder, state, config = models[name, dtype]
+    sequences = {f"n{n}": random_tokens(config["vocab_size"], n, 11 + n) for n in (1, 2, 3)}
+    core = es.build_core(folder, dtype, num_blocks=8)
+    got = es.replay(core, es.schedule_tail(sequences, 2))
+    es.assert_logits_close(got, es.plain_logits(state, config, sequences), dtype,
+                           f"first-tokens/{name}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_run_program(models, expected, tmp_path, dtype):
+    """bin/trace_run as a child process, on the mixed schedule with pages used again."""
+    folder, _, config = models["B", dtype]
+    sequences = sequences_of("B")
+    pool_tokens = 2 * 256 + 64
+    steps = es.schedule_mixed(sequences, pool_tokens)
+    peak = es.peak_tokens(steps, sequences)
+    got = es.run_trace_program(folder, dtype, steps, peak, tmp_path / "out",
+                               config["vocab_size"])
+    es.assert_logits_close(got, expected["B", dtype], dtype, "trace_run/B")
+
+
+def test_step_refuses_what_the_cache_cannot_hold(models):
+    from ayaka_b200.engine.runner import StepEntry
+    from ayaka_b200.errors import CapacityError, InvalidRequestError
+
+    folder, _, config = models["A", "float32"]
+    core = es.build_core(folder, "float32", num_blocks=3)  # two usable pages = 32 tokens
+    core.step([StepEntry("a", list(range(20)), [19])])
+    with pytest.raises(CapacityError):
+        core.step([StepEntry("b", list(range(20)), [])])
+    core.manager.check_integrity()
+    assert "b" not in core.manager
+    with pytest.raises(InvalidRequestError):
+        core.step([StepEntry("a", [config["vocab_size"]], [0])])
+    core.release("a")
+    core.step([StepEntry("b", list(range(20)), [])])
+    core.release("b")
+    core.manager.check_integrity()
+    assert core.manager.num_free_pages() == 2

@@ -1,0 +1,337 @@
+"""Each kernel alone against a plain fp32/fp64 torch reference, at sizes other than the
+engine's tiny models: widths that are no power of two, every head size class, tails in
+every dimension, pages handed out in scrambled order and poisoned with NaN."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+import plain_gpt2 as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _ops():
+    from ayaka_b200.kernels import ops
+    return ops
+
+
+def _randn(*shape, seed=0, dtype=torch.float32, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [1, 100, 1600])
+def test_embed_rows(dtype, width):
+    ops = _ops()
+    table, pos = _randn(37, width, seed=1, dtype=dtype), _randn(19, width, seed=2, dtype=dtype)
+    index = torch.tensor([0, 36, 5, 5, 17], dtype=torch.int32, device=DEV)
+    add = torch.tensor([18, 0, 3, 4, 4], dtype=torch.int32, device=DEV)
+    out = torch.full((7, width + 3), float("nan"), device=DEV)[:, :width]
+    bad = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.embed_rows(table, index, out, add_table=pos, add_index=add, bad_index=bad)
+    expected = table.float()[index.long()] + pos.float()[add.long()]
+    torch.testing.assert_close(out[:5], expected, rtol=0, atol=0)
+    assert torch.isnan(out[5:]).all() and int(bad.item()) == 0
+    ops.embed_rows(table, index, out, bad_index=bad)
+    torch.testing.assert_close(out[:5], table.float()[index.long()], rtol=0, atol=0)
+    index[2] = 37
+    ops.embed_rows(table, index, out, bad_index=bad)
+    assert int(bad.item()) == 1
+
+
+@pytest.mark.parametrize("width", [1, 96, 1600, 5000])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_layer_norm(width, out_dtype):
+    ops = _ops()
+    x = _randn(9, width, seed=3, scale=3.0) + 5.0
+    gamma, beta = _randn(width, seed=4) + 1.0, _randn(width, seed=5)
+    out = torch.zeros(9, width, dtype=out_dtype, device=DEV)
+    ops.layer_norm(x, gamma, beta, 1e-6, out)
+    expected = plain.layer_norm(x.double(), gamma.double(), beta.double(), 1e-6)
+    tol = dict(rtol=1e-5, atol=1e-5) if out_dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(out.double(), expected, **tol)
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    picked = torch.zeros(3, width, dtype=out_dtype, device=DEV)
+    ops.layer_norm(x, gamma, beta, 1e-6, picked, rows=rows)
+    torch.testing.assert_close(picked, out[rows.long()], rtol=0, atol=0)
+
+
+# ---------------------------------------------------------------------------------------------
+def _linear_reference(a, w, bias, activation, residual):
+    y = a.double() @ w.double().t()
+    if bias is not None:
+        y = y + bias.double()
+    if activation == "gelu_tanh":
+        y = plain.gelu(y, "gelu_new")
+    elif activation == "gelu_erf":
+        y = plain.gelu(y, "gelu")
+    if residual is not None:
+        y = y + residual.double()
+    return y
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (33, 77, 50), (130, 64, 257)])
+@pytest.mark.parametrize("activation", ["none", "gelu_tanh", "gelu_erf"])
+def test_linear_float32_is_true_fp32(m, n, k, activation):
+    ops = _ops()
+    a = _randn(m, k, seed=6)
+    w = _randn(n, k, seed=7, scale=1 / math.sqrt(k))
+    bias = _randn(n, seed=8)
+    out = torch.zeros(m, n, device=DEV)
+    ops.linear(a, w, bias, out, activation=activation)
+    torch.testing.assert_close(out.double(), _linear_reference(a, w, bias, activation, None),
+                               rtol=1e-5, atol=1e-5)
+    if activation == "none":
+        base = _randn(m, n, seed=9)
+        acc = base.clone()
+        ops.linear(a, w, bias, acc, residual=True)
+        torch.testing.assert_close(acc.double(), _linear_reference(a, w, bias, "none", base),
+                                   rtol=1e-5, atol=1e-5)
+
+
+def test_linear_float32_sees_what_tf32_would_lose():
+    """A product whose exact value needs more than TF32's 10 mantissa bits."""
+    ops = _ops()
+    a = torch.tensor([[1.0 + 2 ** -14, 1.0]], device=DEV)
+    w = torch.tensor([[1.0, -1.0]], device=DEV)
+    out = torch.zeros(1, 1, device=DEV)
+    ops.linear(a, w, None, out)
+    assert out.item() == 2 ** -14
+
+
+GEMM_SHAPES = [(128, 128, 64), (1, 64, 64), (5, 24, 8), (200, 300, 136), (130, 1000, 1600),
+               (300, 200, 6400), (3, 50257, 160), (2048, 640, 512)]
+
+
+@pytest.mark.parametrize("kernel", ["simt", "tcgen05"])
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+def test_linear_bfloat16(kernel, m, n, k):
+    ops = _ops()
+    a = _randn(m, k, seed=10, dtype=torch.bfloat16)
+    w = _randn(n, k, seed=11, dtype=torch.bfloat16, scale=1 / math.sqrt(k))
+    bias = _randn(n, seed=12)
+    exact = _linear_reference(a, w, bias, "none", None)
+    out32 = torch.full((m, n), float("nan"), device=DEV)
+    ops.linear(a, w, bias, out32, kernel=kernel)
+    torch.testing.assert_close(out32.double(), exact, rtol=1e-4, atol=1e-4)
+    out16 = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.linear(a, w, bias, out16, activation="gelu_tanh", kernel=kernel)
+    torch.testing.assert_close(out16.double(), _linear_reference(a, w, bias, "gelu_tanh", None),
+                               rtol=1e-2, atol=1e-2)
+    base = _randn(m, n, seed=13)
+    acc = base.clone()
+    ops.linear(a, w, None, acc, residual=True, kernel=kernel)
+    torch.testing.assert_close(acc.double(), _linear_reference(a, w, None, "none", base),
+                               rtol=1e-4, atol=1e-4)
+    if kernel == "tcgen05":
+        from ayaka_b200.kernels import gemm_tc
+        gemm_tc.check_status(a.device)
+
+
+@pytest.mark.parametrize("tile_n", [64, 128, 256])
+def test_linear_tcgen05_tiles_and_strides(tile_n):
+    """Every tile width, operands that are column ranges of wider buffers, rows limited."""
+    ops = _ops()
+    from ayaka_b200.kernels import gemm_tc
+    m, n, k = 70, 333, 200
+    a_wide = _randn(96, 3 * k, seed=14, dtype=torch.bfloat16)
+    a = a_wide[:, k:2 * k]
+    w = _randn(n, k, seed=15, dtype=torch.bfloat16, scale=1 / math.sqrt(k))
+    out = torch.full((96, n + 5), float("nan"), device=DEV)[:, :n]
+    gemm_tc.linear_bf16(a, w, None, out, m, 0, False, tile_n=tile_n)
+    gemm_tc.check_status(a.device)
+    torch.testing.assert_close(out[:m].double(), a[:m].double() @ w.double().t(),
+                               rtol=1e-4, atol=1e-4)
+    assert torch.isnan(out[m:]).all()
+
+
+def test_linear_bfloat16_unaligned_k_takes_the_cuda_core_kernel():
+    ops = _ops()
+    a = _randn(9, 700, seed=16, dtype=torch.bfloat16)
+    w = _randn(40, 700, seed=17, dtype=torch.bfloat16, scale=0.05)
+    out = torch.zeros(9, 40, device=DEV)
+    ops.linear(a, w, None, out)  # 700 * 2 bytes is no multiple of 16: TMA cannot read it
+    torch.testing.assert_close(out.double(), a.double() @ w.double().t(), rtol=1e-4, atol=1e-4)
+
+
+def test_linear_batch_invariance():
+    """A row's result does not depend on how many rows run with it."""
+    ops = _ops()
+    for dtype, kernel in ((torch.float32, "simt"), (torch.bfloat16, "tcgen05"),
+                          (torch.bfloat16, "simt")):
+        a = _randn(300, 320, seed=18, dtype=dtype)
+        w = _randn(200, 320, seed=19, dtype=dtype, scale=0.05)
+        whole = torch.zeros(300, 200, device=DEV)
+        ops.linear(a, w, None, whole, kernel=kernel)
+        for rows in (1, 7, 129):
+            part = torch.zeros(rows, 200, device=DEV)
+            ops.linear(a[:rows].contiguous(), w, None, part, kernel=kernel)
+            assert torch.equal(part, whole[:rows])
+
+
+# ---------------------------------------------------------------------------------------------
+def _paged_case(lengths, rows_per_request, heads, kv_heads, head_dim, page_size, dtype, seed,
+                boost=None):
+    """Random q/k/v for whole sequences; K/V scattered into NaN-poisoned pages handed out in
+    reverse order; the step holds the last rows_per_request[b] rows of each request."""
+    g = torch.Generator().manual_seed(seed)
+    pages_needed = [-(-n // page_size) for n in lengths]
+    num_pages = sum(pages_needed) + 3
+    k_pages = torch.full((num_pages, kv_heads, page_size, head_dim), float("nan"))
+    v_pages = torch.full_like(k_pages, float("nan"))
+    free = list(range(num_pages - 1, 0, -1))
+    width = max(pages_needed)
+    table = torch.zeros(len(lengths), width, dtype=torch.int32)
+    seqs = []
+    for b, n in enumerate(lengths):
+        q = torch.randn(n, heads, head_dim, generator=g)
+        k = torch.randn(n, kv_heads, head_dim, generator=g)
+        v = torch.randn(n, kv_heads, head_dim, generator=g)
+        if boost is not None:
+            row, key = boost
+            if row < n:
+                k[key] = q[row, ::heads // kv_heads] * 3.0  # one score stands out for every head
+        q, k, v = (t.to(dtype).float() for t in (q, k, v))
+        seqs.append((q, k, v))
+        for i in range(pages_needed[b]):
+            table[b, i] = free.pop(0)
+        for t in range(n):
+            page, slot = int(table[b, t // page_size]), t % page_size
+            k_pages[page, :, slot] = k[t]
+            v_pages[page, :, slot] = v[t]
+    q_rows, req, pos = [], [], []
+    for b, (n, r) in enumerate(zip(lengths, rows_per_request)):
+        q_rows.append(seqs[b][0][n - r:].reshape(r, heads * head_dim))
+        req += [b] * r
+        pos += list(range(n - r, n))
+    return (torch.cat(q_rows).to(dtype).to(DEV), k_pages.to(dtype).to(DEV),
+            v_pages.to(dtype).to(DEV), table.to(DEV),
+            torch.tensor(req, dtype=torch.int32, device=DEV),
+            torch.tensor(pos, dtype=torch.int32, device=DEV), seqs)
+
+
+def _attention_reference(seqs, lengths, rows_per_request, heads, kv_heads, scale, window):
+    outs = []
+    for (q, k, v), n, r in zip(seqs, lengths, rows_per_request):
+        rep = heads // kv_heads
+        full = plain.causal_attention(q.double(), k.double().repeat_interleave(rep, 1),
+                                      v.double().repeat_interleave(rep, 1), scale, window)
+        outs.append(full[n - r:].reshape(r, -1))
+    return torch.cat(outs)
+
+
+ATTN_CASES = [
+    # lengths, rows, heads, kv_heads, head_dim, page, window
+    ((5, 17, 32, 9), (5, 17, 32, 9), 4, 4, 16, 16, 0),
+    ((1, 64, 130), (1, 1, 1), 3, 3, 32, 16, 0),
+    ((40, 33, 70), (2, 33, 1), 6, 2, 48, 8, 0),
+    ((300,), (300,), 2, 1, 128, 16, 0),
+    ((90, 200), (17, 5), 2, 2, 256, 32, 0),
+    ((100, 257), (30, 1), 5, 5, 64, 16, 24),
+    ((67,), (67,), 3, 1, 80, 4, 5),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", ATTN_CASES)
+def test_attention_paged(dtype, case):
+    ops = _ops()
+    lengths, rows, heads, kv_heads, head_dim, page, window = case
+    q, k_pages, v_pages, table, req, pos, seqs = _paged_case(
+        lengths, rows, heads, kv_heads, head_dim, page, dtype, seed=20)
+    out = torch.full((q.shape[0] + 2, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
+    scale = 0.7 / math.sqrt(head_dim)
+    ops.attention(q, k_pages, v_pages, table, req, pos, out, num_heads=heads, scale=scale,
+                  window=window, rows=q.shape[0])
+    expected = _attention_reference(seqs, lengths, rows, heads, kv_heads, scale, window)
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out[:q.shape[0]].double().cpu(), expected, **tol)
+    assert torch.isnan(out[q.shape[0]:].float()).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_a_far_key_among_hundreds(dtype):
+    """Row 699 of a 700-token request must find key 3 (first page); row 350 key 349."""
+    ops = _ops()
+    lengths, rows, heads, kv_heads, head_dim, page = (700,), (700,), 2, 2, 64, 16
+    for boost in ((699, 3), (350, 349), (16, 15), (16, 0)):
+        q, k_pages, v_pages, table, req, pos, seqs = _paged_case(
+            lengths, rows, heads, kv_heads, head_dim, page, dtype, seed=21, boost=boost)
+        out = torch.zeros(700, heads * head_dim, dtype=dtype, device=DEV)
+        ops.attention(q, k_pages, v_pages, table, req, pos, out, num_heads=heads, scale=1.0)
+        row, key = boost
+        got = out[row].float().cpu().reshape(heads, head_dim)
+        # the boosted key takes almost all the weight, so the output is that key's value
+        torch.testing.assert_close(got, seqs[0][2][key], rtol=2e-2, atol=2e-2)
+        expected = _attention_reference(seqs, lengths, rows, heads, kv_heads, 1.0, 0)
+        tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=2e-2,
+                                                                               atol=2e-2)
+        torch.testing.assert_close(out.double().cpu(), expected, **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_kv_store_then_attend(dtype):
+    """The store writes exactly the slots it is given; a padding row stores nothing and a
+    padding request's rows come out zero."""
+    ops = _ops()
+    heads, head_dim, page = 3, 32, 4
+    k_pages = torch.full((6, heads, page, head_dim), float("nan"), dtype=dtype, device=DEV)
+    v_pages = torch.full_like(k_pages, float("nan"))
+    qkv = _randn(5, 3 * heads * head_dim, seed=22, dtype=dtype)
+    width = heads * head_dim
+    slots = torch.tensor([5 * page + 0, 5 * page + 1, 5 * page + 2, 2 * page + 3, -1],
+                         dtype=torch.int32, device=DEV)
+    ops.kv_store(qkv[:, width:2 * width], qkv[:, 2 * width:], slots, k_pages, v_pages)
+    assert torch.equal(k_pages[5, :, 1], qkv[1, width:2 * width].reshape(heads, head_dim))
+    assert torch.equal(v_pages[2, :, 3], qkv[3, 2 * width:].reshape(heads, head_dim))
+    written = ~torch.isnan(k_pages.float())
+    assert int(written.sum()) == 4 * heads * head_dim
+    table = torch.tensor([[5, 0]], dtype=torch.int32, device=DEV)
+    req = torch.tensor([0, 0, 0, -1], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([0, 1, 2, 0], dtype=torch.int32, device=DEV)
+    out = torch.full((4, width), float("nan"), dtype=dtype, device=DEV)
+    ops.attention(qkv[:4, :width], k_pages, v_pages, table, req, pos, out, num_heads=heads,
+                  scale=0.2)
+    q = qkv[:3, :width].float().cpu().reshape(3, heads, head_dim)
+    k = qkv[:3, width:2 * width].float().cpu().reshape(3, heads, head_dim)
+    v = qkv[:3, 2 * width:].float().cpu().reshape(3, heads, head_dim)
+    expected = plain.causal_attention(q, k, v, 0.2).reshape(3, width)
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out[:3].float().cpu(), expected, **tol)
+    assert torch.equal(out[3].float(), torch.zeros(width, device=DEV))
+
+
+def test_attention_refuses_what_it_cannot_do():
+    ops = _ops()
+    from ayaka_b200.errors import BackendError
+    q = torch.zeros(1, 24, device=DEV)
+    pages = torch.zeros(2, 1, 4, 24, device=DEV)
+    table = torch.ones(1, 1, dtype=torch.int32, device=DEV)
+    zero = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(BackendError):
+        ops.attention(q, pages[..., :20].contiguous(), pages[..., :20].contiguous(), table, zero,
+                      zero, q[:, :20].contiguous(), num_heads=1, scale=1.0)  # head_dim 20
+
+
+# ---------------------------------------------------------------------------------------------
+def test_argmax_smallest_id_on_ties():
+    ops = _ops()
+    logits = _randn(6, 50257, seed=23)
+    logits[0, 77] = logits[0, 40000] = 9.0
+    logits[1, 50256] = 11.0
+    logits[2, 0] = 12.0
+    logits[3] = 1.5
+    logits[4, 5] = float("nan")
+    out = torch.full((6,), -1, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, out)
+    expected = [plain.argmax_smallest_id(torch.nan_to_num(row, nan=-1e30)) for row in logits.cpu()]
+    assert out.tolist() == expected
+    assert out.tolist()[:4] == [77, 50256, 0, 0]
