@@ -1,0 +1,204 @@
+"""Decode steps replayed from CUDA graphs.
+
+A decode-only step (one token per request) launches a few hundred small kernels; launched
+one by one from the host they cost more than they compute. For every bucket of batch sizes
+(1, 2, 4, 8, ...) the whole step — model forward, final norm, head and token choice — is
+captured once into a graph over fixed device buffers. A step then is: fill one pinned
+buffer with the step's metadata and sampling parameters, one host-to-device copy, one graph
+launch, one device-to-host read of the chosen ids. A step smaller than its bucket is padded
+with rows that belong to no request: they store nothing, attend to nothing and their ids
+are dropped. The reference does the same for its torch ops (``python/ayaka/execution/
+graph.py:89-287``); here one graph per bucket serves greedy and sampling rows alike because
+the sampling kernel handles both.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ayaka_b200.engine.core import EngineCore
+from ayaka_b200.kernels import ops
+from ayaka_b200.parts.context import GroupStep, StepContext
+from ayaka_b200.sampling.sampler import SampleRow
+
+__all__ = ["DecodeGraphs"]
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class _Bucket:
+    """Fixed buffers, the step context over them and the captured graph of one batch size."""
+
+    def __init__(self, core: EngineCore, size: int) -> None:
+        manager = core.manager
+        self.size = size
+        self.width = manager.max_pages_per_request
+        groups = len(manager.needs)
+        cursor = 0
+
+        def take(length: int) -> int:
+            nonlocal cursor
+            offset = cursor
+            cursor += _align4(length)
+            return offset
+
+        self.o_tokens, self.o_positions, self.o_request = take(size), take(size), take(size)
+        self.o_row_start, self.o_kv_len, self.o_state = take(size + 1), take(size), take(size)
+        self.o_want = take(size)
+        self.o_groups = [(take(size), take(size * self.width)) for _ in range(groups)]
+        self.o_temperature, self.o_top_p, self.o_min_p = take(size), take(size), take(size)
+        self.o_top_k = take(size)
+        self.o_seeds, self.o_sample_positions = take(2 * size), take(2 * size)
+        self.words = cursor
+        self.staging = torch.zeros(cursor, dtype=torch.int32).pin_memory()
+        self.meta = torch.zeros(cursor, dtype=torch.int32, device=core.device)
+        self.out = torch.zeros(size, dtype=torch.int32, device=core.device)
+        self.out_host = torch.zeros(size, dtype=torch.int32).pin_memory()
+        meta = self.meta
+
+        def view(offset: int, length: int) -> torch.Tensor:
+            return meta[offset:offset + length]
+
+        self.step = StepContext(
+            num_rows=size, num_requests=size,
+            tokens=view(self.o_tokens, size), positions=view(self.o_positions, size),
+            request_of_row=view(self.o_request, size),
+            row_start=view(self.o_row_start, size + 1), kv_len=view(self.o_kv_len, size),
+            state_slot=view(self.o_state, size),
+            host_rows=[1] * size, host_start=[0] * size, host_state_slot=[0] * size,
+            groups=[GroupStep(view(o_table, size * self.width).view(size, self.width),
+                              view(o_slots, size), manager.page_size)
+                    for o_slots, o_table in self.o_groups],
+            workspace=core.runner.workspace, bad_index=core.runner._bad_index,
+            max_kv_len=core.model.spec.max_positions, decode_only=True)
+        self.want_rows = view(self.o_want, size)
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.kernels = 0
+
+    def launch_body(self, core: EngineCore) -> None:
+        size, meta = self.size, self.meta
+        logits = core.model.forward(self.step, core.runner.caches, self.want_rows, size)
+        ops.sample(logits, meta[self.o_temperature:self.o_temperature + size].view(torch.float32),
+                   meta[self.o_top_k:self.o_top_k + size],
+                   meta[self.o_top_p:self.o_top_p + size].view(torch.float32),
+                   meta[self.o_min_p:self.o_min_p + size].view(torch.float32),
+                   meta[self.o_seeds:self.o_seeds + 2 * size].view(torch.int64),
+                   meta[self.o_sample_positions:self.o_sample_positions + 2 * size].view(
+                       torch.int64),
+                   self.out, rows=size)
+
+
+class DecodeGraphs:
+    """Captures and replays decode steps; falls back to nothing — a step it cannot run is
+    run by the ordinary step function."""
+
+    def __init__(self, core: EngineCore, buckets: tuple[int, ...] | None = None) -> None:
+        self.core = core
+        limit = core.manager.max_requests
+        if buckets is None:
+            sizes, size = [], 1
+            while size < limit:
+                sizes.append(size)
+                size *= 2
+            sizes.append(limit)
+            buckets = tuple(sizes)
+        self.sizes = tuple(sorted(set(min(size, limit) for size in buckets)))
+        self._buckets: dict[int, _Bucket] = {}
+        self.replays = 0
+
+    def can_run(self, plan: object) -> bool:
+        entries = plan.entries  # type: ignore[attr-defined]
+        if any(state is not None for state in self.core.cache_plan.run_state):
+            return False  # capture runs the step's kernels more than once: pages take that,
+            # a running per-request state does not
+        return (plan.num_prefill_tokens == 0 and 0 < len(entries) <= self.sizes[-1]  # type: ignore
+                and len(plan.sampled) == len(entries))  # type: ignore[attr-defined]
+
+    def bucket_for(self, count: int) -> _Bucket:
+        size = next(size for size in self.sizes if size >= count)
+        bucket = self._buckets.get(size)
+        if bucket is None:
+            bucket = _Bucket(self.core, size)
+            self._buckets[size] = bucket
+        return bucket
+
+    def run(self, plan: object, rows: list[SampleRow]) -> list[int]:
+        """Run a decode-only plan through its bucket's graph; returns one id per entry."""
+        entries = plan.entries  # type: ignore[attr-defined]
+        count = len(entries)
+        bucket = self.bucket_for(count)
+        self._fill(bucket, entries, rows)
+        bucket.meta.copy_(bucket.staging, non_blocking=True)
+        if bucket.graph is None:
+            self._capture(bucket)
+        bucket.graph.replay()  # type: ignore[union-attr]
+        bucket.out_host.copy_(bucket.out, non_blocking=True)
+        torch.cuda.current_stream(self.core.device).synchronize()
+        self.replays += 1
+        return bucket.out_host[:count].tolist()
+
+    def _capture(self, bucket: _Bucket) -> None:
+        core = self.core
+        with torch.cuda.device(core.device):
+            # twice without capture: allocates the workspace, builds and configures kernels
+            side = torch.cuda.Stream(core.device)
+            side.wait_stream(torch.cuda.current_stream(core.device))
+            with torch.cuda.stream(side):
+                bucket.launch_body(core)
+                bucket.launch_body(core)
+            torch.cuda.current_stream(core.device).wait_stream(side)
+            torch.cuda.synchronize(core.device)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
+            with torch.cuda.graph(graph):
+                bucket.launch_body(core)
+            bucket.kernels = ops.launch_count() - before
+            bucket.graph = graph
+
+    def _fill(self, bucket: _Bucket, entries: object, rows: list[SampleRow]) -> None:
+        manager = self.core.manager
+        size, width, page = bucket.size, bucket.width, manager.page_size
+        host = bucket.staging.numpy()
+        floats = host.view(np.float32)
+        count = len(entries)  # type: ignore[arg-type]
+        host[bucket.o_request:bucket.o_request + size] = -1
+        host[bucket.o_tokens:bucket.o_tokens + size] = 0
+        host[bucket.o_positions:bucket.o_positions + size] = 0
+        host[bucket.o_kv_len:bucket.o_kv_len + size] = 0
+        host[bucket.o_want:bucket.o_want + size] = np.arange(size)
+        host[bucket.o_row_start:bucket.o_row_start + size + 1] = np.arange(size + 1)
+        floats[bucket.o_temperature:bucket.o_temperature + size] = 0.0
+        table_rows = []
+        for b, entry in enumerate(entries):  # type: ignore[arg-type]
+            position = manager.committed(entry.request_id)
+            row = manager.row(entry.request_id)
+            table_rows.append(row)
+            host[bucket.o_tokens + b] = entry.tokens[0]
+            host[bucket.o_positions + b] = position
+            host[bucket.o_request + b] = b
+            host[bucket.o_kv_len + b] = position + 1
+            host[bucket.o_state + b] = row
+        for group, (o_slots, o_table) in enumerate(bucket.o_groups):
+            table = manager.tables[group]
+            host[o_slots:o_slots + size] = -1
+            block = host[o_table:o_table + size * width].reshape(size, width)
+            for b in range(count):
+                block[b] = table[table_rows[b]]
+                position = int(host[bucket.o_positions + b])
+                host[o_slots + b] = int(block[b, position // page]) * page + position % page
+        longs_seed = host[bucket.o_seeds:bucket.o_seeds + 2 * size].view(np.int64)
+        longs_pos = host[bucket.o_sample_positions:
+                         bucket.o_sample_positions + 2 * size].view(np.int64)
+        longs_seed[:] = 0
+        longs_pos[:] = 0
+        for b, row in enumerate(rows):
+            params = row.params
+            floats[bucket.o_temperature + b] = 0.0 if params.greedy else params.temperature
+            floats[bucket.o_top_p + b] = params.top_p
+            floats[bucket.o_min_p + b] = params.min_p
+            host[bucket.o_top_k + b] = max(params.top_k, 0)
+            longs_seed[b] = row.seed
+            longs_pos[b] = row.position

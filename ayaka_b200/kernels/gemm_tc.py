@@ -50,6 +50,9 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
                            "multiples of 8 elements)")
     n, k = weight.shape
     mode = 2 if residual else (0 if out.dtype == torch.bfloat16 else 1)
+    from ayaka_b200.kernels import ops
+
+    ops._launches += 1
     fn = library("gemm_tc").ayk_gemm_bf16_tc
     status = fn(c_void_p(a.data_ptr()), c_int(a.stride(0)), c_void_p(weight.data_ptr()),
                 c_int(weight.stride(0)), c_void_p(0 if bias is None else bias.data_ptr()),

@@ -8,7 +8,6 @@ library or a refused argument raises :class:`~ayaka_b200.errors.BackendError`.
 
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_void_p
 
 import torch
@@ -22,8 +21,10 @@ __all__ = [
     "attention",
     "embed_rows",
     "kv_store",
+    "launch_count",
     "layer_norm",
     "linear",
+    "sample",
 ]
 
 ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2}
@@ -34,7 +35,18 @@ _TYPE = {torch.float32: 0, torch.bfloat16: 1}
 BF16_GEMM = "tcgen05"
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels launched through this module since the process started (a graph capture
+    counts the kernels it records)."""
+    return _launches
+
+
 def _stream() -> c_void_p:
+    global _launches
+    _launches += 1
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -248,4 +260,34 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, *, rows: int | None = None) 
     check(status, op)
 
 
-_ = ctypes  # keep the import for type names used by callers
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor | None,
+           top_p: torch.Tensor | None, min_p: torch.Tensor | None, seeds: torch.Tensor,
+           positions: torch.Tensor, out: torch.Tensor, *, rows: int | None = None) -> None:
+    """One token per row of fp32 logits: temperature, top-k, top-p, min-p and the inverse CDF
+    over the canonical order, the random number from Philox(seed, position) in the kernel.
+
+    ``temperature`` float32 (a row below 1e-5 is greedy); ``top_k`` int32 (<= 0 off);
+    ``top_p``/``min_p`` float32; ``seeds``/``positions`` int64 (position = index in the
+    sequence of the token being produced); ``out`` int32.
+    """
+    op = "sample"
+    _need(op, "logits", logits, torch.float32, 2)
+    _need(op, "temperature", temperature, torch.float32, 1)
+    _need(op, "seeds", seeds, torch.int64, 1)
+    _need(op, "positions", positions, torch.int64, 1)
+    _need(op, "out", out, torch.int32, 1)
+    n = logits.shape[0] if rows is None else rows
+    for name, tensor, dtype in (("top_k", top_k, torch.int32), ("top_p", top_p, torch.float32),
+                                ("min_p", min_p, torch.float32)):
+        if tensor is not None:
+            _need(op, name, tensor, dtype, 1)
+            if tensor.shape[0] < n:
+                raise BackendError(f"{op}: {name} has fewer than {n} rows")
+    if min(temperature.shape[0], seeds.shape[0], positions.shape[0], out.shape[0],
+           logits.shape[0]) < n:
+        raise BackendError(f"{op}: {n} rows do not fit the tensors")
+    status = library("sampling").ayk_sample(
+        _ptr(logits), c_int(logits.stride(0)), c_int(n), c_int(logits.shape[1]),
+        _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(seeds), _ptr(positions),
+        _ptr(out), _stream())
+    check(status, op)

@@ -24,6 +24,8 @@ class Workspace:
         self.max_rows = max_rows
         self.device = device
         self._buffers: dict[tuple[str, int, torch.dtype], torch.Tensor] = {}
+        # a buffer that had to grow is kept: a captured graph may still hold its address
+        self._retired: list[torch.Tensor] = []
 
     def buffer(self, name: str, width: int, dtype: torch.dtype,
                rows: int | None = None) -> torch.Tensor:
@@ -32,6 +34,8 @@ class Workspace:
         found = self._buffers.get(key)
         want = self.max_rows if rows is None else rows
         if found is None or found.shape[0] < want:
+            if found is not None:
+                self._retired.append(found)
             found = torch.zeros((want, width), dtype=dtype, device=self.device)
             self._buffers[key] = found
         return found

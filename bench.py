@@ -1,0 +1,334 @@
+#!/usr/bin/env python3
+"""The benchmark the build driver runs: GPT-2 XL decode and prefill throughput on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on standard output. ``value`` is decoded tokens per second at batch 8 with
+random bf16 weights of GPT-2 XL's sizes (``configs[2]`` of BASELINE.json): eight 512-token
+prompts are prefilled, then W untimed and K timed decode steps run (context grows from
+512 + W towards 1024), timed on the device with CUDA events around the K steps. A decode step
+is the engine's own step: CUDA-graph replay of the whole forward plus token choice, fed from
+pinned host memory, with the chosen ids read back. ``e2e`` is the same measured through the
+Python entry point ``LLM.generate`` with host token ids in and out, as (time of T tokens -
+time of 1 token) / (T - 1), the reference's method (``benchmarks/e2e/decode.py:1-10``).
+``prefill`` is one 2,048-token step (two prompts of 1,024). ``roofline`` divides the bytes a
+decode step must read (every weight once plus the live requests' keys and values) by its
+time and by the measured copy bandwidth. ``points`` holds decode at batch 1 and 64.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+XL = {
+    "architectures": ["GPT2LMHeadModel"], "n_layer": 48, "n_embd": 1600, "n_head": 25,
+    "n_inner": 6400, "vocab_size": 50257, "n_positions": 1024, "layer_norm_epsilon": 1e-5,
+    "activation_function": "gelu_new", "scale_attn_by_inverse_layer_idx": False,
+    "tie_word_embeddings": True,
+}
+PROMPT = 512
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            data = json.loads(path.read_text())
+            if "hbm_gbs" in data and "bf16_tflops" in data:
+                return data, "measured"
+        except (json.JSONDecodeError, OSError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class Clocks:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.process = None
+
+    def start(self) -> None:
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.process = None
+
+    def stop(self) -> dict:
+        if self.process is not None:
+            self.process.terminate()
+            try:
+                self.process.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.process.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, peak, reasons = [], 0, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.file.read().splitlines():
+            fields = [field.strip() for field in line.split(",")]
+            if len(fields) < 7:
+                continue
+            try:
+                sm.append(int(float(fields[0])))
+                peak = max(peak, int(float(fields[1])))
+            except ValueError:
+                continue
+            for name, field in zip(names, fields[3:7]):
+                if field.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": peak or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def layer_weight_bytes(cfg: dict, layers: int) -> int:
+    d, f, v = cfg["n_embd"], cfg["n_inner"], cfg["vocab_size"]
+    per_layer = (3 * d * d + d * d + 2 * d * f) * 2 + (3 * d + d + f + d + 4 * d) * 4
+    return layers * per_layer + v * d * 2 + 2 * d * 4  # + tied head (wte) and ln_f
+
+
+def kv_bytes_per_token(cfg: dict, layers: int) -> int:
+    return layers * 2 * cfg["n_embd"] * 2
+
+
+def prefill_flops(cfg: dict, layers: int, prompts: int, length: int) -> float:
+    d, f, v = cfg["n_embd"], cfg["n_inner"], cfg["vocab_size"]
+    tokens = prompts * length
+    gemm = 2.0 * tokens * (3 * d * d + d * d + 2 * d * f) * layers
+    attention = layers * prompts * 4.0 * d * (length * (length + 1) / 2)
+    return gemm + attention + 2.0 * prompts * d * v
+
+
+def build(cfg: dict, batch: int, tokens_per_step: int, seed: int = 0):
+    import torch
+
+    from ayaka_b200 import LLM, EngineConfig
+    from ayaka_b200.weights.random_init import random_state
+
+    state = random_state(cfg, seed, None, "bfloat16")
+    with tempfile.TemporaryDirectory() as folder:
+        (Path(folder) / "config.json").write_text(json.dumps(cfg))
+        config = EngineConfig(
+            model=folder, dtype="bfloat16", device="cuda:0", block_size=16,
+            kv_reserve_tokens=batch * cfg["n_positions"], max_running=batch,
+            max_tokens_per_step=tokens_per_step, cuda_graph=True)
+        llm = LLM.from_config(config, tensors=state)
+    del state
+    torch.cuda.synchronize()
+    return llm
+
+
+def random_prompts(cfg: dict, count: int, length: int, seed: int) -> list[tuple[int, ...]]:
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    return [tuple(torch.randint(0, cfg["vocab_size"], (length,), generator=g).tolist())
+            for _ in range(count)]
+
+
+def decode_run(llm, cfg: dict, batch: int, warmup: int, steps: int, seed: int) -> dict:
+    """Prefill ``batch`` prompts, then time ``steps`` decode steps after ``warmup`` untimed
+    ones; returns device milliseconds per step and the contexts seen."""
+    import torch
+
+    from ayaka_b200 import SamplingParams
+    from ayaka_b200.kernels import ops
+
+    scheduler = llm.scheduler
+    params = SamplingParams(temperature=0.0, max_tokens=None, ignore_eos=True)
+    for index, prompt in enumerate(random_prompts(cfg, batch, PROMPT, seed)):
+        scheduler.add_request(f"bench-{seed}-{index}", prompt, params)
+    while any(request.prefilling for request in scheduler.running.values()) or scheduler.waiting:
+        llm._advance()
+    for _ in range(warmup):
+        llm._advance()
+    torch.cuda.synchronize()
+    first_context = PROMPT + 1 + warmup
+    launches_before = ops.launch_count()
+    replays_before = llm.graphs.replays if llm.graphs else 0
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall = time.perf_counter()
+    start.record()
+    for _ in range(steps):
+        llm._advance()
+    stop.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - wall
+    ms = start.elapsed_time(stop) / steps
+    replays = (llm.graphs.replays if llm.graphs else 0) - replays_before
+    per_graph = 0
+    if llm.graphs:
+        bucket = llm.graphs.bucket_for(batch)
+        per_graph = bucket.kernels
+    launches = (ops.launch_count() - launches_before) + replays * per_graph
+    for request_id in list(scheduler.running):
+        scheduler.abort(request_id)
+    scheduler.take_events()
+    llm.core.manager.check_integrity()
+    mean_context = first_context + (steps - 1) / 2
+    return {"ms": ms, "wall_ms": wall * 1000 / steps, "mean_context": mean_context,
+            "launches": launches, "replays": replays}
+
+
+def prefill_run(llm, cfg: dict, warmup: int, repeats: int) -> dict:
+    import torch
+
+    from ayaka_b200.engine.runner import StepEntry
+
+    length = cfg["n_positions"]
+    times = []
+    for index in range(warmup + repeats):
+        prompts = random_prompts(cfg, 2, length, 900 + index)
+        entries = [StepEntry(f"prefill-{index}-{i}", prompt, (length - 1,))
+                   for i, prompt in enumerate(prompts)]
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        llm.step(entries)
+        stop.record()
+        torch.cuda.synchronize()
+        if index >= warmup:
+            times.append(start.elapsed_time(stop))
+        for entry in entries:
+            llm.release(entry.request_id)
+    times.sort()
+    return {"ms": times[len(times) // 2], "tokens": 2 * length}
+
+
+def e2e_run(llm, cfg: dict, batch: int, tokens: int) -> dict:
+    """Decode tokens per second through ``LLM.generate``: host ids in, host ids out."""
+    from ayaka_b200 import SamplingParams
+
+    prompts = random_prompts(cfg, batch, PROMPT, 4242)
+
+    def timed(max_tokens: int) -> float:
+        begin = time.perf_counter()
+        outputs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=max_tokens,
+                                                       ignore_eos=True))
+        elapsed = time.perf_counter() - begin
+        assert all(len(o.outputs[0].token_ids) == max_tokens for o in outputs)
+        return elapsed
+
+    timed(4)  # warm
+    one = min(timed(1) for _ in range(2))
+    many = min(timed(tokens) for _ in range(2))
+    per_step = (many - one) / (tokens - 1)
+    bucket = llm.graphs.bucket_for(batch) if llm.graphs else None
+    return {"value": batch / per_step, "unit": "tok/s",
+            "h2d_bytes_per_step": bucket.words * 4 if bucket else 0,
+            "d2h_bytes_per_step": (bucket.size if bucket else batch) * 4,
+            "ms_per_step": per_step * 1000}
+
+
+def reference_arm() -> int:
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "gityuko-hb/ayaka cannot be installed offline here: its build backend "
+                       "(hatchling) is neither installed nor in the wheelhouse, and it requires "
+                       "Python >= 3.13 (this image has 3.12)"}))
+    return 0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=400)
+    parser.add_argument("--warmup", type=int, default=16)
+    parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    parser.add_argument("--layers", type=int, default=48,
+                        help="layers to build (GPT-2 XL has 48); sizes of a layer never change")
+    parser.add_argument("--skip-points", action="store_true",
+                        help="leave out the batch 1 / batch 64 points and the e2e run")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    import torch
+
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device")
+        return 1
+    warmup = max(args.warmup, 3)
+    steps = max(1, min(args.steps, XL["n_positions"] - PROMPT - 2 - warmup))
+    cfg = {**XL, "n_layer": args.layers}
+    peak, peak_source = peaks()
+
+    llm = build(cfg, 64, 2048)
+    clocks = Clocks()
+    clocks.start()
+    main_run = decode_run(llm, cfg, 8, warmup, steps, seed=1)
+    clock_record = clocks.stop()
+    prefill = prefill_run(llm, cfg, 2, 5)
+    points, e2e = {}, None
+    if not args.skip_points:
+        for batch in (1, 64):
+            run = decode_run(llm, cfg, batch, warmup, steps, seed=10 + batch)
+            points[f"decode_b{batch}"] = round(batch * 1000.0 / run["ms"], 1)
+            points[f"decode_b{batch}_ms"] = round(run["ms"], 4)
+        e2e = e2e_run(llm, cfg, 8, 128)
+
+    layers = cfg["n_layer"]
+    step_bytes = layer_weight_bytes(cfg, layers) + \
+        8 * main_run["mean_context"] * kv_bytes_per_token(cfg, layers)
+    achieved = step_bytes / (main_run["ms"] * 1e-3) / 1e9
+    flops = prefill_flops(cfg, layers, 2, cfg["n_positions"])
+    value = 8 * 1000.0 / main_run["ms"]
+    line = {
+        "metric": "decode tok/s at batch 8 (GPT-2 XL, bf16, context 1024)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(main_run["ms"], 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {
+            "model": "gpt2-xl", "n_layer": layers, "n_layer_full": 48, "n_embd": 1600,
+            "n_head": 25, "n_inner": 6400, "vocab_size": 50257, "n_positions": 1024,
+            "global_batch": 8, "seq_len": 1024, "prompt_len": PROMPT,
+            "mean_context": round(main_run["mean_context"], 1), "page_size": 16,
+            "parallelism": "single-gpu", "weights": "random bf16 seed 0",
+            "l2": "inputs larger than L2 (3.1 GB of weights per step)", "cuda_graph": True,
+        },
+        "prefill": {"value": round(prefill["tokens"] * 1000.0 / prefill["ms"], 1),
+                    "tokens": prefill["tokens"], "ms": round(prefill["ms"], 3),
+                    "frac": round(flops / (prefill["ms"] * 1e-3) / (peak["bf16_tflops"] * 1e12),
+                                  4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1),
+                     "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4), "peaks": peak_source},
+        "points": points,
+        "clocks": clock_record,
+        "gpu_launches": int(main_run["launches"]),
+        "host_ms_per_step": round(main_run["wall_ms"], 4),
+    }
+    if e2e is not None:
+        line["e2e"] = {key: (round(val, 2) if isinstance(val, float) else val)
+                       for key, val in e2e.items()}
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,253 @@
+"""Generation through the Python entry point and the command line, the sampling kernel, and
+the scheduler on a real cache that is too small for the crowd."""
+
+from __future__ import annotations
+
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import engine_support as es
+import plain_gpt2 as plain
+from cases import INIT_A, INIT_B, INIT_LOUD, TINY_A, TINY_B, random_tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _llm(folder, dtype, **overrides):
+    from ayaka_b200 import LLM, EngineConfig
+
+    options = dict(model=str(folder), dtype=dtype, max_running=4, num_blocks=64,
+                   max_tokens_per_step=256)
+    options.update(overrides)
+    return LLM.from_config(EngineConfig(**options))
+
+
+def canonical_interval(row: torch.Tensor, temperature: float, token: int) -> tuple[float, float]:
+    """[lo, hi) of ``token`` on the CDF over the canonical order (p descending, id ascending)."""
+    p = torch.softmax(row.double() / temperature, 0)
+    order = sorted(range(len(p)), key=lambda i: (-float(p[i]), i))
+    cumulative = 0.0
+    for index in order:
+        if index == token:
+            return cumulative, cumulative + float(p[index])
+        cumulative += float(p[index])
+    raise AssertionError("token not in the vocabulary")
+
+
+def check_generation(state, config, prompt, got, params, seed, slack):
+    """Every generated token is what the plain implementation allows at its position: the
+    argmax within ``slack`` of the logit scale (greedy), or the token whose CDF interval
+    holds this position's random number within ``slack`` (sampling)."""
+    sequence = list(prompt) + list(got)
+    logits = plain.logits(plain.cast_state(state, torch.float64), config, torch.tensor(sequence))
+    for index, token in enumerate(got):
+        position = len(prompt) + index
+        row = logits[position - 1]
+        if params.greedy:
+            scale = float(row.abs().max())
+            assert float(row[token]) >= float(row.max()) - slack * scale, (index, token)
+        else:
+            u = plain.draw_uniform(seed, position)
+            lo, hi = canonical_interval(row, params.temperature, token)
+            assert lo - slack <= u < hi + slack, (index, token, u, lo, hi)
+
+
+@pytest.mark.parametrize("dtype,slack", [("float32", 1e-4), ("bfloat16", 3e-2)])
+def test_greedy_generation_config_a(tmp_path, dtype, slack):
+    """Tiny A as the benchmark file states it: four prompts of 5, 17, 32 and 9 tokens, 16
+    greedy tokens each, weights N(0, 0.02)."""
+    from ayaka_b200 import SamplingParams
+
+    folder, state = es.make_model(tmp_path / "a", TINY_A, 0, INIT_A, dtype)
+    prompts = [random_tokens(256, n, 300 + n) for n in (5, 17, 32, 9)]
+    params = SamplingParams(temperature=0.0, max_tokens=16)
+    with _llm(folder, dtype) as llm:
+        outputs = llm.generate([tuple(p) for p in prompts], params)
+        llm.core.manager.check_integrity()
+        assert llm.core.manager.live_requests() == []
+    for prompt, output in zip(prompts, outputs):
+        got = output.outputs[0].token_ids
+        assert len(got) == 16 and output.finished
+        assert output.outputs[0].finish_reason.value == "length"
+        assert output.usage.prompt_tokens == len(prompt) and output.usage.completion_tokens == 16
+        check_generation(state, TINY_A, prompt, got, params, output.seed, slack)
+    if dtype == "float32":  # with loud weights the margins are wide: tokens must be equal
+        folder, state = es.make_model(tmp_path / "loud", TINY_A, 0, INIT_LOUD, dtype)
+        with _llm(folder, dtype) as llm:
+            outputs = llm.generate([tuple(p) for p in prompts], params)
+        for prompt, output in zip(prompts, outputs):
+            assert list(output.outputs[0].token_ids) == plain.greedy_generate(
+                state, TINY_A, prompt, 16)
+
+
+@pytest.mark.parametrize("dtype,slack", [("float32", 1e-4), ("bfloat16", 5e-2)])
+def test_temperature_sampling_config_b(tmp_path, dtype, slack):
+    """Tiny B as the benchmark file states it: prompts of 1, 64 and 130 tokens cut into
+    portions of 48 beside decode steps, temperature 0.8, 24 tokens each, pages of 16."""
+    from ayaka_b200 import SamplingParams
+
+    folder, state = es.make_model(tmp_path / "b", TINY_B, 1, INIT_B, dtype)
+    prompts = [random_tokens(503, n, 400 + n) for n in (1, 64, 130)]
+    params = [SamplingParams(temperature=0.8, max_tokens=24, seed=1000 + i) for i in range(3)]
+    with _llm(folder, dtype, max_tokens_per_step=48, block_size=16) as llm:
+        outputs = llm.generate([tuple(p) for p in prompts], params)
+        stats = llm.scheduler.stats
+        assert stats.prefill_tokens == 195 and stats.decode_rows == 3 * 23
+    for prompt, output, one in zip(prompts, outputs, params):
+        got = output.outputs[0].token_ids
+        assert len(got) == 24 and output.seed == one.seed
+        check_generation(state, TINY_B, prompt, got, one, one.seed, slack)
+
+
+def test_same_seed_same_tokens_in_any_company(tmp_path):
+    from ayaka_b200 import SamplingParams
+
+    folder, _ = es.make_model(tmp_path / "b", TINY_B, 1, INIT_LOUD, "float32")
+    prompt = tuple(random_tokens(503, 37, 9))
+    params = SamplingParams(temperature=1.0, top_k=40, top_p=0.9, max_tokens=20, seed=77)
+    with _llm(folder, "float32") as llm:
+        alone = llm.generate(prompt, params).outputs[0].token_ids
+        again = llm.generate(prompt, params).outputs[0].token_ids
+    others = [tuple(random_tokens(503, n, 50 + n)) for n in (3, 90, 12)]
+    with _llm(folder, "float32", max_tokens_per_step=32, block_size=4, num_blocks=200) as llm:
+        crowd = llm.generate([others[0], prompt, *others[1:]],
+                             [SamplingParams(temperature=1.3, max_tokens=9, seed=1), params,
+                              SamplingParams(temperature=0.0, max_tokens=30),
+                              SamplingParams(temperature=0.7, max_tokens=15)])
+    assert alone == again == crowd[1].outputs[0].token_ids
+    other_seed = SamplingParams(temperature=1.0, top_k=40, top_p=0.9, max_tokens=20, seed=78)
+    with _llm(folder, "float32") as llm:
+        assert llm.generate(prompt, other_seed).outputs[0].token_ids != alone
+
+
+def test_a_cache_smaller_than_the_crowd(tmp_path):
+    """Twelve requests, four at a time, on 10 pages: some are cut short by the cache, none gets
+    a wrong token, and every page comes back."""
+    from ayaka_b200 import SamplingParams
+
+    folder, state = es.make_model(tmp_path / "a", TINY_A, 0, INIT_LOUD, "float32")
+    prompts = [random_tokens(256, 6 + 3 * (i % 4), 600 + i) for i in range(12)]
+    params = SamplingParams(temperature=0.0, max_tokens=40)
+    with _llm(folder, "float32", num_blocks=11, block_size=16, max_running=4) as llm:
+        outputs = llm.generate([tuple(p) for p in prompts], params)
+        manager = llm.core.manager
+        manager.check_integrity()
+        assert manager.live_requests() == []
+        assert manager.num_free_pages() == manager.pools[0].num_usable
+        assert llm.scheduler.stats.shed >= 1
+    cut = 0
+    for prompt, output in zip(prompts, outputs):
+        got = list(output.outputs[0].token_ids)
+        assert got == plain.greedy_generate(state, TINY_A, prompt, len(got))
+        if len(got) < 40:
+            cut += 1
+            assert output.notes and "cache is full" in output.notes[0]
+    assert cut >= 1
+
+
+def test_stream_and_stop_token(tmp_path):
+    from ayaka_b200 import SamplingParams
+
+    folder, state = es.make_model(tmp_path / "a", TINY_A, 0, INIT_LOUD, "float32")
+    prompt = random_tokens(256, 11, 5)
+    expected = plain.greedy_generate(state, TINY_A, prompt, 12)
+    with _llm(folder, "float32") as llm:
+        pieces = list(llm.stream(tuple(prompt), SamplingParams(temperature=0.0, max_tokens=12)))
+        assert [t for piece in pieces for t in piece.outputs[0].token_ids] == expected
+        assert pieces[-1].finished and not any(piece.finished for piece in pieces[:-1])
+        stop = expected[4]
+        first = expected.index(stop)
+        output = llm.generate(tuple(prompt), SamplingParams(
+            temperature=0.0, max_tokens=12, stop_token_ids=frozenset({stop})))
+        assert list(output.outputs[0].token_ids) == expected[:first + 1]
+        assert output.outputs[0].finish_reason.value == "stop"
+        assert output.outputs[0].stop_reason == stop
+        generator = llm.stream(tuple(prompt), SamplingParams(temperature=0.0, max_tokens=12))
+        next(generator)
+        generator.close()  # cancels
+        assert llm.core.manager.live_requests() == []
+        from ayaka_b200.errors import InvalidRequestError
+        with pytest.raises(InvalidRequestError):
+            llm.generate("text", None)
+        with pytest.raises(InvalidRequestError):
+            llm.generate((1, 2, 256), None)
+
+
+def test_command_line(tmp_path):
+    folder, state = es.make_model(tmp_path / "a", TINY_A, 0, INIT_LOUD, "float32")
+    prompt = random_tokens(256, 9, 8)
+    done = subprocess.run(
+        [sys.executable, "-m", "ayaka_b200", "run", str(folder), "-p",
+         ",".join(map(str, prompt)), "--max-tokens", "10", "--dtype", "fp32"],
+        capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert done.returncode == 0, done.stderr
+    assert [int(t) for t in done.stdout.split()] == plain.greedy_generate(state, TINY_A, prompt,
+                                                                          10)
+    assert "cache pages" in done.stderr
+    bad = subprocess.run([sys.executable, "-m", "ayaka_b200", "run", str(folder), "-p", "hello"],
+                         capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert bad.returncode == 2 and "Traceback" not in bad.stderr
+    missing = subprocess.run([sys.executable, "-m", "ayaka_b200", "run", str(tmp_path / "none"),
+                              "-p", "1"], capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert missing.returncode == 4
+
+
+# ---- the sampling kernel alone ---------------------------------------------------------------
+@pytest.mark.parametrize("vocab", [503, 50257])
+def test_sample_kernel_against_the_float64_oracle(vocab):
+    from ayaka_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(vocab)
+    rows = 48
+    logits = (torch.randn(rows, vocab, generator=g) * 3.0)
+    logits[5, 10:20] = 7.0  # ties among the most likely tokens
+    logits[6] = 0.25  # every token ties
+    temperature = torch.tensor([0.8, 1.0, 1.7, 0.3] * 12)
+    top_k = torch.tensor([0, 0, 5, 50, 0, 0, 0, 1000] * 6, dtype=torch.int32)
+    top_p = torch.tensor([1.0, 0.9, 1.0, 0.5, 1.0, 0.95] * 8)
+    min_p = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.1, 0.02, 0.0, 0.3] * 6)
+    temperature[7] = 0.0  # a greedy row inside a sampling batch
+    seeds = torch.arange(rows, dtype=torch.int64) * 7919 + 3
+    positions = torch.arange(rows, dtype=torch.int64) + 100
+    out = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    ops.sample(logits.cuda(), temperature.cuda(), top_k.cuda(), top_p.cuda(), min_p.cuda(),
+               seeds.cuda(), positions.cuda(), out)
+    got = out.tolist()
+    exact = 0
+    for r in range(rows):
+        u = plain.draw_uniform(int(seeds[r]), int(positions[r]))
+        want = plain.sample_token(logits[r], float(temperature[r]), u, int(top_k[r]),
+                                  float(top_p[r]), float(min_p[r]))
+        if got[r] == want:
+            exact += 1
+            continue
+        # fp32 exp against float64: only a u within rounding of a CDF boundary may differ
+        assert float(temperature[r]) > 0
+        nudged = {plain.sample_token(logits[r], float(temperature[r]), u + d, int(top_k[r]),
+                                     float(top_p[r]), float(min_p[r]))
+                  for d in (-1e-5, 1e-5)}
+        assert got[r] in nudged, (r, got[r], want)
+    assert exact >= rows - 2
+    assert got[7] == plain.argmax_smallest_id(logits[7])
+
+
+def test_sample_kernel_frequencies_follow_the_distribution():
+    from ayaka_b200.kernels import ops
+
+    probabilities = torch.tensor([0.5, 0.25, 0.125, 0.0625, 0.0625])
+    draws = 4000
+    logits = probabilities.log().repeat(draws, 1).cuda()
+    seeds = torch.full((draws,), 12345, dtype=torch.int64, device="cuda")
+    positions = torch.arange(draws, dtype=torch.int64, device="cuda")
+    out = torch.zeros(draws, dtype=torch.int32, device="cuda")
+    ops.sample(logits, torch.ones(draws, device="cuda"), None, None, None, seeds, positions, out)
+    counts = torch.bincount(out.cpu().long(), minlength=5).double() / draws
+    assert torch.allclose(counts, probabilities.double(), atol=0.03)
+    expected = [plain.sample_token(probabilities.log(), 1.0, plain.draw_uniform(12345, p))
+                for p in range(200)]
+    assert out[:200].tolist() == expected
