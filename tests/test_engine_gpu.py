@@ -164,7 +164,7 @@ def test_step_refuses_what_the_cache_cannot_hold(models):
     from ayaka_b200.errors import CapacityError, InvalidRequestError
 
     folder, _, config = models["A", "float32"]
-    core = es.build_core(folder, "float32", num_blocks=3)  # two usable pages = 32 tokens
+    core = es.build_core(folder, "float32", num_blocks=3, max_running=2)  # two usable pages
     core.step([StepEntry("a", list(range(20)), [19])])
     with pytest.raises(CapacityError):
         core.step([StepEntry("b", list(range(20)), [])])
