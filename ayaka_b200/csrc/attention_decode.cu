@@ -1,0 +1,287 @@
+// Paged attention for decode rows: one query row per request, keys split over several CTAs.
+//
+// A decode step reads every cached key and value of every live request once; with one row
+// per request there is no reuse, so the kernel is built to keep many 16-byte loads in
+// flight. grid = (splits, heads, requests). A CTA of 128 threads takes one contiguous share
+// of the request's keys; TPK threads cooperate on one key (each holds 8 of head_dim's
+// elements), so a CTA covers 128 / TPK keys per pass, four passes unrolled. Scores, the
+// running maximum and sum (online softmax) and the weighted sum of values are fp32. Each
+// CTA leaves (max, sum, weighted values) of its share in scratch memory; the CTA that
+// finishes last for a (request, head) — found with an atomic ticket — merges the shares in
+// split order and writes the output row. With splits == 1 nothing goes through scratch.
+//
+// Scratch: partial [requests * heads * splits * (head_dim + 2)] floats and one int ticket
+// per (request, head), zero before the first launch and left zero by every launch.
+// Cache layout: [page][kv_head][slot][head_dim]; block-table entry 0 = no page.
+#include "common.cuh"
+
+namespace ayk {
+
+constexpr int DEC_THREADS = 128;
+constexpr int DEC_UNROLL = 4;
+
+template <typename T> struct Frag8;
+template <> struct Frag8<float> {
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(p + 4));
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+};
+template <> struct Frag8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+
+// Merge (max, sum, acc[8]) of `other` into the running triple.
+__device__ __forceinline__ void merge_state(float& m, float& l, float* acc, float om, float ol,
+                                            const float* oacc) {
+  const float nm = fmaxf(m, om);
+  if (nm == -INFINITY) return;  // both empty
+  const float a = expf(m - nm), b = expf(om - nm);
+  l = l * a + ol * b;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = acc[i] * a + oacc[i] * b;
+  m = nm;
+}
+
+template <typename T, int TPK>
+__global__ void __launch_bounds__(DEC_THREADS)
+attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k_pages,
+                        const T* __restrict__ v_pages, const int* __restrict__ block_table,
+                        int table_stride, const int* __restrict__ request_of_row,
+                        const int* __restrict__ positions, T* __restrict__ out, int ld_out,
+                        int num_kv_heads, int group, int head_dim, int page_size, float scale,
+                        int window, float* __restrict__ partial, int* __restrict__ tickets) {
+  constexpr int KEYS_PER_PASS = DEC_THREADS / TPK;
+  __shared__ float s_m[DEC_THREADS / 32][TPK], s_l[DEC_THREADS / 32][TPK];
+  __shared__ float s_acc[DEC_THREADS / 32][TPK][8];
+  __shared__ int s_last;
+
+  const int split = blockIdx.x, splits = gridDim.x;
+  const int head = blockIdx.y, num_heads = gridDim.y;
+  const int row = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int sub = tid % TPK;        // which 8 elements of head_dim
+  const int key_slot = tid / TPK;   // which key of the pass
+  const bool dims_ok = sub * 8 < head_dim;
+  const int req = request_of_row[row];
+  T* dst = out + (size_t)row * ld_out + (size_t)head * head_dim;
+  if (req < 0) {  // a padding row: zeros, no scratch, no ticket
+    if (split == 0) {
+      for (int d = tid; d < head_dim; d += DEC_THREADS) stf(dst + d, 0.f);
+    }
+    return;
+  }
+  const int kv_head = head / group;
+  const int pos = positions[row];
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int total = pos + 1 - lo;
+  int share = (total + splits - 1) / splits;
+  share = (share + KEYS_PER_PASS - 1) / KEYS_PER_PASS * KEYS_PER_PASS;
+  const int k_lo = lo + split * share;
+  const int k_hi = k_lo + share < pos + 1 ? k_lo + share : pos + 1;
+
+  float qf[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) qf[i] = 0.f;
+  if (dims_ok) {
+    float tmp[8];
+    Frag8<T>::load(q + (size_t)row * ld_q + (size_t)head * head_dim + sub * 8, tmp);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qf[i] = tmp[i] * scale;
+  }
+  const int* table = block_table + (size_t)req * table_stride;
+  float m = -INFINITY, l = 0.f, acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+
+  for (int base = k_lo; base < k_hi; base += KEYS_PER_PASS * DEC_UNROLL) {
+    float kf[DEC_UNROLL][8], vf[DEC_UNROLL][8];
+    bool valid[DEC_UNROLL];
+#pragma unroll
+    for (int u = 0; u < DEC_UNROLL; ++u) {
+      const int key = base + u * KEYS_PER_PASS + key_slot;
+      valid[u] = key < k_hi;
+      if (valid[u] && dims_ok) {
+        const int page = table[key / page_size];
+        const size_t off = (((size_t)page * num_kv_heads + kv_head) * page_size +
+                            key % page_size) * head_dim + sub * 8;
+        Frag8<T>::load(k_pages + off, kf[u]);
+        Frag8<T>::load(v_pages + off, vf[u]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { kf[u][i] = 0.f; vf[u][i] = 0.f; }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < DEC_UNROLL; ++u) {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s = fmaf(qf[i], kf[u][i], s);
+#pragma unroll
+      for (int o = TPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (valid[u]) {
+        const float nm = fmaxf(m, s);
+        const float corr = expf(m - nm);
+        const float p = expf(s - nm);
+        l = l * corr + p;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, vf[u][i], acc[i] * corr);
+        m = nm;
+      }
+    }
+  }
+  // merge the key slots that share `sub`: first inside the warp, then across warps
+#pragma unroll
+  for (int o = TPK; o < 32; o <<= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o);
+    const float ol = __shfl_xor_sync(0xffffffffu, l, o);
+    float oacc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) oacc[i] = __shfl_xor_sync(0xffffffffu, acc[i], o);
+    merge_state(m, l, acc, om, ol, oacc);
+  }
+  if (lane < TPK) {
+    s_m[warp][lane] = m;
+    s_l[warp][lane] = l;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s_acc[warp][lane][i] = acc[i];
+  }
+  __syncthreads();
+  if (tid < TPK) {
+    m = s_m[0][tid];
+    l = s_l[0][tid];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = s_acc[0][tid][i];
+    for (int w = 1; w < DEC_THREADS / 32; ++w) {
+      merge_state(m, l, acc, s_m[w][tid], s_l[w][tid], s_acc[w][tid]);
+    }
+    if (splits == 1) {
+      if (sub * 8 < head_dim) {
+        const float inv = 1.f / l;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) stf(dst + tid * 8 + i, acc[i] * inv);
+      }
+    } else {
+      float* mine = partial + ((size_t)(row * num_heads + head) * splits + split) *
+                                  (head_dim + 2);
+      if (tid == 0) { mine[0] = m; mine[1] = l; }
+      if (sub * 8 < head_dim) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mine[2 + tid * 8 + i] = acc[i];
+      }
+    }
+  }
+  if (splits == 1) return;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int ticket = atomicAdd(&tickets[row * num_heads + head], 1);
+    s_last = ticket == splits - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float* shares = partial + (size_t)(row * num_heads + head) * splits * (head_dim + 2);
+  float top = -INFINITY;
+  for (int s = 0; s < splits; ++s) top = fmaxf(top, shares[s * (head_dim + 2)]);
+  float denom = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float sm = shares[s * (head_dim + 2)];
+    if (sm != -INFINITY) denom += shares[s * (head_dim + 2) + 1] * expf(sm - top);
+  }
+  for (int d = tid; d < head_dim; d += DEC_THREADS) {
+    float sum = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float sm = shares[s * (head_dim + 2)];
+      if (sm != -INFINITY) sum += shares[s * (head_dim + 2) + 2 + d] * expf(sm - top);
+    }
+    stf(dst + d, sum / denom);
+  }
+  if (tid == 0) tickets[row * num_heads + head] = 0;  // ready for the next launch
+}
+
+template <typename T, int TPK>
+int launch_decode(const void* q, int ld_q, const void* k_pages, const void* v_pages,
+                  const int* block_table, int table_stride, const int* request_of_row,
+                  const int* positions, void* out, int ld_out, int num_rows, int num_heads,
+                  int num_kv_heads, int head_dim, int page_size, float scale, int window,
+                  int splits, float* partial, int* tickets, cudaStream_t stream) {
+  dim3 grid(splits, num_heads, num_rows);
+  attention_decode_kernel<T, TPK><<<grid, DEC_THREADS, 0, stream>>>(
+      (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table, table_stride,
+      request_of_row, positions, (T*)out, ld_out, num_kv_heads, num_heads / num_kv_heads,
+      head_dim, page_size, scale, window, partial, tickets);
+  return launch_status();
+}
+
+template <typename T>
+int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v_pages,
+                     const int* block_table, int table_stride, const int* request_of_row,
+                     const int* positions, void* out, int ld_out, int num_rows, int num_heads,
+                     int num_kv_heads, int head_dim, int page_size, float scale, int window,
+                     int splits, float* partial, int* tickets, cudaStream_t stream) {
+  if (num_rows == 0) return AYK_OK;
+  if (num_rows < 0 || num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads ||
+      page_size < 1 || table_stride < 1 || window < 0 || splits < 1) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (head_dim < 8 || head_dim % 8) return AYK_BAD_ARGUMENT;
+  if (head_dim > 256 || num_heads > 65535 || num_rows > 65535 || splits > 1024) {
+    return AYK_TOO_LARGE;
+  }
+  if (splits > 1 && (partial == nullptr || tickets == nullptr)) return AYK_BAD_ARGUMENT;
+  const size_t vec = 8 * sizeof(T);
+  if (((uintptr_t)k_pages % vec) || ((uintptr_t)v_pages % vec) || ((uintptr_t)q % vec) ||
+      ((size_t)ld_q * sizeof(T)) % vec) {
+    return AYK_BAD_ALIGNMENT;
+  }
+  const int frags = head_dim / 8;
+#define AYK_DECODE(TPK)                                                                        \
+  return launch_decode<T, TPK>(q, ld_q, k_pages, v_pages, block_table, table_stride,          \
+                               request_of_row, positions, out, ld_out, num_rows, num_heads,   \
+                               num_kv_heads, head_dim, page_size, scale, window, splits,      \
+                               partial, tickets, stream)
+  if (frags <= 2) AYK_DECODE(2);
+  if (frags <= 4) AYK_DECODE(4);
+  if (frags <= 8) AYK_DECODE(8);
+  if (frags <= 16) AYK_DECODE(16);
+  AYK_DECODE(32);
+#undef AYK_DECODE
+}
+
+}  // namespace ayk
+
+// type: 0 = float32, 1 = bfloat16. `partial` holds num_rows * num_heads * splits *
+// (head_dim + 2) floats and `tickets` num_rows * num_heads zeroed ints (both unused when
+// splits == 1).
+AYK_API int ayk_attention_decode(const void* q, int ld_q, const void* k_pages,
+                                 const void* v_pages, const int* block_table, int table_stride,
+                                 const int* request_of_row, const int* positions, void* out,
+                                 int ld_out, int num_rows, int num_heads, int num_kv_heads,
+                                 int head_dim, int page_size, float scale, int window,
+                                 int splits, float* partial, int* tickets, int type,
+                                 void* stream) {
+  if (type == 0) {
+    return ayk::attention_decode<float>(q, ld_q, k_pages, v_pages, block_table, table_stride,
+                                        request_of_row, positions, out, ld_out, num_rows,
+                                        num_heads, num_kv_heads, head_dim, page_size, scale,
+                                        window, splits, partial, tickets, (cudaStream_t)stream);
+  }
+  if (type == 1) {
+    return ayk::attention_decode<__nv_bfloat16>(
+        q, ld_q, k_pages, v_pages, block_table, table_stride, request_of_row, positions, out,
+        ld_out, num_rows, num_heads, num_kv_heads, head_dim, page_size, scale, window, splits,
+        partial, tickets, (cudaStream_t)stream);
+  }
+  return AYK_BAD_ARGUMENT;
+}

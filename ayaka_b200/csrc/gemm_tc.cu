@@ -200,6 +200,197 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 0) tmem_dealloc(tmem_base, BN < 32 ? 32 : BN);
 }
 
+// ---------------------------------------------------------------------------------------
+// Few rows (decode): the weight is the 128-row operand and the tokens are the narrow one
+// ("swap A and B"): D[n, m] = sum_k W[n, k] * A[m, k], with m padded to MP in {16, 32, 64}.
+// A step with a handful of tokens is pure weight streaming, and N / 128 CTAs are too few to
+// pull the weights at HBM speed, so K is split over the CTAs of a thread-block cluster
+// (grid.y = cluster size S). Each CTA accumulates its K range in tensor memory, parks the
+// partial [MP, 128] tile in its shared memory, and after a cluster barrier CTA r sums columns
+// r*MP/S .. (r+1)*MP/S over all peers through distributed shared memory in rank order 0..S-1
+// (a fixed order: the result does not change from run to run), applies the epilogue and
+// stores. Thread t owns output column n0 + t, so a warp's stores are contiguous.
+template <int MP, int STAGES>
+struct SmallSmem {
+  static constexpr int W_BYTES = TC_BM * TC_BK * 2;
+  static constexpr int A_BYTES = MP * TC_BK * 2;
+  static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
+  static constexpr int PARTIAL_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int PARTIAL_BYTES = MP * TC_BM * 4;
+  static constexpr int BAR_OFFSET = PARTIAL_OFFSET + PARTIAL_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16;
+  static constexpr int DYNAMIC = TOTAL + 1024;
+};
+
+__device__ __forceinline__ void store_output(void* out, int ldo, int m, int n, float v, int mode,
+                                             int act) {
+  if (mode == OUT_BF16) {
+    reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] =
+        __float2bfloat16_rn(activate(v, act));
+  } else if (mode == OUT_F32) {
+    reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = activate(v, act);
+  } else {
+    float* dst = reinterpret_cast<float*>(out) + (size_t)m * ldo + n;
+    *dst = *dst + v;
+  }
+}
+
+template <int MP, int STAGES>
+__global__ void __launch_bounds__(128)
+gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
+                     const __grid_constant__ CUtensorMap map_a, const float* __restrict__ bias,
+                     void* __restrict__ out, int ldo, int M, int N, int K, int act, int mode,
+                     int kb_per_split, int* __restrict__ status) {
+  using L = SmallSmem<MP, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
+  float* partial = reinterpret_cast<float*>(smem + L::PARTIAL_OFFSET);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty = full + STAGES;
+  uint64_t* accum = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * TC_BM;
+  const int splits = gridDim.y;
+  const int rank = blockIdx.y;  // cluster = (1, splits, 1): the rank inside the cluster
+  const int num_kb = (K + TC_BK - 1) / TC_BK;
+  const int kb_lo = rank * kb_per_split;
+  const int kb_hi = kb_lo + kb_per_split < num_kb ? kb_lo + kb_per_split : num_kb;
+  const int my_kb = kb_hi > kb_lo ? kb_hi - kb_lo : 0;
+  constexpr uint32_t TMEM_COLS = MP < 32 ? 32 : MP;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    *failed = 0;
+    mbar_fence_init();
+    tma_prefetch_map(&map_w);
+    tma_prefetch_map(&map_a);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  int issued = 0;
+  if (warp == 0 && lane == 0) {
+    for (int i = 0; i < my_kb; ++i) {
+      const int s = i % STAGES;
+      if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) {
+        *failed = 1;
+        break;
+      }
+      uint8_t* w_tile = smem + s * L::STAGE_BYTES;
+      mbar_expect_tx(&full[s], L::STAGE_BYTES);
+      tma_load_2d(w_tile, &map_w, &full[s], (kb_lo + i) * TC_BK, n0);
+      tma_load_2d(w_tile + L::W_BYTES, &map_a, &full[s], (kb_lo + i) * TC_BK, 0);
+      issued = i + 1;
+    }
+  } else if (warp == 1 && lane == 0) {
+    constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, MP);
+    bool ok = true;
+    for (int i = 0; i < my_kb; ++i) {
+      const int s = i % STAGES;
+      if (!mbar_wait(&full[s], (i / STAGES) & 1)) {
+        *failed = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint8_t* w_tile = smem + s * L::STAGE_BYTES;
+      const uint8_t* a_tile = w_tile + L::W_BYTES;
+#pragma unroll
+      for (int k = 0; k < TC_BK / 16; ++k) {
+        umma_f16(tmem_base, umma_desc_k128(w_tile, k * 32), umma_desc_k128(a_tile, k * 32),
+                 idesc, (i | k) != 0);
+      }
+      umma_commit(&empty[s]);
+    }
+    if (ok && my_kb > 0) umma_commit(accum);
+  }
+  __syncwarp();
+  bool have = true;
+  if (my_kb > 0) {
+    have = mbar_wait(accum, 0);
+    if (!have) *failed = 1;
+  }
+  tc_fence_after();
+
+  // this CTA's partial sums: thread t holds output column n0 + t for every padded row
+  const int t = threadIdx.x;
+  const int n = n0 + t;
+  if (splits == 1) {
+    if (have && *failed == 0) {
+#pragma unroll
+      for (int c = 0; c < MP / 16; ++c) {
+        uint32_t raw[16];
+        tmem_ld_32x16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 16), raw);
+        tmem_ld_wait();
+        if (n < N) {
+          const float b = bias != nullptr ? __ldg(bias + n) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = c * 16 + j;
+            if (m < M) store_output(out, ldo, m, n, __uint_as_float(raw[j]) + b, mode, act);
+          }
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < MP / 16; ++c) {
+      uint32_t raw[16];
+      if (my_kb > 0 && have) {
+        tmem_ld_32x16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 16), raw);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) raw[j] = 0u;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) partial[(c * 16 + j) * TC_BM + t] = __uint_as_float(raw[j]);
+      __syncwarp();
+    }
+    __syncthreads();
+    cluster_sync_all();
+    const int cols = MP / splits;  // the host picks splits that divide MP
+    if (*failed == 0 && n < N) {
+      const float b = bias != nullptr ? __ldg(bias + n) : 0.f;
+      for (int j = 0; j < cols; ++j) {
+        const int m = rank * cols + j;
+        if (m >= M) break;
+        float sum = 0.f;
+        for (int p = 0; p < splits; ++p) sum += ld_peer_f32(partial + m * TC_BM + t, p);
+        store_output(out, ldo, m, n, sum + b, mode, act);
+      }
+    }
+    cluster_sync_all();  // nobody leaves while a peer may still read its tile
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*failed != 0) {
+    if (warp == 0 && lane == 0) {
+      for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i) {
+        mbar_wait(&full[i % STAGES], (i / STAGES) & 1);
+      }
+      atomicExch(status, AYK_WAIT_TIMEOUT);
+    }
+    __syncthreads();
+  }
+  if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
 // Tensor maps are cached by what they describe: weights are static and activations live in
 // persistent buffers, so a serving process encodes each map once.
 struct MapKey {
@@ -267,6 +458,44 @@ int launch_gemm_tc(const void* a, int lda, const void* w, int ldw, const float* 
   return launch_status();
 }
 
+template <int MP, int STAGES>
+int launch_gemm_tc_small(const void* a, int lda, const void* w, int ldw, const float* bias,
+                         void* out, int ldo, int M, int N, int K, int act, int mode, int splits,
+                         int* status, cudaStream_t stream) {
+  using L = SmallSmem<MP, STAGES>;
+  CUtensorMap map_a, map_w;
+  int r = cached_map(w, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BM, &map_w);
+  if (r != AYK_OK) return r;
+  r = cached_map(a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, MP, &map_a);
+  if (r != AYK_OK) return r;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_small_kernel<MP, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYNAMIC);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int num_kb = (K + TC_BK - 1) / TC_BK;
+  if (splits < 1) splits = 1;
+  while (splits > 1 && (splits > num_kb || splits > 8 || MP % splits)) splits >>= 1;
+  int kb_per_split = (num_kb + splits - 1) / splits;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((N + TC_BM - 1) / TC_BM, splits, 1);
+  config.blockDim = dim3(128, 1, 1);
+  config.dynamicSmemBytes = L::DYNAMIC;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = 1;
+  attribute[0].val.clusterDim.y = splits;
+  attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&config, gemm_tc_small_kernel<MP, STAGES>, map_w, map_a,
+                                     bias, out, ldo, M, N, K, act, mode, kb_per_split, status);
+  return e == cudaSuccess ? launch_status() : (int)e;
+}
+
 }  // namespace ayk
 
 // mode: 0 = bf16 out with activation, 1 = fp32 out with activation, 2 = fp32 out += (residual).
@@ -288,6 +517,27 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
     return AYK_BAD_ALIGNMENT;
   }
   cudaStream_t s = (cudaStream_t)stream;
+  if (tile_n == 0 && M <= 64) tile_n = -1;  // few rows: the weight-streaming kernel
+  if (tile_n < 0) {
+    if (M > 64) return AYK_BAD_ARGUMENT;
+    int splits = -tile_n;  // -1: choose; -2, -4, -8: that many K splits; -100: one split
+    if (tile_n == -100) splits = 1;
+    if (tile_n == -1) {
+      const int tiles = (N + TC_BM - 1) / TC_BM;
+      splits = 1;
+      while (splits < 8 && tiles * splits * 2 <= 296) splits <<= 1;
+    }
+    if (M <= 16) {
+      return launch_gemm_tc_small<16, 5>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
+                                         splits, status, s);
+    }
+    if (M <= 32) {
+      return launch_gemm_tc_small<32, 5>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
+                                         splits, status, s);
+    }
+    return launch_gemm_tc_small<64, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
+                                       splits, status, s);
+  }
   if (tile_n == 0) tile_n = 128;
   switch (tile_n) {
     case 64:

@@ -19,6 +19,8 @@ __all__ = [
     "ACTIVATIONS",
     "argmax",
     "attention",
+    "attention_decode",
+    "decode_splits",
     "embed_rows",
     "kv_store",
     "launch_count",
@@ -244,6 +246,56 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                 c_int(out.stride(0)), c_int(n), c_int(num_heads), c_int(kv_heads),
                 c_int(head_dim), c_int(page_size), c_float(scale), c_int(window),
                 c_int(_TYPE[q.dtype]), _stream())
+    check(status, op)
+
+
+def decode_splits(num_rows: int, num_heads: int, max_kv_len: int) -> int:
+    """How many CTAs share one (request, head) of a decode step: enough to fill the GPU a few
+    times over, never less than 64 keys each."""
+    want = -(-592 // max(1, num_rows * num_heads))
+    return max(1, min(want, -(-max_kv_len // 64), 64))
+
+
+def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                     block_table: torch.Tensor, request_of_row: torch.Tensor,
+                     positions: torch.Tensor, out: torch.Tensor, *, num_heads: int, scale: float,
+                     window: int = 0, rows: int | None = None, splits: int = 1,
+                     partial: torch.Tensor | None = None,
+                     tickets: torch.Tensor | None = None) -> None:
+    """Attention for steps whose every request brings one row (same contract as
+    :func:`attention`). ``splits`` CTAs share each (request, head); with more than one,
+    ``partial`` (float32, at least rows * heads * splits * (head_dim + 2)) and ``tickets``
+    (int32 zeros, at least rows * heads; left zero) are scratch."""
+    op = "attention_decode"
+    _need(op, "q", q, ndim=2)
+    _need(op, "out", out, q.dtype, 2)
+    _need(op, "k_pages", k_pages, q.dtype, 4)
+    _need(op, "v_pages", v_pages, q.dtype, 4)
+    _need(op, "block_table", block_table, torch.int32, 2)
+    _need(op, "request_of_row", request_of_row, torch.int32, 1)
+    _need(op, "positions", positions, torch.int32, 1)
+    if q.dtype not in _TYPE or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+        raise BackendError(f"{op}: contiguous float32 or bfloat16 pages only")
+    _, kv_heads, page_size, head_dim = k_pages.shape
+    n = q.shape[0] if rows is None else rows
+    if q.shape[1] != num_heads * head_dim or out.shape[1] != q.shape[1] or n > out.shape[0] \
+            or n > request_of_row.shape[0] or n > positions.shape[0] or \
+            v_pages.shape != k_pages.shape:
+        raise BackendError(f"{op}: shapes do not fit")
+    if splits > 1:
+        if partial is None or tickets is None:
+            raise BackendError(f"{op}: more than one split needs scratch")
+        _need(op, "partial", partial, torch.float32)
+        _need(op, "tickets", tickets, torch.int32)
+        if partial.numel() < n * num_heads * splits * (head_dim + 2) or \
+                tickets.numel() < n * num_heads:
+            raise BackendError(f"{op}: the scratch buffers are too small")
+    status = library("attention_decode").ayk_attention_decode(
+        _ptr(q), c_int(q.stride(0)), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+        c_int(block_table.stride(0)), _ptr(request_of_row), _ptr(positions), _ptr(out),
+        c_int(out.stride(0)), c_int(n), c_int(num_heads), c_int(kv_heads), c_int(head_dim),
+        c_int(page_size), c_float(scale), c_int(window), c_int(splits), _ptr(partial),
+        _ptr(tickets), c_int(_TYPE[q.dtype]), _stream())
     check(status, op)
 
 

@@ -90,7 +90,24 @@ class Attention(Mixer):
         if cache.writes:
             ops.kv_store(k, v, group.slot_mapping, cache.k_pages, cache.v_pages, rows=n)
         attended = step.workspace.buffer("attention.out", self.q_width, self.ctx.dtype)
-        ops.attention(q, cache.k_pages, cache.v_pages, group.block_table, step.request_of_row,
-                      step.positions, attended, num_heads=self.num_heads, scale=self.scale,
-                      window=self.window, rows=n)
+        if step.decode_only:
+            # one row per request: the split-KV kernel; its scratch lives in the workspace
+            reach = min(step.max_kv_len, self.window) if self.window else step.max_kv_len
+            splits = ops.decode_splits(n, self.num_heads, reach)
+            partial = tickets = None
+            if splits > 1:
+                # rows * heads * splits never exceeds 592 + rows * heads (see decode_splits)
+                pairs = step.workspace.max_rows * self.num_heads
+                partial = step.workspace.buffer(
+                    "attention.partial", (592 + pairs) * (self.head_dim + 2), torch.float32,
+                    rows=1)
+                tickets = step.workspace.buffer("attention.tickets", pairs, torch.int32, rows=1)
+            ops.attention_decode(q, cache.k_pages, cache.v_pages, group.block_table,
+                                 step.request_of_row, step.positions, attended,
+                                 num_heads=self.num_heads, scale=self.scale, window=self.window,
+                                 rows=n, splits=splits, partial=partial, tickets=tickets)
+        else:
+            ops.attention(q, cache.k_pages, cache.v_pages, group.block_table,
+                          step.request_of_row, step.positions, attended,
+                          num_heads=self.num_heads, scale=self.scale, window=self.window, rows=n)
         ops.linear(attended, self.out_weight, self.out_bias, residual, residual=True, rows=n)

@@ -153,6 +153,44 @@ def test_linear_tcgen05_tiles_and_strides(tile_n):
     assert torch.isnan(out[m:]).all()
 
 
+@pytest.mark.parametrize("splits", [-100, -2, -4, -8, 0])
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 40, 64])
+def test_linear_tcgen05_few_rows(m, splits):
+    """The weight-streaming kernel of decode steps: every padded row count, every K split
+    (a negative tile selects it: -100 one CTA per tile, -2/-4/-8 that many cluster CTAs)."""
+    from ayaka_b200.kernels import gemm_tc
+    for n, k in ((1600, 1600), (300, 6400), (50257, 160), (136, 72)):
+        a = _randn(m, k, seed=30, dtype=torch.bfloat16)
+        w = _randn(n, k, seed=31, dtype=torch.bfloat16, scale=1 / math.sqrt(k))
+        bias = _randn(n, seed=32)
+        exact = a.double() @ w.double().t() + bias.double()
+        out = torch.full((m + 1, n), float("nan"), device=DEV)
+        gemm_tc.linear_bf16(a, w, bias, out, m, 0, False, tile_n=splits)
+        gemm_tc.check_status(a.device)
+        torch.testing.assert_close(out[:m].double(), exact, rtol=1e-4, atol=1e-4)
+        assert torch.isnan(out[m:]).all()
+        base = _randn(m, n, seed=33)
+        acc = base.clone()
+        gemm_tc.linear_bf16(a, w, bias, acc, m, 0, True, tile_n=splits)
+        torch.testing.assert_close(acc.double(), exact + base.double(), rtol=1e-4, atol=1e-4)
+        half = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+        gemm_tc.linear_bf16(a, w, bias, half, m, 2, False, tile_n=splits)
+        torch.testing.assert_close(half.double(), plain.gelu(exact, "gelu"), rtol=1e-2, atol=1e-2)
+    gemm_tc.check_status(a.device)
+
+
+def test_linear_tcgen05_few_rows_is_reproducible():
+    from ayaka_b200.kernels import gemm_tc
+    a = _randn(8, 6400, seed=34, dtype=torch.bfloat16)
+    w = _randn(1600, 6400, seed=35, dtype=torch.bfloat16, scale=0.02)
+    first = torch.zeros(8, 1600, device=DEV)
+    gemm_tc.linear_bf16(a, w, None, first, 8, 0, False)
+    for _ in range(5):
+        again = torch.zeros(8, 1600, device=DEV)
+        gemm_tc.linear_bf16(a, w, None, again, 8, 0, False)
+        assert torch.equal(first, again)
+
+
 def test_linear_bfloat16_unaligned_k_takes_the_cuda_core_kernel():
     ops = _ops()
     a = _randn(9, 700, seed=16, dtype=torch.bfloat16)
@@ -171,10 +209,19 @@ def test_linear_batch_invariance():
         w = _randn(200, 320, seed=19, dtype=dtype, scale=0.05)
         whole = torch.zeros(300, 200, device=DEV)
         ops.linear(a, w, None, whole, kernel=kernel)
-        for rows in (1, 7, 129):
+        for rows in (65, 70, 129):
             part = torch.zeros(rows, 200, device=DEV)
             ops.linear(a[:rows].contiguous(), w, None, part, kernel=kernel)
             assert torch.equal(part, whole[:rows])
+        # up to 64 rows the bfloat16 tensor-core product splits K over a cluster: the same
+        # sums in another order, equal within fp32 rounding and equal among themselves
+        small = torch.zeros(64, 200, device=DEV)
+        ops.linear(a[:64].contiguous(), w, None, small, kernel=kernel)
+        torch.testing.assert_close(small, whole[:64], rtol=1e-5, atol=1e-5)
+        for rows in (1, 7, 33):
+            part = torch.zeros(rows, 200, device=DEV)
+            ops.linear(a[:rows].contiguous(), w, None, part, kernel=kernel)
+            assert torch.equal(part, small[:rows])
 
 
 # ---------------------------------------------------------------------------------------------
@@ -307,6 +354,47 @@ def test_kv_store_then_attend(dtype):
     tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(out[:3].float().cpu(), expected, **tol)
     assert torch.equal(out[3].float(), torch.zeros(width, device=DEV))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+@pytest.mark.parametrize("case", [
+    # lengths, heads, kv_heads, head_dim, page, window
+    ((1, 64, 130, 700), 3, 3, 32, 16, 0),
+    ((1000, 17), 25, 25, 64, 16, 0),
+    ((40, 33, 70, 2), 6, 2, 48, 8, 0),
+    ((300, 5), 2, 1, 128, 16, 0),
+    ((90,), 2, 2, 256, 32, 0),
+    ((100, 257, 3), 4, 4, 16, 16, 24),
+    ((67, 400), 3, 1, 80, 4, 50),
+])
+def test_attention_decode_split_kv(dtype, splits, case):
+    """One row per request, the keys split over several CTAs and merged by the last one;
+    twice in a row on the same scratch, which the kernel must leave ready for reuse."""
+    ops = _ops()
+    lengths, heads, kv_heads, head_dim, page, window = case
+    rows = (1,) * len(lengths)
+    q, k_pages, v_pages, table, req, pos, seqs = _paged_case(
+        lengths, rows, heads, kv_heads, head_dim, page, dtype, seed=24, boost=(999, 2))
+    n = q.shape[0]
+    # a padding row in the middle of the batch
+    q = torch.cat([q[:1], torch.full_like(q[:1], float("nan")), q[1:]])
+    req = torch.cat([req[:1], torch.tensor([-1], dtype=torch.int32, device=DEV), req[1:]])
+    pos = torch.cat([pos[:1], torch.zeros(1, dtype=torch.int32, device=DEV), pos[1:]])
+    partial = torch.full(((n + 1) * heads * splits * (head_dim + 2),), float("nan"), device=DEV)
+    tickets = torch.zeros((n + 1) * heads, dtype=torch.int32, device=DEV)
+    scale = 0.9 / math.sqrt(head_dim)
+    expected = _attention_reference(seqs, lengths, rows, heads, kv_heads, scale, window)
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    for _ in range(2):
+        out = torch.full((n + 1, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
+        ops.attention_decode(q, k_pages, v_pages, table, req, pos, out, num_heads=heads,
+                             scale=scale, window=window, splits=splits, partial=partial,
+                             tickets=tickets)
+        got = torch.cat([out[:1], out[2:]]).double().cpu()
+        torch.testing.assert_close(got, expected, **tol)
+        assert torch.equal(out[1].float(), torch.zeros(heads * head_dim, device=DEV))
+        assert int(tickets.abs().sum()) == 0
 
 
 def test_attention_refuses_what_it_cannot_do():
