@@ -66,6 +66,8 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
   __shared__ float s_acc[DEC_THREADS / 32][TPK][8];
   __shared__ int s_last;
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int split = blockIdx.x, splits = gridDim.x;
   const int head = blockIdx.y, num_heads = gridDim.y;
   const int row = blockIdx.z;
@@ -217,11 +219,11 @@ int launch_decode(const void* q, int ld_q, const void* k_pages, const void* v_pa
                   int num_kv_heads, int head_dim, int page_size, float scale, int window,
                   int splits, float* partial, int* tickets, cudaStream_t stream) {
   dim3 grid(splits, num_heads, num_rows);
-  attention_decode_kernel<T, TPK><<<grid, DEC_THREADS, 0, stream>>>(
-      (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table, table_stride,
-      request_of_row, positions, (T*)out, ld_out, num_kv_heads, num_heads / num_kv_heads,
-      head_dim, page_size, scale, window, partial, tickets);
-  return launch_status();
+  return launch_kernel(attention_decode_kernel<T, TPK>, grid, dim3(DEC_THREADS), 0, stream, 1,
+                       (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table,
+                       table_stride, request_of_row, positions, (T*)out, ld_out, num_kv_heads,
+                       num_heads / num_kv_heads, head_dim, page_size, scale, window, partial,
+                       tickets);
 }
 
 template <typename T>
@@ -260,6 +262,8 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
 }
 
 }  // namespace ayk
+
+AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
 
 // type: 0 = float32, 1 = bfloat16. `partial` holds num_rows * num_heads * splits *
 // (head_dim + 2) floats and `tickets` num_rows * num_heads zeroed ints (both unused when

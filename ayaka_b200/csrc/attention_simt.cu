@@ -51,6 +51,8 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
   __shared__ __align__(16) float q_s[ATT_WARPS][ATT_MAX_HD];
   __shared__ float p_s[ATT_WARPS][32];
   __shared__ long long off_s[ATT_WARPS][32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * ATT_WARPS + warp;
   const int head = blockIdx.y;
@@ -131,6 +133,8 @@ __global__ void kv_store_kernel(const T* __restrict__ k, const T* __restrict__ v
                                 const int* __restrict__ slot_mapping, T* __restrict__ k_pages,
                                 T* __restrict__ v_pages, int num_kv_heads, int head_dim,
                                 int page_size) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int slot = slot_mapping[row];
   if (slot < 0) return;
@@ -160,11 +164,11 @@ int attention_simt(const void* q, int ld_q, const void* k_pages, const void* v_p
   const size_t vec = 8 * sizeof(T);
   if (((uintptr_t)k_pages % vec) || ((uintptr_t)v_pages % vec)) return AYK_BAD_ALIGNMENT;
   dim3 grid((num_rows + ATT_WARPS - 1) / ATT_WARPS, num_heads);
-  attention_simt_kernel<T><<<grid, ATT_WARPS * 32, 0, stream>>>(
-      (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table, table_stride,
-      request_of_row, positions, (T*)out, ld_out, num_rows, num_kv_heads,
-      num_heads / num_kv_heads, head_dim, page_size, scale, window);
-  return launch_status();
+  return launch_kernel(attention_simt_kernel<T>, grid, dim3(ATT_WARPS * 32), 0, stream, 1,
+                       (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table,
+                       table_stride, request_of_row, positions, (T*)out, ld_out, num_rows,
+                       num_kv_heads, num_heads / num_kv_heads, head_dim, page_size, scale,
+                       window);
 }
 
 template <typename T>
@@ -176,15 +180,16 @@ int kv_store(const void* k, const void* v, int ld_kv, const int* slot_mapping, v
       ld_kv < num_kv_heads * head_dim) {
     return AYK_BAD_ARGUMENT;
   }
-  kv_store_kernel<T><<<num_rows, 256, 0, stream>>>((const T*)k, (const T*)v, ld_kv,
-                                                    slot_mapping, (T*)k_pages, (T*)v_pages,
-                                                    num_kv_heads, head_dim, page_size);
-  return launch_status();
+  return launch_kernel(kv_store_kernel<T>, dim3(num_rows), dim3(256), 0, stream, 1,
+                       (const T*)k, (const T*)v, ld_kv, slot_mapping, (T*)k_pages, (T*)v_pages,
+                       num_kv_heads, head_dim, page_size);
 }
 
 }  // namespace ayk
 
 using bf16 = __nv_bfloat16;
+
+AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
 
 // type: 0 = float32, 1 = bfloat16 (queries, pages and output share it).
 AYK_API int ayk_attention_simt(const void* q, int ld_q, const void* k_pages, const void* v_pages,

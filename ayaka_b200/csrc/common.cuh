@@ -80,6 +80,52 @@ __device__ __forceinline__ float activate(float x, int act) {
   return x;
 }
 
+// Programmatic dependent launch: a kernel launched with the attribute may start while its
+// predecessor in the stream is still running; pdl_wait() blocks until the predecessor has
+// finished and its writes are visible, so everything before it (barrier set-up, tensor-memory
+// allocation, weight prefetch) overlaps the predecessor's tail. Every kernel launched through
+// launch_kernel() calls pdl_wait() before it touches anything another kernel produces or
+// reads, which keeps the chain transitive.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+inline int& pdl_enabled() {
+  static int enabled = 1;
+  return enabled;
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                         cudaStream_t stream, int cluster_y, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int n = 0;
+  if (cluster_y > 1) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = 1;
+    attrs[n].val.clusterDim.y = cluster_y;
+    attrs[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl_enabled()) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  config.attrs = attrs;
+  config.numAttrs = n;
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaGetLastError();
+  return e == cudaSuccess ? AYK_OK : (int)e;
+}
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? AYK_OK : (int)e;

@@ -11,6 +11,8 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
                                   const int* __restrict__ add_index, int add_rows,
                                   float* __restrict__ out, int ld_out, int width,
                                   int* __restrict__ bad_index) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   int id = index[row];
   if (id < 0 || id >= table_rows) {
@@ -43,16 +45,17 @@ int embed_rows(const void* table, const int* index, int table_rows, const void* 
   if (rows < 0 || width < 1 || ld_out < width || table_rows < 1) return AYK_BAD_ARGUMENT;
   if (add_table != nullptr && (add_index == nullptr || add_rows < 1)) return AYK_BAD_ARGUMENT;
   const int threads = width >= 1024 ? 256 : 128;
-  embed_rows_kernel<T><<<rows, threads, 0, stream>>>(
-      (const T*)table, index, table_rows, (const T*)add_table, add_index, add_rows, out, ld_out,
-      width, bad_index);
-  return launch_status();
+  return launch_kernel(embed_rows_kernel<T>, dim3(rows), dim3(threads), 0, stream, 1,
+                       (const T*)table, index, table_rows, (const T*)add_table, add_index,
+                       add_rows, out, ld_out, width, bad_index);
 }
 
 }  // namespace ayk
 
 // `bad_index` is one device int, set to 1 when an id falls outside its table (the row then
 // uses id 0); the host checks ids before the step, this only makes a slip visible.
+AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
+
 AYK_API int ayk_embed_rows_f32(const void* table, const int* index, int table_rows,
                                const void* add_table, const int* add_index, int add_rows,
                                float* out, int ld_out, int rows, int width, int* bad_index,

@@ -19,6 +19,8 @@ gemm_simt_kernel(const TA* __restrict__ a, int lda, const TW* __restrict__ w, in
                  int K, int act) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int ty = tid >> 4, tx = tid & 15;
@@ -88,14 +90,15 @@ int gemm_simt(const void* a, int lda, const void* w, int ldw, const float* bias,
   const long long gy = (M + BM - 1) / BM;
   if (gy > 65535) return AYK_TOO_LARGE;
   dim3 grid((N + BN - 1) / BN, (unsigned)gy);
-  gemm_simt_kernel<TA, TW, TOut, MODE><<<grid, 256, 0, stream>>>(
-      (const TA*)a, lda, (const TW*)w, ldw, bias, (TOut*)out, ldo, M, N, K, act);
-  return launch_status();
+  return launch_kernel(gemm_simt_kernel<TA, TW, TOut, MODE>, grid, dim3(256), 0, stream, 1,
+                       (const TA*)a, lda, (const TW*)w, ldw, bias, (TOut*)out, ldo, M, N, K, act);
 }
 
 }  // namespace ayk
 
 using bf16 = __nv_bfloat16;
+
+AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
 
 // in_type / out_type: 0 = float32, 1 = bfloat16. `residual` != 0: out is fp32 and is added to.
 AYK_API int ayk_gemm_simt(const void* a, int lda, const void* w, int ldw, const float* bias,

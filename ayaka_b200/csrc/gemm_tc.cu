@@ -76,18 +76,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  pdl_launch_dependents();
   int issued = 0;  // k-blocks whose copies the producer has started
   if (warp == 0 && lane == 0) {
+    // weights do not depend on the kernel before this one: fetch the first stages' weight
+    // tiles at once, wait for the predecessor, then fetch the activations
+    const int ahead = num_kb < STAGES ? num_kb : STAGES;
+    for (int kb = 0; kb < ahead; ++kb) {
+      uint8_t* a_tile = smem + kb * L::STAGE_BYTES;
+      mbar_expect_tx(&full[kb], L::STAGE_BYTES);
+      tma_load_2d(a_tile + TC_A_BYTES, &map_w, &full[kb], kb * TC_BK, n0);
+    }
+    pdl_wait();
     for (int kb = 0; kb < num_kb; ++kb) {
       const int s = kb % STAGES;
-      if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1)) {
-        *failed = 1;
-        break;
-      }
       uint8_t* a_tile = smem + s * L::STAGE_BYTES;
-      mbar_expect_tx(&full[s], L::STAGE_BYTES);
+      if (kb >= STAGES) {
+        if (!mbar_wait(&empty[s], ((kb / STAGES) & 1) ^ 1)) {
+          *failed = 1;
+          break;
+        }
+        mbar_expect_tx(&full[s], L::STAGE_BYTES);
+        tma_load_2d(a_tile + TC_A_BYTES, &map_w, &full[s], kb * TC_BK, n0);
+      }
       tma_load_2d(a_tile, &map_a, &full[s], kb * TC_BK, m0);
-      tma_load_2d(a_tile + TC_A_BYTES, &map_w, &full[s], kb * TC_BK, n0);
       issued = kb + 1;
     }
   } else if (warp == 1 && lane == 0) {
@@ -115,6 +127,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   // ---- epilogue: all four warps -----------------------------------------------------
   __syncwarp();
+  pdl_wait();
   bool have = mbar_wait(accum, 0);
   if (!have) *failed = 1;
   tc_fence_after();
@@ -281,17 +294,28 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  pdl_launch_dependents();
   int issued = 0;
   if (warp == 0 && lane == 0) {
+    // the weight tiles of the first stages start before the kernel ahead has finished
+    const int ahead = my_kb < STAGES ? my_kb : STAGES;
+    for (int i = 0; i < ahead; ++i) {
+      uint8_t* w_tile = smem + i * L::STAGE_BYTES;
+      mbar_expect_tx(&full[i], L::STAGE_BYTES);
+      tma_load_2d(w_tile, &map_w, &full[i], (kb_lo + i) * TC_BK, n0);
+    }
+    pdl_wait();
     for (int i = 0; i < my_kb; ++i) {
       const int s = i % STAGES;
-      if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) {
-        *failed = 1;
-        break;
-      }
       uint8_t* w_tile = smem + s * L::STAGE_BYTES;
-      mbar_expect_tx(&full[s], L::STAGE_BYTES);
-      tma_load_2d(w_tile, &map_w, &full[s], (kb_lo + i) * TC_BK, n0);
+      if (i >= STAGES) {
+        if (!mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) {
+          *failed = 1;
+          break;
+        }
+        mbar_expect_tx(&full[s], L::STAGE_BYTES);
+        tma_load_2d(w_tile, &map_w, &full[s], (kb_lo + i) * TC_BK, n0);
+      }
       tma_load_2d(w_tile + L::W_BYTES, &map_a, &full[s], (kb_lo + i) * TC_BK, 0);
       issued = i + 1;
     }
@@ -318,6 +342,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
     if (ok && my_kb > 0) umma_commit(accum);
   }
   __syncwarp();
+  pdl_wait();
   bool have = true;
   if (my_kb > 0) {
     have = mbar_wait(accum, 0);
@@ -453,9 +478,8 @@ int launch_gemm_tc(const void* a, int lda, const void* w, int ldw, const float* 
   const long long gy = (M + TC_BM - 1) / TC_BM;
   if (gy > 65535) return AYK_TOO_LARGE;
   dim3 grid((N + BN - 1) / BN, (unsigned)gy);
-  gemm_tc_kernel<BN, STAGES><<<grid, 128, L::DYNAMIC, stream>>>(map_a, map_w, bias, out, ldo, M,
-                                                                N, K, act, mode, vec_ok, status);
-  return launch_status();
+  return launch_kernel(gemm_tc_kernel<BN, STAGES>, grid, dim3(128), L::DYNAMIC, stream, 1, map_a,
+                       map_w, bias, out, ldo, M, N, K, act, mode, vec_ok, status);
 }
 
 template <int MP, int STAGES>
@@ -479,24 +503,14 @@ int launch_gemm_tc_small(const void* a, int lda, const void* w, int ldw, const f
   if (splits < 1) splits = 1;
   while (splits > 1 && (splits > num_kb || splits > 8 || MP % splits)) splits >>= 1;
   int kb_per_split = (num_kb + splits - 1) / splits;
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3((N + TC_BM - 1) / TC_BM, splits, 1);
-  config.blockDim = dim3(128, 1, 1);
-  config.dynamicSmemBytes = L::DYNAMIC;
-  config.stream = stream;
-  cudaLaunchAttribute attribute[1];
-  attribute[0].id = cudaLaunchAttributeClusterDimension;
-  attribute[0].val.clusterDim.x = 1;
-  attribute[0].val.clusterDim.y = splits;
-  attribute[0].val.clusterDim.z = 1;
-  config.attrs = attribute;
-  config.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&config, gemm_tc_small_kernel<MP, STAGES>, map_w, map_a,
-                                     bias, out, ldo, M, N, K, act, mode, kb_per_split, status);
-  return e == cudaSuccess ? launch_status() : (int)e;
+  return launch_kernel(gemm_tc_small_kernel<MP, STAGES>, dim3((N + TC_BM - 1) / TC_BM, splits, 1),
+                       dim3(128), L::DYNAMIC, stream, splits, map_w, map_a, bias, out, ldo, M, N,
+                       K, act, mode, kb_per_split, status);
 }
 
 }  // namespace ayk
+
+AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
 
 // mode: 0 = bf16 out with activation, 1 = fp32 out with activation, 2 = fp32 out += (residual).
 // tile_n: 64, 128 or 256 (0 = choose). `status` is one device int that a CTA sets to

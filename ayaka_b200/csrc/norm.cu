@@ -12,6 +12,8 @@ __global__ void layer_norm_kernel(const float* __restrict__ x, int ld_x,
                                   const float* __restrict__ beta, float eps,
                                   TOut* __restrict__ out, int ld_out, int width) {
   __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* src = x + (size_t)(rows != nullptr ? rows[r] : r) * ld_x;
   float s = 0.f;
@@ -40,12 +42,13 @@ int layer_norm(const float* x, int ld_x, const int* rows, const float* gamma, co
     return AYK_BAD_ARGUMENT;
   }
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-  layer_norm_kernel<TOut><<<n, threads, 0, stream>>>(x, ld_x, rows, gamma, beta, eps,
-                                                      (TOut*)out, ld_out, width);
-  return launch_status();
+  return launch_kernel(layer_norm_kernel<TOut>, dim3(n), dim3(threads), 0, stream, 1, x, ld_x,
+                       rows, gamma, beta, eps, (TOut*)out, ld_out, width);
 }
 
 }  // namespace ayk
+
+AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
 
 AYK_API int ayk_layer_norm_f32(const float* x, int ld_x, const int* rows, const float* gamma,
                                const float* beta, float eps, void* out, int ld_out, int n,

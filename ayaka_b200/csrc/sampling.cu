@@ -57,6 +57,8 @@ __global__ void __launch_bounds__(256)
 argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out) {
   __shared__ float sv[8];
   __shared__ int si[8];
+  pdl_launch_dependents();
+  pdl_wait();
   const int best = block_argmax(logits + (size_t)blockIdx.x * ld, vocab, sv, si);
   if (threadIdx.x == 0) out[blockIdx.x] = best;
 }
@@ -267,6 +269,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
               int* __restrict__ out) {
   extern __shared__ __align__(16) unsigned char sample_smem[];
   SampleShared& sh = *reinterpret_cast<SampleShared*>(sample_smem);
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * ld;
   const float temp = temperature[r];
@@ -356,11 +360,13 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
 
 }  // namespace ayk
 
+AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
+
 AYK_API int ayk_argmax(const float* logits, int ld, int rows, int vocab, int* out, void* stream) {
   if (rows == 0) return AYK_OK;
   if (rows < 0 || vocab < 1 || ld < vocab) return AYK_BAD_ARGUMENT;
-  ayk::argmax_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(logits, ld, vocab, out);
-  return ayk::launch_status();
+  return ayk::launch_kernel(ayk::argmax_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream,
+                            1, logits, ld, vocab, out);
 }
 
 // temperature [rows] fp32; top_k [rows] int32 (<= 0: off) or null; top_p, min_p [rows] fp32 or
@@ -382,7 +388,7 @@ AYK_API int ayk_sample(const float* logits, int ld, int rows, int vocab, const f
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  ayk::sample_kernel<<<rows, ayk::SMP_THREADS, bytes, (cudaStream_t)stream>>>(
-      logits, ld, vocab, temperature, top_k, top_p, min_p, seeds, positions, out);
-  return ayk::launch_status();
+  return ayk::launch_kernel(ayk::sample_kernel, dim3(rows), dim3(ayk::SMP_THREADS), bytes,
+                            (cudaStream_t)stream, 1, logits, ld, vocab, temperature, top_k,
+                            top_p, min_p, seeds, positions, out);
 }

@@ -27,6 +27,7 @@ __all__ = [
     "layer_norm",
     "linear",
     "sample",
+    "set_pdl",
 ]
 
 ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2}
@@ -38,6 +39,15 @@ BF16_GEMM = "tcgen05"
 
 
 _launches = 0
+
+
+def set_pdl(enabled: bool) -> None:
+    """Switch programmatic dependent launch on or off in every library (it is on by default;
+    measurements switch it off to see what it buys). Graphs captured earlier keep their edges."""
+    from ayaka_b200.kernels.build import library_names
+
+    for name in library_names():
+        library(name).ayk_set_pdl(c_int(1 if enabled else 0))
 
 
 def launch_count() -> int:
