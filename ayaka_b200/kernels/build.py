@@ -49,9 +49,19 @@ def _nvcc() -> str | None:
     return None
 
 
-def _digest(name: str) -> str:
+#: Libraries compiled once per value of a macro, and the values :func:`build_all` prepares.
+VARIANTS: dict[str, tuple[str, tuple[int, ...]]] = {
+    "attention_prefill": ("AYK_HEAD_DIM", (16, 32, 48, 64, 128)),
+}
+
+
+def _defines(defines: dict[str, int] | None) -> list[str]:
+    return [f"-D{key}={value}" for key, value in sorted((defines or {}).items())]
+
+
+def _digest(name: str, defines: dict[str, int] | None = None) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(_FLAGS).encode())
+    h.update(" ".join([*_FLAGS, *_defines(defines)]).encode())
     h.update((CSRC / f"{name}.cu").read_bytes())
     for header in sorted(CSRC.glob("*.cuh")):
         h.update(header.name.encode())
@@ -81,7 +91,8 @@ def _say(text: str) -> None:
     print(f"ayaka_b200: {text}", file=sys.stderr, flush=True)
 
 
-def _compile(name: str, filename: str, verbose: bool) -> Path:
+def _compile(name: str, filename: str, verbose: bool,
+             defines: dict[str, int] | None = None) -> Path:
     nvcc = _nvcc()
     if nvcc is None:
         raise BackendError(
@@ -90,9 +101,11 @@ def _compile(name: str, filename: str, verbose: bool) -> Path:
     folder = _writable_build_dir()
     target = folder / filename
     partial = folder / f".{filename}.{os.getpid()}.{threading.get_ident()}.tmp"
-    command = [nvcc, *_FLAGS, "-I", str(CSRC), "-o", str(partial), str(CSRC / f"{name}.cu")]
+    command = [nvcc, *_FLAGS, *_defines(defines), "-I", str(CSRC), "-o", str(partial),
+               str(CSRC / f"{name}.cu")]
+    label = name + "".join(f" {d[2:]}" for d in _defines(defines))
     if verbose:
-        _say(f"compiling {name}.cu for sm_100a ...")
+        _say(f"compiling {label}.cu for sm_100a ...")
     started = time.monotonic()
     process = subprocess.Popen(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
                                text=True, cwd=str(folder))
@@ -110,30 +123,45 @@ def _compile(name: str, filename: str, verbose: bool) -> Path:
         partial.unlink(missing_ok=True)
         raise BackendError(f"nvcc failed on {name}.cu:\n{output}")
     os.replace(partial, target)
-    for stale in folder.glob(f"libayk_{name}.*.so"):
-        if stale != target:
+    tag = _tag(defines)
+    for stale in folder.glob(f"libayk_{name}{tag}.*.so"):
+        if stale != target and stale.name.count(".") == target.name.count("."):
             stale.unlink(missing_ok=True)
     if verbose:
-        _say(f"compiled {name}.cu in {time.monotonic() - started:.1f} s")
+        _say(f"compiled {label}.cu in {time.monotonic() - started:.1f} s")
     return target
 
 
-def ensure_built(name: str, *, verbose: bool = True) -> Path:
-    """Return the path of the shared library of ``csrc/<name>.cu``, compiling it if needed."""
+def _tag(defines: dict[str, int] | None) -> str:
+    return "".join(f"-{key.lower()}{value}" for key, value in sorted((defines or {}).items()))
+
+
+def ensure_built(name: str, *, verbose: bool = True,
+                 defines: dict[str, int] | None = None) -> Path:
+    """Return the path of the shared library of ``csrc/<name>.cu`` (compiled with the given
+    macro definitions), compiling it if needed."""
     if not (CSRC / f"{name}.cu").is_file():
         raise BackendError(f"no CUDA source {CSRC / (name + '.cu')}")
+    key = name + _tag(defines)
     with _locks_guard:
-        lock = _locks.setdefault(name, threading.Lock())
+        lock = _locks.setdefault(key, threading.Lock())
     with lock:
-        filename = f"libayk_{name}.{_digest(name)}.so"
+        filename = f"libayk_{key}.{_digest(name, defines)}.so"
         for folder in (CSRC / "_build", _fallback_dir()):
             if (folder / filename).is_file():
                 return folder / filename
-        return _compile(name, filename, verbose)
+        return _compile(name, filename, verbose, defines)
 
 
 def build_all(*, verbose: bool = True) -> list[Path]:
     """Compile every library, several nvcc processes at a time, and return their paths."""
-    names = library_names()
-    with ThreadPoolExecutor(max_workers=max(1, min(os.cpu_count() or 1, len(names)))) as pool:
-        return list(pool.map(lambda name: ensure_built(name, verbose=verbose), names))
+    jobs: list[tuple[str, dict[str, int] | None]] = []
+    for name in library_names():
+        if name in VARIANTS:
+            macro, values = VARIANTS[name]
+            jobs.extend((name, {macro: value}) for value in values)
+        else:
+            jobs.append((name, None))
+    with ThreadPoolExecutor(max_workers=max(1, min(os.cpu_count() or 1, len(jobs)))) as pool:
+        return list(pool.map(
+            lambda job: ensure_built(job[0], verbose=verbose, defines=job[1]), jobs))

@@ -8,7 +8,7 @@ import threading
 from ayaka_b200.errors import BackendError
 from ayaka_b200.kernels.build import ensure_built
 
-__all__ = ["check", "library", "loaded_libraries"]
+__all__ = ["check", "library", "loaded_libraries", "set_pdl"]
 
 _REFUSALS = {
     -1: "an argument the kernel does not take (a size, a stride or a missing pointer)",
@@ -19,19 +19,34 @@ _REFUSALS = {
 }
 _libraries: dict[str, ctypes.CDLL] = {}
 _guard = threading.Lock()
+_pdl = True
 
 
-def library(name: str) -> ctypes.CDLL:
-    """The shared library built from ``csrc/<name>.cu``; built on first use, loaded once."""
+def set_pdl(enabled: bool) -> None:
+    """Programmatic dependent launch on or off, in the libraries loaded so far and in those
+    loaded later."""
+    global _pdl
     with _guard:
-        found = _libraries.get(name)
+        _pdl = bool(enabled)
+        for found in _libraries.values():
+            found.ayk_set_pdl(ctypes.c_int(1 if _pdl else 0))
+
+
+def library(name: str, **defines: int) -> ctypes.CDLL:
+    """The shared library built from ``csrc/<name>.cu`` (with the given macro definitions);
+    built on first use, loaded once."""
+    key = name + "".join(f"-{k}{v}" for k, v in sorted(defines.items()))
+    with _guard:
+        found = _libraries.get(key)
         if found is None:
-            path = ensure_built(name)
+            path = ensure_built(name, defines=defines or None)
             try:
                 found = ctypes.CDLL(str(path))
             except OSError as error:
                 raise BackendError(f"cannot load {path}: {error}") from None
-            _libraries[name] = found
+            if not _pdl:
+                found.ayk_set_pdl(ctypes.c_int(0))
+            _libraries[key] = found
         return found
 
 

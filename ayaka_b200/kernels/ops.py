@@ -20,6 +20,7 @@ __all__ = [
     "argmax",
     "attention",
     "attention_decode",
+    "attention_prefill",
     "decode_splits",
     "embed_rows",
     "kv_store",
@@ -44,10 +45,9 @@ _launches = 0
 def set_pdl(enabled: bool) -> None:
     """Switch programmatic dependent launch on or off in every library (it is on by default;
     measurements switch it off to see what it buys). Graphs captured earlier keep their edges."""
-    from ayaka_b200.kernels.build import library_names
+    from ayaka_b200.kernels import lib
 
-    for name in library_names():
-        library(name).ayk_set_pdl(c_int(1 if enabled else 0))
+    lib.set_pdl(enabled)
 
 
 def launch_count() -> int:
@@ -256,6 +256,44 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                 c_int(out.stride(0)), c_int(n), c_int(num_heads), c_int(kv_heads),
                 c_int(head_dim), c_int(page_size), c_float(scale), c_int(window),
                 c_int(_TYPE[q.dtype]), _stream())
+    check(status, op)
+
+
+def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      block_table: torch.Tensor, row_start: torch.Tensor, kv_len: torch.Tensor,
+                      out: torch.Tensor, *, num_heads: int, scale: float, host_rows: list[int],
+                      window: int = 0) -> None:
+    """Causal attention of prompt portions in bfloat16 on the tensor cores.
+
+    Request ``b`` owns rows ``row_start[b] .. row_start[b + 1]`` of ``q`` and ``out``, which
+    are the last rows of its ``kv_len[b]`` cached tokens; ``host_rows`` is the host copy of
+    the row counts (the grid is sized from it). The library is compiled for the head size.
+    """
+    op = "attention_prefill"
+    _need(op, "q", q, torch.bfloat16, 2)
+    _need(op, "out", out, torch.bfloat16, 2)
+    _need(op, "k_pages", k_pages, torch.bfloat16, 4)
+    _need(op, "v_pages", v_pages, torch.bfloat16, 4)
+    _need(op, "block_table", block_table, torch.int32, 2)
+    _need(op, "row_start", row_start, torch.int32, 1)
+    _need(op, "kv_len", kv_len, torch.int32, 1)
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous():
+        raise BackendError(f"{op}: contiguous pages only")
+    _, kv_heads, page_size, head_dim = k_pages.shape
+    count = len(host_rows)
+    if q.shape[1] != num_heads * head_dim or out.shape[1] != q.shape[1] or \
+            row_start.shape[0] < count + 1 or kv_len.shape[0] < count or \
+            block_table.shape[0] < count or v_pages.shape != k_pages.shape:
+        raise BackendError(f"{op}: shapes do not fit")
+    if head_dim % 16 or not 16 <= head_dim <= 256:
+        raise BackendError(f"{op}: head_dim must be a multiple of 16 in [16, 256]")
+    tiles = sum(-(-rows // 64) for rows in host_rows)
+    fn = library("attention_prefill", AYK_HEAD_DIM=head_dim).ayk_attention_prefill
+    status = fn(_ptr(q), c_int(q.stride(0)), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                c_int(block_table.stride(0)), _ptr(row_start), _ptr(kv_len), _ptr(out),
+                c_int(out.stride(0)), c_int(count), c_int(tiles), c_int(num_heads),
+                c_int(kv_heads), c_int(head_dim), c_int(page_size), c_float(scale),
+                c_int(window), _stream())
     check(status, op)
 
 

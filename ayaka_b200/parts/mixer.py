@@ -106,6 +106,12 @@ class Attention(Mixer):
                                  step.request_of_row, step.positions, attended,
                                  num_heads=self.num_heads, scale=self.scale, window=self.window,
                                  rows=n, splits=splits, partial=partial, tickets=tickets)
+        elif self.ctx.dtype == torch.bfloat16:
+            # prompt portions (and any single rows beside them): tensor-core flash attention
+            ops.attention_prefill(q, cache.k_pages, cache.v_pages, group.block_table,
+                                  step.row_start, step.kv_len, attended,
+                                  num_heads=self.num_heads, scale=self.scale,
+                                  host_rows=step.host_rows, window=self.window)
         else:
             ops.attention(q, cache.k_pages, cache.v_pages, group.block_table,
                           step.request_of_row, step.positions, attended,

@@ -356,6 +356,40 @@ def test_kv_store_then_attend(dtype):
     assert torch.equal(out[3].float(), torch.zeros(width, device=DEV))
 
 
+@pytest.mark.parametrize("case", ATTN_CASES + [
+    ((1024, 1024), (1024, 1024), 25, 25, 64, 16, 0),
+    ((700, 3, 200), (130, 3, 65), 4, 2, 32, 16, 0),
+    ((500,), (250,), 2, 2, 64, 128, 100),
+])
+def test_attention_prefill_tensor_cores(case):
+    """The bfloat16 flash kernel for prompt portions: tiles of 64 rows, every head size class,
+    grouped heads, windows, requests of one row beside long ones, pages in scrambled order."""
+    ops = _ops()
+    lengths, rows, heads, kv_heads, head_dim, page, window = case
+    if head_dim % 16:
+        pytest.skip("head sizes are multiples of 16")
+    q, k_pages, v_pages, table, req, pos, seqs = _paged_case(
+        lengths, rows, heads, kv_heads, head_dim, page, torch.bfloat16, seed=25, boost=(699, 3))
+    n = q.shape[0]
+    starts = [0]
+    for r in rows:
+        starts.append(starts[-1] + r)
+    row_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+    kv_len = torch.tensor(lengths, dtype=torch.int32, device=DEV)
+    out = torch.full((n + 2, heads * head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+    scale = 0.7 / math.sqrt(head_dim)
+    ops.attention_prefill(q, k_pages, v_pages, table, row_start, kv_len, out, num_heads=heads,
+                          scale=scale, host_rows=list(rows), window=window)
+    expected = _attention_reference(seqs, lengths, rows, heads, kv_heads, scale, window)
+    torch.testing.assert_close(out[:n].double().cpu(), expected, rtol=2e-2, atol=2e-2)
+    assert torch.isnan(out[n:].float()).all()
+    # the plain CUDA-core kernel agrees far more closely than either agrees with float64
+    plain_out = torch.zeros(n, heads * head_dim, dtype=torch.bfloat16, device=DEV)
+    ops.attention(q, k_pages, v_pages, table, req, pos, plain_out, num_heads=heads, scale=scale,
+                  window=window)
+    torch.testing.assert_close(out[:n].float(), plain_out.float(), rtol=2e-2, atol=1e-2)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("splits", [1, 2, 5, 16])
 @pytest.mark.parametrize("case", [
