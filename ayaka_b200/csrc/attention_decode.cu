@@ -22,6 +22,10 @@ constexpr int DEC_UNROLL = 4;
 
 template <typename T> struct Frag8;
 template <> struct Frag8<float> {
+  static __device__ __forceinline__ void copy(float* dst, const float* src) {
+    *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+    *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(src + 4);
+  }
   static __device__ __forceinline__ void load(const float* p, float* v) {
     const float4 a = __ldg(reinterpret_cast<const float4*>(p));
     const float4 b = __ldg(reinterpret_cast<const float4*>(p + 4));
@@ -30,6 +34,9 @@ template <> struct Frag8<float> {
   }
 };
 template <> struct Frag8<__nv_bfloat16> {
+  static __device__ __forceinline__ void copy(__nv_bfloat16* dst, const __nv_bfloat16* src) {
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+  }
   static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
     const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -60,7 +67,9 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
                         int table_stride, const int* __restrict__ request_of_row,
                         const int* __restrict__ positions, T* __restrict__ out, int ld_out,
                         int num_kv_heads, int group, int head_dim, int page_size, float scale,
-                        int window, float* __restrict__ partial, int* __restrict__ tickets) {
+                        int window, float* __restrict__ partial, int* __restrict__ tickets,
+                        const T* __restrict__ k_new, const T* __restrict__ v_new, int ld_new,
+                        T* __restrict__ k_store, T* __restrict__ v_store) {
   constexpr int KEYS_PER_PASS = DEC_THREADS / TPK;
   __shared__ float s_m[DEC_THREADS / 32][TPK], s_l[DEC_THREADS / 32][TPK];
   __shared__ float s_acc[DEC_THREADS / 32][TPK][8];
@@ -117,8 +126,20 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
         const int page = table[key / page_size];
         const size_t off = (((size_t)page * num_kv_heads + kv_head) * page_size +
                             key % page_size) * head_dim + sub * 8;
-        Frag8<T>::load(k_pages + off, kf[u]);
-        Frag8<T>::load(v_pages + off, vf[u]);
+        if (k_new != nullptr && key == pos) {
+          // the row's own key and value come straight from this step's projection; the first
+          // head of each group also puts them into the cache (the fused KV store)
+          const size_t src = (size_t)row * ld_new + (size_t)kv_head * head_dim + sub * 8;
+          Frag8<T>::load(k_new + src, kf[u]);
+          Frag8<T>::load(v_new + src, vf[u]);
+          if (k_store != nullptr && head % group == 0) {
+            Frag8<T>::copy(k_store + off, k_new + src);
+            Frag8<T>::copy(v_store + off, v_new + src);
+          }
+        } else {
+          Frag8<T>::load(k_pages + off, kf[u]);
+          Frag8<T>::load(v_pages + off, vf[u]);
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) { kf[u][i] = 0.f; vf[u][i] = 0.f; }
@@ -217,13 +238,16 @@ int launch_decode(const void* q, int ld_q, const void* k_pages, const void* v_pa
                   const int* block_table, int table_stride, const int* request_of_row,
                   const int* positions, void* out, int ld_out, int num_rows, int num_heads,
                   int num_kv_heads, int head_dim, int page_size, float scale, int window,
-                  int splits, float* partial, int* tickets, cudaStream_t stream) {
+                  int splits, float* partial, int* tickets, const void* k_new,
+                  const void* v_new, int ld_new, int store, cudaStream_t stream) {
   dim3 grid(splits, num_heads, num_rows);
   return launch_kernel(attention_decode_kernel<T, TPK>, grid, dim3(DEC_THREADS), 0, stream, 1,
                        (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table,
                        table_stride, request_of_row, positions, (T*)out, ld_out, num_kv_heads,
                        num_heads / num_kv_heads, head_dim, page_size, scale, window, partial,
-                       tickets);
+                       tickets, (const T*)k_new, (const T*)v_new, ld_new,
+                       store ? (T*)const_cast<void*>(k_pages) : (T*)nullptr,
+                       store ? (T*)const_cast<void*>(v_pages) : (T*)nullptr);
 }
 
 template <typename T>
@@ -231,8 +255,17 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
                      const int* block_table, int table_stride, const int* request_of_row,
                      const int* positions, void* out, int ld_out, int num_rows, int num_heads,
                      int num_kv_heads, int head_dim, int page_size, float scale, int window,
-                     int splits, float* partial, int* tickets, cudaStream_t stream) {
+                     int splits, float* partial, int* tickets, const void* k_new,
+                     const void* v_new, int ld_new, int store, cudaStream_t stream) {
   if (num_rows == 0) return AYK_OK;
+  if ((k_new == nullptr) != (v_new == nullptr) || (store && k_new == nullptr)) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (k_new != nullptr && (((uintptr_t)k_new % (8 * sizeof(T))) ||
+                           ((uintptr_t)v_new % (8 * sizeof(T))) ||
+                           ((size_t)ld_new * sizeof(T)) % (8 * sizeof(T)))) {
+    return AYK_BAD_ALIGNMENT;
+  }
   if (num_rows < 0 || num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads ||
       page_size < 1 || table_stride < 1 || window < 0 || splits < 1) {
     return AYK_BAD_ARGUMENT;
@@ -252,7 +285,7 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
   return launch_decode<T, TPK>(q, ld_q, k_pages, v_pages, block_table, table_stride,          \
                                request_of_row, positions, out, ld_out, num_rows, num_heads,   \
                                num_kv_heads, head_dim, page_size, scale, window, splits,      \
-                               partial, tickets, stream)
+                               partial, tickets, k_new, v_new, ld_new, store, stream)
   if (frags <= 2) AYK_DECODE(2);
   if (frags <= 4) AYK_DECODE(4);
   if (frags <= 8) AYK_DECODE(8);
@@ -267,25 +300,29 @@ AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
 
 // type: 0 = float32, 1 = bfloat16. `partial` holds num_rows * num_heads * splits *
 // (head_dim + 2) floats and `tickets` num_rows * num_heads zeroed ints (both unused when
-// splits == 1).
+// splits == 1). With k_new/v_new ([rows, kv_heads * head_dim], row stride ld_new) each row's
+// own key and value are read from there instead of the cache, and with `store` they are also
+// written into the row's cache slot (the step's KV store, fused).
 AYK_API int ayk_attention_decode(const void* q, int ld_q, const void* k_pages,
                                  const void* v_pages, const int* block_table, int table_stride,
                                  const int* request_of_row, const int* positions, void* out,
                                  int ld_out, int num_rows, int num_heads, int num_kv_heads,
                                  int head_dim, int page_size, float scale, int window,
-                                 int splits, float* partial, int* tickets, int type,
+                                 int splits, float* partial, int* tickets, const void* k_new,
+                                 const void* v_new, int ld_new, int store, int type,
                                  void* stream) {
   if (type == 0) {
     return ayk::attention_decode<float>(q, ld_q, k_pages, v_pages, block_table, table_stride,
                                         request_of_row, positions, out, ld_out, num_rows,
                                         num_heads, num_kv_heads, head_dim, page_size, scale,
-                                        window, splits, partial, tickets, (cudaStream_t)stream);
+                                        window, splits, partial, tickets, k_new, v_new, ld_new,
+                                        store, (cudaStream_t)stream);
   }
   if (type == 1) {
     return ayk::attention_decode<__nv_bfloat16>(
         q, ld_q, k_pages, v_pages, block_table, table_stride, request_of_row, positions, out,
         ld_out, num_rows, num_heads, num_kv_heads, head_dim, page_size, scale, window, splits,
-        partial, tickets, (cudaStream_t)stream);
+        partial, tickets, k_new, v_new, ld_new, store, (cudaStream_t)stream);
   }
   return AYK_BAD_ARGUMENT;
 }

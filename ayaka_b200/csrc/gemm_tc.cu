@@ -223,12 +223,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // r*MP/S .. (r+1)*MP/S over all peers through distributed shared memory in rank order 0..S-1
 // (a fixed order: the result does not change from run to run), applies the epilogue and
 // stores. Thread t owns output column n0 + t, so a warp's stores are contiguous.
-template <int MP, int STAGES>
+// With LN (the fused LayerNorm): the activation tile is not copied by TMA but computed by the
+// CTA from the fp32 residual stream — mean and variance of each row over the whole width,
+// then (x - mean) * rstd * gamma + beta for the CTA's own K range, rounded to bf16 and written
+// into shared memory in the same 128-byte-swizzled layout TMA would have produced. The
+// stages then hold weight tiles only, and the CTA's whole K range of activations (at most
+// MAXKB blocks of 64) stays resident.
+template <int MP, int STAGES, bool LN = false, int MAXKB = 0>
 struct SmallSmem {
   static constexpr int W_BYTES = TC_BM * TC_BK * 2;
   static constexpr int A_BYTES = MP * TC_BK * 2;
-  static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
-  static constexpr int PARTIAL_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int STAGE_BYTES = LN ? W_BYTES : W_BYTES + A_BYTES;
+  static constexpr int A_REGION_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int A_REGION_BYTES = LN ? MAXKB * A_BYTES : 0;
+  static constexpr int PARTIAL_OFFSET = A_REGION_OFFSET + A_REGION_BYTES;
   static constexpr int PARTIAL_BYTES = MP * TC_BM * 4;
   static constexpr int BAR_OFFSET = PARTIAL_OFFSET + PARTIAL_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16;
@@ -248,13 +256,22 @@ __device__ __forceinline__ void store_output(void* out, int ldo, int m, int n, f
   }
 }
 
-template <int MP, int STAGES>
+struct LnArgs {
+  const float* x;      // fp32 rows to normalise
+  int ld_x;
+  const int* rows;     // row m of the product normalises x[rows[m]] (null: x[m])
+  const float* gamma;
+  const float* beta;   // may be null
+  float eps;
+};
+
+template <int MP, int STAGES, bool LN, int MAXKB>
 __global__ void __launch_bounds__(128)
 gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
                      const __grid_constant__ CUtensorMap map_a, const float* __restrict__ bias,
                      void* __restrict__ out, int ldo, int M, int N, int K, int act, int mode,
-                     int kb_per_split, int* __restrict__ status) {
-  using L = SmallSmem<MP, STAGES>;
+                     int kb_per_split, int* __restrict__ status, LnArgs ln) {
+  using L = SmallSmem<MP, STAGES, LN, MAXKB>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
   float* partial = reinterpret_cast<float*>(smem + L::PARTIAL_OFFSET);
@@ -304,22 +321,99 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
       mbar_expect_tx(&full[i], L::STAGE_BYTES);
       tma_load_2d(w_tile, &map_w, &full[i], (kb_lo + i) * TC_BK, n0);
     }
-    pdl_wait();
-    for (int i = 0; i < my_kb; ++i) {
-      const int s = i % STAGES;
-      uint8_t* w_tile = smem + s * L::STAGE_BYTES;
-      if (i >= STAGES) {
-        if (!mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) {
-          *failed = 1;
-          break;
+    if (!LN) {
+      pdl_wait();
+      for (int i = 0; i < my_kb; ++i) {
+        const int s = i % STAGES;
+        uint8_t* w_tile = smem + s * L::STAGE_BYTES;
+        if (i >= STAGES) {
+          if (!mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) {
+            *failed = 1;
+            break;
+          }
+          mbar_expect_tx(&full[s], L::STAGE_BYTES);
+          tma_load_2d(w_tile, &map_w, &full[s], (kb_lo + i) * TC_BK, n0);
         }
-        mbar_expect_tx(&full[s], L::STAGE_BYTES);
-        tma_load_2d(w_tile, &map_w, &full[s], (kb_lo + i) * TC_BK, n0);
+        tma_load_2d(w_tile + L::W_BYTES, &map_a, &full[s], (kb_lo + i) * TC_BK, 0);
+        issued = i + 1;
       }
-      tma_load_2d(w_tile + L::W_BYTES, &map_a, &full[s], (kb_lo + i) * TC_BK, 0);
+    } else {
+      issued = ahead;
+    }
+  }
+  if (LN) {
+    // every thread: wait for the kernel ahead, then normalise this CTA's K range into shared
+    pdl_wait();
+    uint8_t* a_region = smem + L::A_REGION_OFFSET;
+    const int k_lo = kb_lo * TC_BK;
+    const int k_hi = kb_hi * TC_BK;  // may pass K: the tail is zero-filled
+    for (int m = warp; m < M; m += 4) {
+      const float* src = ln.x + (size_t)(ln.rows != nullptr ? ln.rows[m] : m) * ln.ld_x;
+      float sum = 0.f;
+      for (int c = lane * 4; c < K; c += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(src + c);
+        sum += (v.x + v.y) + (v.z + v.w);
+      }
+      const float mean = warp_sum(sum) / (float)K;
+      float sq = 0.f;
+      for (int c = lane * 4; c < K; c += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(src + c);
+        const float a = v.x - mean, b = v.y - mean, cc = v.z - mean, d = v.w - mean;
+        sq += (a * a + b * b) + (cc * cc + d * d);
+      }
+      const float rstd = rsqrtf(warp_sum(sq) / (float)K + ln.eps);
+      // one 16-byte chunk (8 elements) per lane and pass
+      for (int k = k_lo + lane * 8; k < k_hi; k += 256) {
+        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+        if (k < K) {
+          float v[8];
+          const float4 x0 = *reinterpret_cast<const float4*>(src + k);
+          const float4 x1 = *reinterpret_cast<const float4*>(src + k + 4);
+          const float4 g0 = __ldg(reinterpret_cast<const float4*>(ln.gamma + k));
+          const float4 g1 = __ldg(reinterpret_cast<const float4*>(ln.gamma + k + 4));
+          v[0] = (x0.x - mean) * rstd * g0.x; v[1] = (x0.y - mean) * rstd * g0.y;
+          v[2] = (x0.z - mean) * rstd * g0.z; v[3] = (x0.w - mean) * rstd * g0.w;
+          v[4] = (x1.x - mean) * rstd * g1.x; v[5] = (x1.y - mean) * rstd * g1.y;
+          v[6] = (x1.z - mean) * rstd * g1.z; v[7] = (x1.w - mean) * rstd * g1.w;
+          if (ln.beta != nullptr) {
+            const float4 b0 = __ldg(reinterpret_cast<const float4*>(ln.beta + k));
+            const float4 b1 = __ldg(reinterpret_cast<const float4*>(ln.beta + k + 4));
+            v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+            v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+          }
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
+          __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
+          __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
+          packed.x = *reinterpret_cast<uint32_t*>(&h0);
+          packed.y = *reinterpret_cast<uint32_t*>(&h1);
+          packed.z = *reinterpret_cast<uint32_t*>(&h2);
+          packed.w = *reinterpret_cast<uint32_t*>(&h3);
+        }
+        const int local = k - k_lo;
+        const int kb = local / TC_BK, chunk = (local % TC_BK) / 8;
+        uint8_t* dst = a_region + kb * L::A_BYTES + m * 128 + ((chunk ^ (m & 7)) << 4);
+        *reinterpret_cast<uint4*>(dst) = packed;
+      }
+    }
+    // make the generic-proxy writes visible to the tensor core's (async proxy) reads
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+  }
+  if (LN && warp == 0 && lane == 0) {
+    // the rest of the weight tiles, as stages come free
+    for (int i = issued; i < my_kb; ++i) {
+      const int s = i % STAGES;
+      if (!mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) {
+        *failed = 1;
+        break;
+      }
+      mbar_expect_tx(&full[s], L::STAGE_BYTES);
+      tma_load_2d(smem + s * L::STAGE_BYTES, &map_w, &full[s], (kb_lo + i) * TC_BK, n0);
       issued = i + 1;
     }
-  } else if (warp == 1 && lane == 0) {
+  }
+  if (warp == 1 && lane == 0) {
     constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, MP);
     bool ok = true;
     for (int i = 0; i < my_kb; ++i) {
@@ -331,7 +425,8 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
       }
       tc_fence_after();
       const uint8_t* w_tile = smem + s * L::STAGE_BYTES;
-      const uint8_t* a_tile = w_tile + L::W_BYTES;
+      const uint8_t* a_tile = LN ? smem + L::A_REGION_OFFSET + i * L::A_BYTES
+                                 : w_tile + L::W_BYTES;
 #pragma unroll
       for (int k = 0; k < TC_BK / 16; ++k) {
         umma_f16(tmem_base, umma_desc_k128(w_tile, k * 32), umma_desc_k128(a_tile, k * 32),
@@ -482,19 +577,23 @@ int launch_gemm_tc(const void* a, int lda, const void* w, int ldw, const float* 
                        map_w, bias, out, ldo, M, N, K, act, mode, vec_ok, status);
 }
 
-template <int MP, int STAGES>
+template <int MP, int STAGES, bool LN, int MAXKB>
 int launch_gemm_tc_small(const void* a, int lda, const void* w, int ldw, const float* bias,
                          void* out, int ldo, int M, int N, int K, int act, int mode, int splits,
-                         int* status, cudaStream_t stream) {
-  using L = SmallSmem<MP, STAGES>;
+                         int* status, LnArgs ln, cudaStream_t stream) {
+  using L = SmallSmem<MP, STAGES, LN, MAXKB>;
   CUtensorMap map_a, map_w;
   int r = cached_map(w, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BM, &map_w);
   if (r != AYK_OK) return r;
-  r = cached_map(a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, MP, &map_a);
-  if (r != AYK_OK) return r;
+  if (LN) {
+    map_a = map_w;  // unused by the kernel
+  } else {
+    r = cached_map(a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, MP, &map_a);
+    if (r != AYK_OK) return r;
+  }
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_small_kernel<MP, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_small_kernel<MP, STAGES, LN, MAXKB>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYNAMIC);
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -502,10 +601,25 @@ int launch_gemm_tc_small(const void* a, int lda, const void* w, int ldw, const f
   const int num_kb = (K + TC_BK - 1) / TC_BK;
   if (splits < 1) splits = 1;
   while (splits > 1 && (splits > num_kb || splits > 8 || MP % splits)) splits >>= 1;
-  int kb_per_split = (num_kb + splits - 1) / splits;
-  return launch_kernel(gemm_tc_small_kernel<MP, STAGES>, dim3((N + TC_BM - 1) / TC_BM, splits, 1),
-                       dim3(128), L::DYNAMIC, stream, splits, map_w, map_a, bias, out, ldo, M, N,
-                       K, act, mode, kb_per_split, status);
+  if (LN) {  // the CTA's whole K range of activations must fit its shared-memory region
+    while (splits < 8 && (num_kb + splits - 1) / splits > MAXKB) splits <<= 1;
+    if ((num_kb + splits - 1) / splits > MAXKB || MP % splits) return AYK_TOO_LARGE;
+  }
+  const int kb_per_split = (num_kb + splits - 1) / splits;
+  return launch_kernel(gemm_tc_small_kernel<MP, STAGES, LN, MAXKB>,
+                       dim3((N + TC_BM - 1) / TC_BM, splits, 1), dim3(128), L::DYNAMIC, stream,
+                       splits, map_w, map_a, bias, out, ldo, M, N, K, act, mode, kb_per_split,
+                       status, ln);
+}
+
+inline int pick_splits(int tile_n, int N) {
+  // -1: choose; -2, -4, -8: that many K splits; -100: one split
+  if (tile_n == -100) return 1;
+  if (tile_n != -1) return -tile_n;
+  const int tiles = (N + TC_BM - 1) / TC_BM;
+  int splits = 1;
+  while (splits < 8 && tiles * splits * 2 <= 296) splits <<= 1;
+  return splits;
 }
 
 }  // namespace ayk
@@ -534,25 +648,20 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
   if (tile_n == 0 && M <= 64) tile_n = -1;  // few rows: the weight-streaming kernel
   if (tile_n < 0) {
     if (M > 64) return AYK_BAD_ARGUMENT;
-    int splits = -tile_n;  // -1: choose; -2, -4, -8: that many K splits; -100: one split
-    if (tile_n == -100) splits = 1;
-    if (tile_n == -1) {
-      const int tiles = (N + TC_BM - 1) / TC_BM;
-      splits = 1;
-      while (splits < 8 && tiles * splits * 2 <= 296) splits <<= 1;
-    }
+    const int splits = pick_splits(tile_n, N);
+    const LnArgs none = {nullptr, 0, nullptr, nullptr, nullptr, 0.f};
     if (M <= 16) {
-      return launch_gemm_tc_small<16, 5>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
-                                         splits, status, s);
+      return launch_gemm_tc_small<16, 5, false, 0>(a, lda, w, ldw, bias, out, ldo, M, N, K, act,
+                                                   mode, splits, status, none, s);
     }
     if (M <= 32) {
-      return launch_gemm_tc_small<32, 5>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
-                                         splits, status, s);
+      return launch_gemm_tc_small<32, 5, false, 0>(a, lda, w, ldw, bias, out, ldo, M, N, K, act,
+                                                   mode, splits, status, none, s);
     }
-    return launch_gemm_tc_small<64, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
-                                       splits, status, s);
+    return launch_gemm_tc_small<64, 4, false, 0>(a, lda, w, ldw, bias, out, ldo, M, N, K, act,
+                                                 mode, splits, status, none, s);
   }
-  if (tile_n == 0) tile_n = 128;
+  if (tile_n == 0) tile_n = 256;  // measured best at GPT-2 XL's shapes (fewest smem bytes per flop)
   switch (tile_n) {
     case 64:
       return launch_gemm_tc<64, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
@@ -563,4 +672,42 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
     default:
       return AYK_BAD_ARGUMENT;
   }
+}
+
+// The same product for at most 64 rows with the LayerNorm of the input fused in:
+// out = act(LayerNorm(x[rows]) @ W^T + bias). x is the fp32 residual stream (row stride ld_x, a
+// multiple of 4), rows an optional gather index, gamma/beta fp32 [K]. K must be a multiple of
+// 8 and at most 8 * MAXKB * 64 for the row class (AYK_TOO_LARGE otherwise: run the norm as its
+// own kernel). splits: 0 = choose, else the number of K splits (1, 2, 4 or 8).
+AYK_API int ayk_gemm_bf16_tc_ln(const float* x, int ld_x, const int* rows, const float* gamma,
+                                const float* beta, float eps, const void* w, int ldw,
+                                const float* bias, void* out, int ldo, int M, int N, int K,
+                                int act, int mode, int splits, int* status, void* stream) {
+  using namespace ayk;
+  if (M == 0 || N == 0) return AYK_OK;
+  if (M < 0 || M > 64 || N < 0 || K < 1 || ld_x < K || ldw < K || ldo < N || status == nullptr ||
+      x == nullptr || gamma == nullptr || !(eps > 0.f)) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (mode < OUT_BF16 || mode > OUT_RESIDUAL_F32 || act < ACT_NONE || act > ACT_GELU_ERF ||
+      (mode == OUT_RESIDUAL_F32 && act != ACT_NONE)) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (((uintptr_t)w % 16) || (ldw % 8) || (K % 8) || ((uintptr_t)x % 16) || (ld_x % 4) ||
+      ((uintptr_t)gamma % 16) || ((uintptr_t)beta % 16)) {
+    return AYK_BAD_ALIGNMENT;
+  }
+  const LnArgs ln = {x, ld_x, rows, gamma, beta, eps};
+  const int want = splits > 0 ? splits : pick_splits(-1, N);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (M <= 16) {
+    return launch_gemm_tc_small<16, 4, true, 13>(nullptr, 0, w, ldw, bias, out, ldo, M, N, K, act,
+                                                 mode, want, status, ln, s);
+  }
+  if (M <= 32) {
+    return launch_gemm_tc_small<32, 4, true, 13>(nullptr, 0, w, ldw, bias, out, ldo, M, N, K, act,
+                                                 mode, want, status, ln, s);
+  }
+  return launch_gemm_tc_small<64, 4, true, 7>(nullptr, 0, w, ldw, bias, out, ldo, M, N, K, act,
+                                              mode, want, status, ln, s);
 }

@@ -27,6 +27,7 @@ __all__ = [
     "launch_count",
     "layer_norm",
     "linear",
+    "linear_normed",
     "sample",
     "set_pdl",
 ]
@@ -195,6 +196,36 @@ def linear(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out
     check(status, op)
 
 
+def linear_normed(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor | None, eps: float,
+                  weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, *,
+                  scratch: torch.Tensor, count: int, activation: str = "none",
+                  row_index: torch.Tensor | None = None) -> None:
+    """``out = act(LayerNorm(x) @ weight.T + bias)`` for ``count`` rows (``x[row_index]`` with
+    a gather index). With bfloat16 weights and at most 64 rows the norm is computed inside the
+    matrix product's kernel; otherwise it runs first, into ``scratch`` (``[>= count, K]`` in
+    the weight's dtype), and the product follows. Same arithmetic either way: statistics and
+    the affine map in fp32, one rounding to the weight's dtype."""
+    op = "linear_normed"
+    if activation not in ACTIVATIONS:
+        raise BackendError(f"{op}: unknown activation {activation!r}")
+    if weight.dtype == torch.bfloat16 and BF16_GEMM == "tcgen05":
+        from ayaka_b200.kernels import gemm_tc
+
+        _need(op, "x", x, torch.float32, 2)
+        _need(op, "weight", weight, torch.bfloat16, 2)
+        _need(op, "out", out, ndim=2)
+        if gemm_tc.can_fuse_norm(x, weight, gamma, beta, count):
+            n, k = weight.shape
+            if x.shape[1] != k or out.shape[1] != n or out.shape[0] < count or \
+                    gamma.shape[0] != k or (bias is not None and bias.shape[0] != n):
+                raise BackendError(f"{op}: shapes do not fit")
+            gemm_tc.linear_normed_bf16(x, gamma, beta, eps, weight, bias, out, count,
+                                       ACTIVATIONS[activation], row_index)
+            return
+    layer_norm(x, gamma, beta, eps, scratch, rows=row_index, count=count)
+    linear(scratch, weight, bias, out, activation=activation, rows=count)
+
+
 def kv_store(k: torch.Tensor, v: torch.Tensor, slot_mapping: torch.Tensor,
              k_pages: torch.Tensor, v_pages: torch.Tensor, *, rows: int | None = None) -> None:
     """Write this step's key and value rows ``[N, kv_heads * head_dim]`` into the pages.
@@ -309,11 +340,15 @@ def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
                      positions: torch.Tensor, out: torch.Tensor, *, num_heads: int, scale: float,
                      window: int = 0, rows: int | None = None, splits: int = 1,
                      partial: torch.Tensor | None = None,
-                     tickets: torch.Tensor | None = None) -> None:
+                     tickets: torch.Tensor | None = None, k_new: torch.Tensor | None = None,
+                     v_new: torch.Tensor | None = None, store: bool = False) -> None:
     """Attention for steps whose every request brings one row (same contract as
     :func:`attention`). ``splits`` CTAs share each (request, head); with more than one,
     ``partial`` (float32, at least rows * heads * splits * (head_dim + 2)) and ``tickets``
-    (int32 zeros, at least rows * heads; left zero) are scratch."""
+    (int32 zeros, at least rows * heads; left zero) are scratch. With ``k_new``/``v_new``
+    (``[rows, kv_heads * head_dim]``, column ranges of the projection output) each row's own
+    key and value are taken from there, and with ``store`` the kernel also writes them into
+    the row's cache slot, so no separate KV store runs."""
     op = "attention_decode"
     _need(op, "q", q, ndim=2)
     _need(op, "out", out, q.dtype, 2)
@@ -338,12 +373,24 @@ def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         if partial.numel() < n * num_heads * splits * (head_dim + 2) or \
                 tickets.numel() < n * num_heads:
             raise BackendError(f"{op}: the scratch buffers are too small")
+    if k_new is not None:
+        if v_new is None:
+            raise BackendError(f"{op}: k_new needs v_new")
+        _need(op, "k_new", k_new, q.dtype, 2)
+        _need(op, "v_new", v_new, q.dtype, 2)
+        if k_new.shape[1] != kv_heads * head_dim or v_new.shape != k_new.shape or \
+                k_new.stride(0) != v_new.stride(0) or k_new.shape[0] < n:
+            raise BackendError(f"{op}: k_new/v_new do not fit")
+    elif store:
+        raise BackendError(f"{op}: store needs k_new and v_new")
     status = library("attention_decode").ayk_attention_decode(
         _ptr(q), c_int(q.stride(0)), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
         c_int(block_table.stride(0)), _ptr(request_of_row), _ptr(positions), _ptr(out),
         c_int(out.stride(0)), c_int(n), c_int(num_heads), c_int(kv_heads), c_int(head_dim),
         c_int(page_size), c_float(scale), c_int(window), c_int(splits), _ptr(partial),
-        _ptr(tickets), c_int(_TYPE[q.dtype]), _stream())
+        _ptr(tickets), _ptr(k_new), _ptr(v_new),
+        c_int(0 if k_new is None else k_new.stride(0)), c_int(1 if store else 0),
+        c_int(_TYPE[q.dtype]), _stream())
     check(status, op)
 
 

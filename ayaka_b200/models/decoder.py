@@ -70,9 +70,15 @@ class DecoderModel(Part):
             return None
         chosen = step.workspace.buffer("model.head_in", spec.hidden_size, self.ctx.dtype,
                                        rows=num_want)
-        self.final_norm.forward(residual, chosen, count=num_want,  # type: ignore[attr-defined]
-                                rows=want_rows)
         logits = step.workspace.buffer("model.logits", spec.vocab_size, torch.float32,
                                        rows=num_want)
-        self.head.forward(chosen, logits, count=num_want)  # type: ignore[attr-defined]
+        from ayaka_b200.parts.norm import LayerNorm
+
+        if hasattr(self.head, "forward_normed") and type(self.final_norm) is LayerNorm:
+            self.head.forward_normed(self.final_norm, residual, want_rows,  # type: ignore
+                                     chosen, logits, count=num_want)
+        else:
+            self.final_norm.forward(residual, chosen, count=num_want,  # type: ignore
+                                    rows=want_rows)
+            self.head.forward(chosen, logits, count=num_want)  # type: ignore[attr-defined]
         return logits[:num_want]

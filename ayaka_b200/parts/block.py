@@ -44,7 +44,22 @@ class PreNormBlock(Block):
     def forward(self, residual: torch.Tensor, step: StepContext, cache: LayerCache) -> None:
         n = step.num_rows
         hidden = step.workspace.buffer("block.normed", self.width, self.ctx.dtype)
-        self.mixer_norm.forward(residual, hidden, count=n)  # type: ignore[attr-defined]
-        self.mixer.forward(hidden, residual, step, cache)  # type: ignore[attr-defined]
-        self.feed_forward_norm.forward(residual, hidden, count=n)  # type: ignore[attr-defined]
-        self.feed_forward.forward(hidden, residual, step)  # type: ignore[attr-defined]
+        # a part that can apply the norm itself gets the residual and the norm part
+        if hasattr(self.mixer, "forward_normed") and _plain_norm(self.mixer_norm):
+            self.mixer.forward_normed(self.mixer_norm, residual, step, cache)  # type: ignore
+        else:
+            self.mixer_norm.forward(residual, hidden, count=n)  # type: ignore[attr-defined]
+            self.mixer.forward(hidden, residual, step, cache)  # type: ignore[attr-defined]
+        if hasattr(self.feed_forward, "forward_normed") and _plain_norm(self.feed_forward_norm):
+            self.feed_forward.forward_normed(  # type: ignore[attr-defined]
+                self.feed_forward_norm, residual, step)
+        else:
+            self.feed_forward_norm.forward(residual, hidden, count=n)  # type: ignore
+            self.feed_forward.forward(hidden, residual, step)  # type: ignore[attr-defined]
+
+
+def _plain_norm(norm: Part) -> bool:
+    """Whether ``norm`` is the LayerNorm a fused kernel can apply from (weight, bias, eps)."""
+    from ayaka_b200.parts.norm import LayerNorm
+
+    return type(norm) is LayerNorm

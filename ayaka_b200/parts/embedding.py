@@ -102,3 +102,11 @@ class LinearHead(Part):
 
     def forward(self, hidden: torch.Tensor, logits: torch.Tensor, *, count: int) -> None:
         ops.linear(hidden, self.weight, None, logits, rows=count)
+
+    def forward_normed(self, norm: Part, residual: torch.Tensor, rows: torch.Tensor,
+                       scratch: torch.Tensor, logits: torch.Tensor, *, count: int) -> None:
+        """``logits = LayerNorm(residual[rows]) @ weight.T`` with the norm fused where the
+        kernel allows it."""
+        ops.linear_normed(residual, norm.weight, norm.bias, norm.eps,  # type: ignore
+                          self.weight, None, logits, scratch=scratch, count=count,
+                          row_index=rows)

@@ -14,7 +14,8 @@ __all__ = ["DenseMLP", "FeedForward"]
 
 class FeedForward(Part):
     """Interface of a feed-forward: read ``hidden`` (``[N, width]``, compute dtype) and **add**
-    the result to ``residual`` (fp32 ``[N, width]``) in place."""
+    the result to ``residual`` (fp32 ``[N, width]``) in place. Optional:
+    ``forward_normed(norm, residual, step)`` applies the norm itself (see ``Mixer``)."""
 
     def forward(self, hidden: torch.Tensor, residual: torch.Tensor, step: StepContext) -> None:
         raise NotImplementedError
@@ -47,4 +48,13 @@ class DenseMLP(FeedForward):
         inner = step.workspace.buffer("feed_forward.inner", self.inner, self.ctx.dtype)
         ops.linear(hidden, self.up_weight, self.up_bias, inner, activation=self.activation,
                    rows=n)
+        ops.linear(inner, self.down_weight, self.down_bias, residual, residual=True, rows=n)
+
+    def forward_normed(self, norm: Part, residual: torch.Tensor, step: StepContext) -> None:
+        n = step.num_rows
+        inner = step.workspace.buffer("feed_forward.inner", self.inner, self.ctx.dtype)
+        scratch = step.workspace.buffer("block.normed", self.width, self.ctx.dtype)
+        ops.linear_normed(residual, norm.weight, norm.bias, norm.eps,  # type: ignore
+                          self.up_weight, self.up_bias, inner, scratch=scratch, count=n,
+                          activation=self.activation)
         ops.linear(inner, self.down_weight, self.down_bias, residual, residual=True, rows=n)

@@ -20,6 +20,10 @@ class Mixer(Part):
     ``hidden`` (``[N, width]`` in the compute dtype: the normalised residual), and **adds**
     its result to ``residual`` (fp32 ``[N, width]``) in place. It may use ``cache`` as its
     needs say and ``step.workspace`` for scratch.
+
+    Optional: ``forward_normed(norm, residual, step, cache)`` — the same, but the part applies
+    ``norm`` (a norm part with ``weight``, ``bias``, ``eps``) to ``residual`` itself, which lets
+    it fuse the norm into its first kernel. A block calls it when the part has it.
     """
 
     def cache_need(self) -> CacheNeed | None:
@@ -77,17 +81,31 @@ class Attention(Mixer):
 
     def forward(self, hidden: torch.Tensor, residual: torch.Tensor, step: StepContext,
                 cache: LayerCache) -> None:
-        n = step.num_rows
-        group = step.groups[cache.group]  # type: ignore[index]
         qkv = step.workspace.buffer("attention.qkv", self.q_width + 2 * self.kv_width,
                                     self.ctx.dtype)
-        ops.linear(hidden, self.qkv_weight, self.qkv_bias, qkv, rows=n)
+        ops.linear(hidden, self.qkv_weight, self.qkv_bias, qkv, rows=step.num_rows)
+        self._attend(qkv, residual, step, cache)
+
+    def forward_normed(self, norm: Part, residual: torch.Tensor, step: StepContext,
+                       cache: LayerCache) -> None:
+        qkv = step.workspace.buffer("attention.qkv", self.q_width + 2 * self.kv_width,
+                                    self.ctx.dtype)
+        scratch = step.workspace.buffer("block.normed", self.width, self.ctx.dtype)
+        ops.linear_normed(residual, norm.weight, norm.bias, norm.eps,  # type: ignore
+                          self.qkv_weight, self.qkv_bias, qkv, scratch=scratch,
+                          count=step.num_rows)
+        self._attend(qkv, residual, step, cache)
+
+    def _attend(self, qkv: torch.Tensor, residual: torch.Tensor, step: StepContext,
+                cache: LayerCache) -> None:
+        n = step.num_rows
+        group = step.groups[cache.group]  # type: ignore[index]
         q = qkv[:, :self.q_width]
         k = qkv[:, self.q_width:self.q_width + self.kv_width]
         v = qkv[:, self.q_width + self.kv_width:]
         if self.position is not None:
             self.position.on_query_key(q, k, step)  # type: ignore[attr-defined]
-        if cache.writes:
+        if cache.writes and not step.decode_only:
             ops.kv_store(k, v, group.slot_mapping, cache.k_pages, cache.v_pages, rows=n)
         attended = step.workspace.buffer("attention.out", self.q_width, self.ctx.dtype)
         if step.decode_only:
@@ -105,7 +123,9 @@ class Attention(Mixer):
             ops.attention_decode(q, cache.k_pages, cache.v_pages, group.block_table,
                                  step.request_of_row, step.positions, attended,
                                  num_heads=self.num_heads, scale=self.scale, window=self.window,
-                                 rows=n, splits=splits, partial=partial, tickets=tickets)
+                                 rows=n, splits=splits, partial=partial, tickets=tickets,
+                                 k_new=k if cache.writes else None,
+                                 v_new=v if cache.writes else None, store=cache.writes)
         elif self.ctx.dtype == torch.bfloat16:
             # prompt portions (and any single rows beside them): tensor-core flash attention
             ops.attention_prefill(q, cache.k_pages, cache.v_pages, group.block_table,

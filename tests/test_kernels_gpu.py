@@ -179,6 +179,60 @@ def test_linear_tcgen05_few_rows(m, splits):
     gemm_tc.check_status(a.device)
 
 
+@pytest.mark.parametrize("m", [1, 8, 16, 20, 33, 64])
+@pytest.mark.parametrize("n,k", [(4800, 1600), (300, 96), (50257, 160), (136, 840)])
+def test_linear_with_fused_layer_norm(m, n, k):
+    """LayerNorm computed inside the few-rows matrix product: against float64, and against
+    the two-kernel path it replaces (same roundings: the results agree to the last bf16 bit
+    except where an fp32 sum lands on a rounding boundary)."""
+    ops = _ops()
+    from ayaka_b200.kernels import gemm_tc
+    x = _randn(m + 3, k, seed=40, scale=2.0) + 0.5
+    gamma, beta = _randn(k, seed=41) * 0.2 + 1.0, _randn(k, seed=42) * 0.3
+    w = _randn(n, k, seed=43, dtype=torch.bfloat16, scale=1 / math.sqrt(k))
+    bias = _randn(n, seed=44)
+    index = torch.arange(m + 2, 2, -1, dtype=torch.int32, device=DEV)  # rows m+2 .. 3
+    assert gemm_tc.can_fuse_norm(x, w, gamma, beta, m)
+    normed = plain.layer_norm(x.double()[index.long()], gamma.double(), beta.double(), 1e-5)
+    exact = normed.to(torch.bfloat16).double() @ w.double().t() + bias.double()
+    out = torch.full((m + 1, n), float("nan"), device=DEV)
+    scratch = torch.zeros(m, k, dtype=torch.bfloat16, device=DEV)
+    ops.linear_normed(x, gamma, beta, 1e-5, w, bias, out, scratch=scratch, count=m,
+                      row_index=index)
+    gemm_tc.check_status(x.device)
+    assert int(scratch.abs().sum()) == 0  # the fused path never touched the scratch
+    torch.testing.assert_close(out[:m].double(), exact, rtol=2e-3, atol=2e-3)
+    assert torch.isnan(out[m:]).all()
+    two = torch.zeros(m, n, device=DEV)
+    ops.layer_norm(x, gamma, beta, 1e-5, scratch, rows=index, count=m)
+    ops.linear(scratch, w, bias, two, rows=m)
+    torch.testing.assert_close(out[:m], two, rtol=2e-3, atol=2e-3)
+    half = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.linear_normed(x, gamma, None, 1e-5, w, bias, half, scratch=scratch, count=m,
+                      activation="gelu_tanh")
+    plain_normed = plain.layer_norm(x.double()[:m], gamma.double(), torch.zeros(k).double().to(DEV),
+                                    1e-5)
+    want = plain.gelu(plain_normed.to(torch.bfloat16).double() @ w.double().t() + bias.double(),
+                      "gelu_new")
+    torch.testing.assert_close(half.double(), want, rtol=2e-2, atol=2e-2)
+
+
+def test_linear_normed_falls_back_when_it_cannot_fuse():
+    ops = _ops()
+    # float32 weights, and more than 64 rows in bfloat16: the norm runs as its own kernel
+    for dtype, m in ((torch.float32, 9), (torch.bfloat16, 100)):
+        x = _randn(m, 96, seed=45)
+        gamma, beta = _randn(96, seed=46) + 1.0, _randn(96, seed=47)
+        w = _randn(40, 96, seed=48, dtype=dtype, scale=0.1)
+        out = torch.zeros(m, 40, device=DEV)
+        scratch = torch.zeros(m, 96, dtype=dtype, device=DEV)
+        ops.linear_normed(x, gamma, beta, 1e-6, w, None, out, scratch=scratch, count=m)
+        normed = plain.layer_norm(x.double(), gamma.double(), beta.double(), 1e-6)
+        assert float(scratch.float().abs().sum()) > 0
+        torch.testing.assert_close(out.double(), normed.to(dtype).double() @ w.double().t(),
+                                   rtol=1e-4, atol=1e-4)
+
+
 def test_linear_tcgen05_few_rows_is_reproducible():
     from ayaka_b200.kernels import gemm_tc
     a = _randn(8, 6400, seed=34, dtype=torch.bfloat16)
@@ -429,6 +483,29 @@ def test_attention_decode_split_kv(dtype, splits, case):
         torch.testing.assert_close(got, expected, **tol)
         assert torch.equal(out[1].float(), torch.zeros(heads * head_dim, device=DEV))
         assert int(tickets.abs().sum()) == 0
+    # the fused KV store: wipe each row's own slot in the cache, hand its key and value in
+    # from "this step's projection", and the kernel must both use and store them
+    kv_width = kv_heads * head_dim
+    k_new = torch.zeros(n + 1, kv_width, dtype=dtype, device=DEV)
+    v_new = torch.zeros_like(k_new)
+    wiped_k, wiped_v = k_pages.clone(), v_pages.clone()
+    at = 0
+    for b, length in enumerate(lengths):
+        row = at if at == 0 else at + 1  # the padding row sits at index 1
+        page, slot = int(table[b, (length - 1) // page]), (length - 1) % page
+        k_new[row] = k_pages[page, :, slot].reshape(-1)
+        v_new[row] = v_pages[page, :, slot].reshape(-1)
+        wiped_k[page, :, slot] = float("nan")
+        wiped_v[page, :, slot] = float("nan")
+        at += 1
+    out = torch.full((n + 1, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
+    ops.attention_decode(q, wiped_k, wiped_v, table, req, pos, out, num_heads=heads, scale=scale,
+                         window=window, splits=splits, partial=partial, tickets=tickets,
+                         k_new=k_new, v_new=v_new, store=True)
+    got = torch.cat([out[:1], out[2:]]).double().cpu()
+    torch.testing.assert_close(got, expected, **tol)
+    assert torch.equal(wiped_k.nan_to_num(7.0), k_pages.nan_to_num(7.0))
+    assert torch.equal(wiped_v.nan_to_num(7.0), v_pages.nan_to_num(7.0))
 
 
 def test_attention_refuses_what_it_cannot_do():
