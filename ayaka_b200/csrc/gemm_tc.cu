@@ -256,6 +256,8 @@ __device__ __forceinline__ void store_output(void* out, int ldo, int m, int n, f
   }
 }
 
+constexpr int LN_MAX_K = 2048;  // widest row the fused LayerNorm holds in registers
+
 struct LnArgs {
   const float* x;      // fp32 rows to normalise
   int ld_x;
@@ -347,53 +349,85 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
     uint8_t* a_region = smem + L::A_REGION_OFFSET;
     const int k_lo = kb_lo * TC_BK;
     const int k_hi = kb_hi * TC_BK;  // may pass K: the tail is zero-filled
+    // One warp per row. The row (at most LN_MAX_K = 2048 wide) is fetched once, all loads in
+    // flight together, and stays in registers for the mean, the variance about that mean and
+    // the normalised values: one memory round trip per row on the kernel's critical path.
     for (int m = warp; m < M; m += 4) {
       const float* src = ln.x + (size_t)(ln.rows != nullptr ? ln.rows[m] : m) * ln.ld_x;
+      float4 held[LN_MAX_K / 128];
+#pragma unroll
+      for (int i = 0; i < LN_MAX_K / 128; ++i) {
+        const int c = i * 128 + lane * 4;
+        held[i] = c < K ? *reinterpret_cast<const float4*>(src + c)
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
       float sum = 0.f;
-      for (int c = lane * 4; c < K; c += 128) {
-        const float4 v = *reinterpret_cast<const float4*>(src + c);
-        sum += (v.x + v.y) + (v.z + v.w);
+#pragma unroll
+      for (int i = 0; i < LN_MAX_K / 128; ++i) {
+        sum += (held[i].x + held[i].y) + (held[i].z + held[i].w);
       }
       const float mean = warp_sum(sum) / (float)K;
       float sq = 0.f;
-      for (int c = lane * 4; c < K; c += 128) {
-        const float4 v = *reinterpret_cast<const float4*>(src + c);
-        const float a = v.x - mean, b = v.y - mean, cc = v.z - mean, d = v.w - mean;
-        sq += (a * a + b * b) + (cc * cc + d * d);
+#pragma unroll
+      for (int i = 0; i < LN_MAX_K / 128; ++i) {
+        if (i * 128 + lane * 4 < K) {
+          const float a = held[i].x - mean, b = held[i].y - mean;
+          const float c = held[i].z - mean, d = held[i].w - mean;
+          sq += (a * a + b * b) + (c * c + d * d);
+        }
       }
       const float rstd = rsqrtf(warp_sum(sq) / (float)K + ln.eps);
-      // one 16-byte chunk (8 elements) per lane and pass
-      for (int k = k_lo + lane * 8; k < k_hi; k += 256) {
-        uint4 packed = make_uint4(0u, 0u, 0u, 0u);
-        if (k < K) {
-          float v[8];
-          const float4 x0 = *reinterpret_cast<const float4*>(src + k);
-          const float4 x1 = *reinterpret_cast<const float4*>(src + k + 4);
-          const float4 g0 = __ldg(reinterpret_cast<const float4*>(ln.gamma + k));
-          const float4 g1 = __ldg(reinterpret_cast<const float4*>(ln.gamma + k + 4));
-          v[0] = (x0.x - mean) * rstd * g0.x; v[1] = (x0.y - mean) * rstd * g0.y;
-          v[2] = (x0.z - mean) * rstd * g0.z; v[3] = (x0.w - mean) * rstd * g0.w;
-          v[4] = (x1.x - mean) * rstd * g1.x; v[5] = (x1.y - mean) * rstd * g1.y;
-          v[6] = (x1.z - mean) * rstd * g1.z; v[7] = (x1.w - mean) * rstd * g1.w;
-          if (ln.beta != nullptr) {
-            const float4 b0 = __ldg(reinterpret_cast<const float4*>(ln.beta + k));
-            const float4 b1 = __ldg(reinterpret_cast<const float4*>(ln.beta + k + 4));
-            v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-            v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+      // this CTA's K range: lane pairs own 16-byte chunks (8 elements = two float4)
+#pragma unroll
+      for (int i = 0; i < LN_MAX_K / 128; ++i) {
+        const int c = i * 128 + lane * 4;  // this lane's 4 elements
+        // partner lane (lane ^ 1) holds the other half of the 8-element chunk
+        const float4 mine = held[i];
+        float4 other;
+        other.x = __shfl_xor_sync(0xffffffffu, mine.x, 1);
+        other.y = __shfl_xor_sync(0xffffffffu, mine.y, 1);
+        other.z = __shfl_xor_sync(0xffffffffu, mine.z, 1);
+        other.w = __shfl_xor_sync(0xffffffffu, mine.w, 1);
+        const int k = c & ~7;  // start of the chunk
+        if ((lane & 1) == 0 && k >= k_lo && k < k_hi) {
+          uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+          if (k < K) {
+            const float4 g0 = __ldg(reinterpret_cast<const float4*>(ln.gamma + k));
+            const float4 g1 = __ldg(reinterpret_cast<const float4*>(ln.gamma + k + 4));
+            float v[8];
+            v[0] = (mine.x - mean) * rstd * g0.x; v[1] = (mine.y - mean) * rstd * g0.y;
+            v[2] = (mine.z - mean) * rstd * g0.z; v[3] = (mine.w - mean) * rstd * g0.w;
+            v[4] = (other.x - mean) * rstd * g1.x; v[5] = (other.y - mean) * rstd * g1.y;
+            v[6] = (other.z - mean) * rstd * g1.z; v[7] = (other.w - mean) * rstd * g1.w;
+            if (ln.beta != nullptr) {
+              const float4 b0 = __ldg(reinterpret_cast<const float4*>(ln.beta + k));
+              const float4 b1 = __ldg(reinterpret_cast<const float4*>(ln.beta + k + 4));
+              v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+              v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+            }
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
+            packed.x = *reinterpret_cast<uint32_t*>(&h0);
+            packed.y = *reinterpret_cast<uint32_t*>(&h1);
+            packed.z = *reinterpret_cast<uint32_t*>(&h2);
+            packed.w = *reinterpret_cast<uint32_t*>(&h3);
           }
-          __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
-          __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
-          __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
-          __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
-          packed.x = *reinterpret_cast<uint32_t*>(&h0);
-          packed.y = *reinterpret_cast<uint32_t*>(&h1);
-          packed.z = *reinterpret_cast<uint32_t*>(&h2);
-          packed.w = *reinterpret_cast<uint32_t*>(&h3);
+          const int local = k - k_lo;
+          const int kb = local / TC_BK, chunk = (local % TC_BK) / 8;
+          uint8_t* dst = a_region + kb * L::A_BYTES + m * 128 + ((chunk ^ (m & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = packed;
         }
-        const int local = k - k_lo;
-        const int kb = local / TC_BK, chunk = (local % TC_BK) / 8;
-        uint8_t* dst = a_region + kb * L::A_BYTES + m * 128 + ((chunk ^ (m & 7)) << 4);
-        *reinterpret_cast<uint4*>(dst) = packed;
+      }
+      // columns of this CTA's last block that lie past K (K is no multiple of 64): zeros
+      for (int k = ((K + 7) & ~7) + lane * 8; k < k_hi; k += 256) {
+        if (k >= k_lo) {
+          const int local = k - k_lo;
+          const int kb = local / TC_BK, chunk = (local % TC_BK) / 8;
+          *reinterpret_cast<uint4*>(a_region + kb * L::A_BYTES + m * 128 +
+                                    ((chunk ^ (m & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+        }
       }
     }
     // make the generic-proxy writes visible to the tensor core's (async proxy) reads
@@ -674,21 +708,22 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
   }
 }
 
-// The same product for at most 64 rows with the LayerNorm of the input fused in:
+// The same product for at most 16 rows of width at most 2048 with the LayerNorm of the input
+// fused in (more rows would make every CTA repeat too much of the norm):
 // out = act(LayerNorm(x[rows]) @ W^T + bias). x is the fp32 residual stream (row stride ld_x, a
 // multiple of 4), rows an optional gather index, gamma/beta fp32 [K]. K must be a multiple of
-// 8 and at most 8 * MAXKB * 64 for the row class (AYK_TOO_LARGE otherwise: run the norm as its
-// own kernel). splits: 0 = choose, else the number of K splits (1, 2, 4 or 8).
+// 8 (AYK_TOO_LARGE beyond the limits: run the norm as its own kernel). splits: 0 = choose, else the number of K splits (1, 2, 4 or 8).
 AYK_API int ayk_gemm_bf16_tc_ln(const float* x, int ld_x, const int* rows, const float* gamma,
                                 const float* beta, float eps, const void* w, int ldw,
                                 const float* bias, void* out, int ldo, int M, int N, int K,
                                 int act, int mode, int splits, int* status, void* stream) {
   using namespace ayk;
   if (M == 0 || N == 0) return AYK_OK;
-  if (M < 0 || M > 64 || N < 0 || K < 1 || ld_x < K || ldw < K || ldo < N || status == nullptr ||
+  if (M < 0 || N < 0 || K < 1 || ld_x < K || ldw < K || ldo < N || status == nullptr ||
       x == nullptr || gamma == nullptr || !(eps > 0.f)) {
     return AYK_BAD_ARGUMENT;
   }
+  if (M > 16 || K > LN_MAX_K) return AYK_TOO_LARGE;
   if (mode < OUT_BF16 || mode > OUT_RESIDUAL_F32 || act < ACT_NONE || act > ACT_GELU_ERF ||
       (mode == OUT_RESIDUAL_F32 && act != ACT_NONE)) {
     return AYK_BAD_ARGUMENT;
@@ -700,14 +735,6 @@ AYK_API int ayk_gemm_bf16_tc_ln(const float* x, int ld_x, const int* rows, const
   const LnArgs ln = {x, ld_x, rows, gamma, beta, eps};
   const int want = splits > 0 ? splits : pick_splits(-1, N);
   cudaStream_t s = (cudaStream_t)stream;
-  if (M <= 16) {
-    return launch_gemm_tc_small<16, 4, true, 13>(nullptr, 0, w, ldw, bias, out, ldo, M, N, K, act,
-                                                 mode, want, status, ln, s);
-  }
-  if (M <= 32) {
-    return launch_gemm_tc_small<32, 4, true, 13>(nullptr, 0, w, ldw, bias, out, ldo, M, N, K, act,
-                                                 mode, want, status, ln, s);
-  }
-  return launch_gemm_tc_small<64, 4, true, 7>(nullptr, 0, w, ldw, bias, out, ldo, M, N, K, act,
-                                              mode, want, status, ln, s);
+  return launch_gemm_tc_small<16, 4, true, 13>(nullptr, 0, w, ldw, bias, out, ldo, M, N, K, act,
+                                               mode, want, status, ln, s);
 }

@@ -63,19 +63,20 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
     check(status, "linear (tcgen05)")
 
 
-#: largest K (in 64-wide blocks) the fused-LayerNorm kernel keeps resident, per padded rows
-_LN_MAX_BLOCKS = {16: 13 * 8, 32: 13 * 8, 64: 7 * 8}
+#: the fused-LayerNorm kernel's limits: rows of a step, width of a row
+LN_MAX_ROWS, LN_MAX_WIDTH = 16, 2048
 
 
 def can_fuse_norm(x: torch.Tensor, weight: torch.Tensor, gamma: torch.Tensor,
                   beta: torch.Tensor | None, rows: int) -> bool:
-    """Whether ``linear_normed_bf16`` takes these operands: at most 64 rows, a width the
-    kernel can keep in shared memory, and the alignments of its vector loads."""
-    if not 0 < rows <= 64 or weight.dtype != torch.bfloat16 or x.dtype != torch.float32:
+    """Whether ``linear_normed_bf16`` takes these operands: at most 16 rows no wider than 2048
+    (each CTA normalises all rows itself, from registers), and the alignments of its vector
+    loads."""
+    if not 0 < rows <= LN_MAX_ROWS or weight.dtype != torch.bfloat16 or \
+            x.dtype != torch.float32:
         return False
     k = weight.shape[1]
-    padded = 16 if rows <= 16 else (32 if rows <= 32 else 64)
-    return (k % 8 == 0 and -(-k // 64) <= _LN_MAX_BLOCKS[padded] and x.stride(0) % 4 == 0
+    return (k % 8 == 0 and k <= LN_MAX_WIDTH and x.stride(0) % 4 == 0
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
             and weight.stride(0) % 8 == 0 and gamma.data_ptr() % 16 == 0
             and (beta is None or beta.data_ptr() % 16 == 0))

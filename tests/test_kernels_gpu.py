@@ -179,8 +179,8 @@ def test_linear_tcgen05_few_rows(m, splits):
     gemm_tc.check_status(a.device)
 
 
-@pytest.mark.parametrize("m", [1, 8, 16, 20, 33, 64])
-@pytest.mark.parametrize("n,k", [(4800, 1600), (300, 96), (50257, 160), (136, 840)])
+@pytest.mark.parametrize("m", [1, 3, 8, 16])
+@pytest.mark.parametrize("n,k", [(4800, 1600), (300, 96), (50257, 160), (136, 840), (64, 2048)])
 def test_linear_with_fused_layer_norm(m, n, k):
     """LayerNorm computed inside the few-rows matrix product: against float64, and against
     the two-kernel path it replaces (same roundings: the results agree to the last bf16 bit
@@ -219,8 +219,8 @@ def test_linear_with_fused_layer_norm(m, n, k):
 
 def test_linear_normed_falls_back_when_it_cannot_fuse():
     ops = _ops()
-    # float32 weights, and more than 64 rows in bfloat16: the norm runs as its own kernel
-    for dtype, m in ((torch.float32, 9), (torch.bfloat16, 100)):
+    # float32 weights, and more than 16 rows in bfloat16: the norm runs as its own kernel
+    for dtype, m in ((torch.float32, 9), (torch.bfloat16, 17)):
         x = _randn(m, 96, seed=45)
         gamma, beta = _randn(96, seed=46) + 1.0, _randn(96, seed=47)
         w = _randn(40, 96, seed=48, dtype=dtype, scale=0.1)
@@ -492,11 +492,11 @@ def test_attention_decode_split_kv(dtype, splits, case):
     at = 0
     for b, length in enumerate(lengths):
         row = at if at == 0 else at + 1  # the padding row sits at index 1
-        page, slot = int(table[b, (length - 1) // page]), (length - 1) % page
-        k_new[row] = k_pages[page, :, slot].reshape(-1)
-        v_new[row] = v_pages[page, :, slot].reshape(-1)
-        wiped_k[page, :, slot] = float("nan")
-        wiped_v[page, :, slot] = float("nan")
+        where, slot = int(table[b, (length - 1) // page]), (length - 1) % page
+        k_new[row] = k_pages[where, :, slot].reshape(-1)
+        v_new[row] = v_pages[where, :, slot].reshape(-1)
+        wiped_k[where, :, slot] = float("nan")
+        wiped_v[where, :, slot] = float("nan")
         at += 1
     out = torch.full((n + 1, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
     ops.attention_decode(q, wiped_k, wiped_v, table, req, pos, out, num_heads=heads, scale=scale,
