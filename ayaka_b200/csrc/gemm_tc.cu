@@ -520,11 +520,26 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
     const int cols = MP / splits;  // the host picks splits that divide MP
     if (*failed == 0 && n < N) {
       const float b = bias != nullptr ? __ldg(bias + n) : 0.f;
+      // remote addresses of this thread's column in every peer's tile
+      uint32_t peer_base[8];
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {
+        peer_base[p] = p < splits ? peer_address(partial + t, (uint32_t)p) : 0u;
+      }
       for (int j = 0; j < cols; ++j) {
         const int m = rank * cols + j;
         if (m >= M) break;
-        float sum = 0.f;
-        for (int p = 0; p < splits; ++p) sum += ld_peer_f32(partial + m * TC_BM + t, p);
+        // all loads first (they are independent), then the sum in rank order
+        float v[8];
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+          v[p] = p < splits ? ld_cluster_f32(peer_base[p] + (uint32_t)(m * TC_BM * 4)) : 0.f;
+        }
+        float sum = v[0];
+#pragma unroll
+        for (int p = 1; p < 8; ++p) {
+          if (p < splits) sum += v[p];
+        }
         store_output(out, ldo, m, n, sum + b, mode, act);
       }
     }
@@ -646,11 +661,14 @@ int launch_gemm_tc_small(const void* a, int lda, const void* w, int ldw, const f
                        status, ln);
 }
 
-inline int pick_splits(int tile_n, int N) {
+inline int pick_splits(int tile_n, int N, int M) {
   // -1: choose; -2, -4, -8: that many K splits; -100: one split
   if (tile_n == -100) return 1;
   if (tile_n != -1) return -tile_n;
   const int tiles = (N + TC_BM - 1) / TC_BM;
+  // measured on GPT-2 XL's shapes: with more than 32 rows the cluster reduction of a
+  // [64, 128] tile costs more than it buys unless the tiles are very few
+  if (M > 32) return tiles >= 32 ? 1 : 8;
   int splits = 1;
   while (splits < 8 && tiles * splits * 2 <= 296) splits <<= 1;
   return splits;
@@ -682,7 +700,7 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
   if (tile_n == 0 && M <= 64) tile_n = -1;  // few rows: the weight-streaming kernel
   if (tile_n < 0) {
     if (M > 64) return AYK_BAD_ARGUMENT;
-    const int splits = pick_splits(tile_n, N);
+    const int splits = pick_splits(tile_n, N, M);
     const LnArgs none = {nullptr, 0, nullptr, nullptr, nullptr, 0.f};
     if (M <= 16) {
       return launch_gemm_tc_small<16, 5, false, 0>(a, lda, w, ldw, bias, out, ldo, M, N, K, act,
@@ -733,7 +751,7 @@ AYK_API int ayk_gemm_bf16_tc_ln(const float* x, int ld_x, const int* rows, const
     return AYK_BAD_ALIGNMENT;
   }
   const LnArgs ln = {x, ld_x, rows, gamma, beta, eps};
-  const int want = splits > 0 ? splits : pick_splits(-1, N);
+  const int want = splits > 0 ? splits : pick_splits(-1, N, M);
   cudaStream_t s = (cudaStream_t)stream;
   return launch_gemm_tc_small<16, 4, true, 13>(nullptr, 0, w, ldw, bias, out, ldo, M, N, K, act,
                                                mode, want, status, ln, s);

@@ -34,12 +34,74 @@ __global__ void layer_norm_kernel(const float* __restrict__ x, int ld_x,
   }
 }
 
+// The same with the row held in registers: one pass over global memory (all loads in flight
+// at once), mean and variance from the registers. For rows of at most 256 * 4 * VEC floats
+// whose addresses allow 16-byte loads.
+template <typename TOut, int VEC>
+__global__ void __launch_bounds__(256)
+layer_norm_held_kernel(const float* __restrict__ x, int ld_x, const int* __restrict__ rows,
+                       const float* __restrict__ gamma, const float* __restrict__ beta,
+                       float eps, TOut* __restrict__ out, int ld_out, int width) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const float* src = x + (size_t)(rows != nullptr ? rows[r] : r) * ld_x;
+  float4 held[VEC];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int c = (i * 256 + threadIdx.x) * 4;
+    held[i] = c < width ? *reinterpret_cast<const float4*>(src + c)
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+    s += (held[i].x + held[i].y) + (held[i].z + held[i].w);
+  }
+  const float mean = block_sum(s, scratch) / (float)width;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    if ((i * 256 + threadIdx.x) * 4 < width) {
+      const float a = held[i].x - mean, b = held[i].y - mean;
+      const float c = held[i].z - mean, d = held[i].w - mean;
+      q += (a * a + b * b) + (c * c + d * d);
+    }
+  }
+  const float inv = rsqrtf(block_sum(q, scratch) / (float)width + eps);
+  TOut* dst = out + (size_t)r * ld_out;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int c = (i * 256 + threadIdx.x) * 4;
+    if (c < width) {
+      const float4 g = __ldg(reinterpret_cast<const float4*>(gamma + c));
+      float v0 = (held[i].x - mean) * inv * g.x, v1 = (held[i].y - mean) * inv * g.y;
+      float v2 = (held[i].z - mean) * inv * g.z, v3 = (held[i].w - mean) * inv * g.w;
+      if (beta != nullptr) {
+        const float4 b = __ldg(reinterpret_cast<const float4*>(beta + c));
+        v0 += b.x; v1 += b.y; v2 += b.z; v3 += b.w;
+      }
+      stf(dst + c, v0); stf(dst + c + 1, v1); stf(dst + c + 2, v2); stf(dst + c + 3, v3);
+    }
+  }
+}
+
 template <typename TOut>
 int layer_norm(const float* x, int ld_x, const int* rows, const float* gamma, const float* beta,
                float eps, void* out, int ld_out, int n, int width, cudaStream_t stream) {
   if (n == 0) return AYK_OK;
   if (n < 0 || width < 1 || ld_x < width || ld_out < width || !(eps > 0.f)) {
     return AYK_BAD_ARGUMENT;
+  }
+  const bool vector_ok = width % 4 == 0 && ld_x % 4 == 0 && ((uintptr_t)x % 16) == 0 &&
+                         ((uintptr_t)gamma % 16) == 0 && ((uintptr_t)beta % 16) == 0;
+  if (vector_ok && width <= 8192 && width >= 256) {
+#define AYK_LN_HELD(VEC)                                                                       \
+  return launch_kernel(layer_norm_held_kernel<TOut, VEC>, dim3(n), dim3(256), 0, stream, 1, x,  \
+                       ld_x, rows, gamma, beta, eps, (TOut*)out, ld_out, width)
+    if (width <= 1024) AYK_LN_HELD(1);
+    if (width <= 2048) AYK_LN_HELD(2);
+    if (width <= 4096) AYK_LN_HELD(4);
+    AYK_LN_HELD(8);
+#undef AYK_LN_HELD
   }
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   return launch_kernel(layer_norm_kernel<TOut>, dim3(n), dim3(threads), 0, stream, 1, x, ld_x,

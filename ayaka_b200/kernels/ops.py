@@ -57,6 +57,12 @@ def launch_count() -> int:
     return _launches
 
 
+def _status_word(device: torch.device) -> torch.Tensor:
+    from ayaka_b200.kernels import gemm_tc
+
+    return gemm_tc.status_word(device)
+
+
 def _stream() -> c_void_p:
     global _launches
     _launches += 1
@@ -390,7 +396,7 @@ def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         c_int(page_size), c_float(scale), c_int(window), c_int(splits), _ptr(partial),
         _ptr(tickets), _ptr(k_new), _ptr(v_new),
         c_int(0 if k_new is None else k_new.stride(0)), c_int(1 if store else 0),
-        c_int(_TYPE[q.dtype]), _stream())
+        _ptr(_status_word(q.device)), c_int(_TYPE[q.dtype]), _stream())
     check(status, op)
 
 
