@@ -1,17 +1,23 @@
 // Paged attention for decode rows: one query row per request, keys split over several CTAs.
 //
 // A decode step reads every cached key and value of every live request once; with one row
-// per request there is no reuse, so the kernel is built to keep many bytes in flight.
-// grid = (splits, heads, requests). A CTA of 128 threads takes one contiguous share of the
-// request's keys and streams it through a ring of shared-memory stages: one thread issues
-// bulk asynchronous copies (cp.async.bulk, a page's run of keys of one head is contiguous in
-// the cache) that complete on an mbarrier, several chunks ahead of the arithmetic. TPK threads
-// cooperate on one key (each holds 8 of head_dim's elements), so a CTA covers 128 / TPK keys
-// per pass. Scores, the running maximum and sum (online softmax) and the weighted sum of
-// values are fp32. Every wait is bounded and reports through `status`. Each
-// CTA leaves (max, sum, weighted values) of its share in scratch memory; the CTA that
-// finishes last for a (request, head) — found with an atomic ticket — merges the shares in
-// split order and writes the output row. With splits == 1 nothing goes through scratch.
+// per request there is no reuse, so the kernel is built to keep many loads in flight and to
+// spend few instructions per key. grid = (splits, heads, requests). The request's keys are cut
+// into splits * 4 contiguous shares, one per warp; the four warps of a CTA never wait for one
+// another. TPK lanes of a warp share one key (8 elements of head_dim each, one 16-byte piece
+// of the key and one of the value); a lane works on a batch of keys at a time — scores, one
+// update of its running maximum and sum (online softmax) and the weighted values, all in fp32
+// — while cp.async copies of the next three batches are in flight into the lane's own strip
+// of shared memory (a queue nobody else reads, so it needs no barrier). Block-table entries sit one per lane and travel by shuffle, so no load of a key
+// waits on a load of a table entry. Only at the end are the lanes', then the warps' shares
+// folded together.
+//
+// Each CTA ends with (max, sum, weighted values) of its share. Up to 8 splits form a
+// thread-block cluster and rank 0 merges the shares through distributed shared memory after
+// one cluster barrier. With scratch memory (required beyond 8 splits) every CTA writes its
+// share there and the CTA that finishes last for a (request, head) — found with an atomic
+// ticket — merges them. Either way the shares are merged in split order. With splits == 1
+// nothing is merged.
 //
 // Scratch: partial [requests * heads * splits * (head_dim + 2)] floats and one int ticket
 // per (request, head), zero before the first launch and left zero by every launch.
@@ -20,8 +26,9 @@
 
 namespace ayk {
 
-constexpr int DEC_THREADS = 128;
-constexpr int DEC_STAGES = 4;
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_THREADS = DEC_WARPS * 32;
+constexpr int DEC_DEPTH = 3;  // batches whose copies are in flight ahead of the arithmetic
 
 template <typename T> struct Frag8;
 template <> struct Frag8<float> {
@@ -29,24 +36,23 @@ template <> struct Frag8<float> {
     *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
     *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(src + 4);
   }
-  static __device__ __forceinline__ void load_shared(const float* p, float* v) {
+  static __device__ __forceinline__ void load(const float* p, float* v) {
     const float4 a = *reinterpret_cast<const float4*>(p);
     const float4 b = *reinterpret_cast<const float4*>(p + 4);
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
     v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
   }
-  static __device__ __forceinline__ void load(const float* p, float* v) {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
-    const float4 b = __ldg(reinterpret_cast<const float4*>(p + 4));
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  static __device__ __forceinline__ void load2(const float* p, float& a, float& b) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    a = v.x;
+    b = v.y;
   }
 };
 template <> struct Frag8<__nv_bfloat16> {
   static __device__ __forceinline__ void copy(__nv_bfloat16* dst, const __nv_bfloat16* src) {
     *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
   }
-  static __device__ __forceinline__ void load_shared(const __nv_bfloat16* p, float* v) {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
     const uint4 raw = *reinterpret_cast<const uint4*>(p);
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
@@ -55,14 +61,10 @@ template <> struct Frag8<__nv_bfloat16> {
       v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
     }
   }
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      v[2 * i] = __uint_as_float(w[i] << 16);
-      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
+  static __device__ __forceinline__ void load2(const __nv_bfloat16* p, float& a, float& b) {
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+    a = __uint_as_float(w << 16);
+    b = __uint_as_float(w & 0xffff0000u);
   }
 };
 
@@ -78,7 +80,76 @@ __device__ __forceinline__ void merge_state(float& m, float& l, float* acc, floa
   m = nm;
 }
 
-template <typename T, int TPK>
+#ifdef AYK_DEC_TRACE
+__device__ long long dec_trace[64];
+#define DEC_MARK(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) dec_trace[i] = clock64(); } while (0)
+#else
+#define DEC_MARK(i)
+#endif
+
+// 8 consecutive elements as they lie in memory (16 bytes of bfloat16, 32 bytes of float32).
+template <typename T> struct Raw8;
+template <> struct Raw8<__nv_bfloat16> {
+  uint4 v;
+  __device__ __forceinline__ void fetch(const __nv_bfloat16* p) {
+    v = __ldg(reinterpret_cast<const uint4*>(p));
+  }
+  // `stride`: 16-byte units between the pieces of one value (one piece here)
+  __device__ __forceinline__ void from_shared(const uint4* p, int stride) { v = p[0]; }
+  __device__ __forceinline__ void zero() { v = make_uint4(0u, 0u, 0u, 0u); }
+  __device__ __forceinline__ void store(__nv_bfloat16* p) const {
+    *reinterpret_cast<uint4*>(p) = v;
+  }
+  __device__ __forceinline__ void widen(float* f) const {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+template <> struct Raw8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void fetch(const float* p) {
+    a = __ldg(reinterpret_cast<const float4*>(p));
+    b = __ldg(reinterpret_cast<const float4*>(p + 4));
+  }
+  __device__ __forceinline__ void from_shared(const uint4* p, int stride) {
+    const uint4 lo = p[0], hi = p[stride];
+    a = make_float4(__uint_as_float(lo.x), __uint_as_float(lo.y), __uint_as_float(lo.z),
+                    __uint_as_float(lo.w));
+    b = make_float4(__uint_as_float(hi.x), __uint_as_float(hi.y), __uint_as_float(hi.z),
+                    __uint_as_float(hi.w));
+  }
+  __device__ __forceinline__ void zero() {
+    a = make_float4(0.f, 0.f, 0.f, 0.f);
+    b = a;
+  }
+  __device__ __forceinline__ void store(float* p) const {
+    *reinterpret_cast<float4*>(p) = a;
+    *reinterpret_cast<float4*>(p + 4) = b;
+  }
+  __device__ __forceinline__ void widen(float* f) const {
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+};
+
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_group() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N> __device__ __forceinline__ void cp_async_wait_group() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <typename T, int TPK, int BATCH>
 __global__ void __launch_bounds__(DEC_THREADS)
 attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k_pages,
                         const T* __restrict__ v_pages, const int* __restrict__ block_table,
@@ -87,25 +158,31 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
                         int num_kv_heads, int group, int head_dim, int page_size, float scale,
                         int window, float* __restrict__ partial, int* __restrict__ tickets,
                         const T* __restrict__ k_new, const T* __restrict__ v_new, int ld_new,
-                        T* __restrict__ k_store, T* __restrict__ v_store, int chunk_keys,
-                        int* __restrict__ status) {
-  constexpr int KEYS_PER_PASS = DEC_THREADS / TPK;
-  __shared__ float s_m[DEC_THREADS / 32][TPK], s_l[DEC_THREADS / 32][TPK];
-  __shared__ float s_acc[DEC_THREADS / 32][TPK][8];
+                        T* __restrict__ k_store, T* __restrict__ v_store, int clustered,
+                        int page_shift) {
+  constexpr int SLOTS = 32 / TPK;          // keys a warp covers per pass
+  constexpr int STEP = SLOTS * BATCH;      // keys a warp covers per batch
+  __shared__ float s_m[DEC_WARPS][TPK], s_l[DEC_WARPS][TPK];  // each warp's (max, sum) ...
+  __shared__ float s_wacc[DEC_WARPS][TPK][8];                 // ... and weighted values
+  __shared__ float c_share[2 + 256];         // this CTA's (max, sum, weighted values)
   __shared__ int s_last;
-  __shared__ __align__(8) uint64_t s_full[DEC_STAGES];
-  extern __shared__ __align__(128) unsigned char dec_smem[];
 
+  DEC_MARK(0);
   pdl_launch_dependents();
   pdl_wait();
   const int split = blockIdx.x, splits = gridDim.x;
   const int head = blockIdx.y, num_heads = gridDim.y;
   const int row = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int sub = tid % TPK;        // which 8 elements of head_dim
-  const int key_slot = tid / TPK;   // which key of the pass
+  const int sub = lane % TPK;   // which 8 elements of head_dim
+  const int slot = lane / TPK;  // which key of a pass
   const bool dims_ok = sub * 8 < head_dim;
+  // the three loads every CTA starts with, issued together
   const int req = request_of_row[row];
+  const int pos = positions[row];
+  Raw8<T> q_raw;
+  q_raw.zero();
+  if (dims_ok) q_raw.fetch(q + (size_t)row * ld_q + (size_t)head * head_dim + sub * 8);
   T* dst = out + (size_t)row * ld_out + (size_t)head * head_dim;
   if (req < 0) {  // a padding row: zeros, no scratch, no ticket
     if (split == 0) {
@@ -114,174 +191,214 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
     return;
   }
   const int kv_head = head / group;
-  const int pos = positions[row];
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int total = pos + 1 - lo;
-  int share = (total + splits - 1) / splits;
-  share = (share + KEYS_PER_PASS - 1) / KEYS_PER_PASS * KEYS_PER_PASS;
-  const int k_lo = lo + split * share;
+  // the request's keys lo..pos are cut into splits * warps contiguous shares, a multiple of
+  // a batch each (so every warp but the last works on full batches)
+  const int num_shares = splits * DEC_WARPS;
+  int share = (pos + 1 - lo + num_shares - 1) / num_shares;
+  share = (share + STEP - 1) / STEP * STEP;
+  const int k_lo = lo + (split * DEC_WARPS + warp) * share;
   const int k_hi = k_lo + share < pos + 1 ? k_lo + share : pos + 1;
+  const int* table = block_table + (size_t)req * table_stride;
 
   float qf[8];
+  q_raw.widen(qf);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) qf[i] = 0.f;
-  if (dims_ok) {
-    float tmp[8];
-    Frag8<T>::load(q + (size_t)row * ld_q + (size_t)head * head_dim + sub * 8, tmp);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) qf[i] = tmp[i] * scale;
-  }
-  const int* table = block_table + (size_t)req * table_stride;
-  float m = -INFINITY, l = 0.f, acc[8];
+  for (int i = 0; i < 8; ++i) qf[i] *= scale;
+  // key -> (page index, slot): a shift and a mask when the page size is a power of two (an
+  // integer division costs more instructions than all the arithmetic on a key)
+  const int page_mask = page_size - 1;
+  auto page_of = [&](int key) { return page_shift >= 0 ? key >> page_shift : key / page_size; };
+  auto slot_of = [&](int key) { return page_shift >= 0 ? key & page_mask : key % page_size; };
+  // the warp's slice of the block table: one entry per lane, handed around by shuffles, so
+  // that no load of a key waits on a load of a table entry (refilled every 32 pages)
+  int first_page = page_of(k_lo);
+  int my_entry = 0;
+  auto refill_table = [&](int from_page) {
+    first_page = from_page;
+    const int last_page = k_hi > k_lo ? page_of(k_hi - 1) : from_page;
+    my_entry = from_page + lane <= last_page ? table[from_page + lane] : 0;
+  };
+  refill_table(first_page);
+
+  float run_max = -INFINITY, run_sum = 0.f, acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  const size_t head_off = (size_t)kv_head * page_size * head_dim + (size_t)sub * 8;
+  const size_t page_elems = (size_t)num_kv_heads * page_size * head_dim;
+  const bool patch = k_new != nullptr && pos >= k_lo && pos < k_hi;
 
-  // ---- the ring of stages: chunk c holds keys k_lo + c * chunk_keys .. of K, then of V -----
-  const int stage_elems = chunk_keys * head_dim;  // elements of K (and of V) per stage
-  T* ring = reinterpret_cast<T*>(dec_smem);
-  const int num_chunks = k_hi > k_lo ? (k_hi - k_lo + chunk_keys - 1) / chunk_keys : 0;
-  if (tid == 0) {
-    for (int s = 0; s < DEC_STAGES; ++s) mbar_init(&s_full[s], 1);
-    mbar_fence_init();
-  }
-  __syncthreads();
-  // one thread copies a chunk: runs of keys inside one page are contiguous in the cache
-  auto issue = [&](int c) {
-    const int stage = c % DEC_STAGES;
-    const int c_lo = k_lo + c * chunk_keys;
-    const int c_hi = c_lo + chunk_keys < k_hi ? c_lo + chunk_keys : k_hi;
-    const uint32_t row_bytes = (uint32_t)head_dim * sizeof(T);
-    mbar_expect_tx(&s_full[stage], 2u * (uint32_t)(c_hi - c_lo) * row_bytes);
-    T* k_dst = ring + (size_t)stage * 2 * stage_elems;
-    T* v_dst = k_dst + stage_elems;
-    for (int key = c_lo; key < c_hi;) {
-      const int slot = key % page_size;
-      int run = page_size - slot;
-      if (run > c_hi - key) run = c_hi - key;
-      const int page = table[key / page_size];
-      const size_t off = (((size_t)page * num_kv_heads + kv_head) * page_size + slot) * head_dim;
-      bulk_load(k_dst + (size_t)(key - c_lo) * head_dim, k_pages + off, run * row_bytes,
-                &s_full[stage]);
-      bulk_load(v_dst + (size_t)(key - c_lo) * head_dim, v_pages + off, run * row_bytes,
-                &s_full[stage]);
-      key += run;
-    }
+  // Each lane copies exactly the 16-byte pieces it will read itself (its keys' and values'
+  // 8 elements) with cp.async into a private strip of shared memory, DEC_DEPTH batches ahead
+  // of the arithmetic: a first-in-first-out queue that needs no barrier, because nobody else
+  // ever looks at a lane's strip. Strip layout: [stage][key of batch][K, V][lane], 16-byte
+  // pieces (two per lane and kind for float32), so copies and reads are conflict-free.
+  constexpr int PIECES = sizeof(T) == 2 ? 1 : 2;  // 16-byte pieces per 8 elements
+  extern __shared__ __align__(16) unsigned char dec_smem[];
+  uint4* strip = reinterpret_cast<uint4*>(dec_smem) +
+                 (size_t)warp * (DEC_DEPTH + 1) * BATCH * 2 * PIECES * 32;
+  auto piece = [&](int stage, int u, int kind, int part) {
+    return strip + ((((size_t)stage * BATCH + u) * 2 + kind) * PIECES + part) * 32 + lane;
   };
-  int issued = 0;  // chunks whose copies thread 0 has started
-  if (tid == 0) {
-    for (int c = 0; c < DEC_STAGES - 1 && c < num_chunks; ++c) issue(c);
-    issued = num_chunks < DEC_STAGES - 1 ? num_chunks : DEC_STAGES - 1;
-  }
-  bool gave_up = false;
-  int c = 0;
-  for (; c < num_chunks; ++c) {
-    // the stage of chunk c + STAGES - 1 was read in the last iteration, which ended with a
-    // barrier: it is free
-    if (tid == 0 && c + DEC_STAGES - 1 < num_chunks) {
-      issue(c + DEC_STAGES - 1);
-      issued = c + DEC_STAGES;
-    }
-    const int stage = c % DEC_STAGES;
-    const bool landed = mbar_wait(&s_full[stage], (c / DEC_STAGES) & 1);
-    if (__syncthreads_or(!landed)) {  // all threads agree, whoever ran out of patience
-      gave_up = true;
-      break;
-    }
-    const int c_lo = k_lo + c * chunk_keys;
-    const T* k_src = ring + (size_t)stage * 2 * stage_elems;
-    const T* v_src = k_src + stage_elems;
-    for (int local = key_slot; local < chunk_keys; local += KEYS_PER_PASS) {
-      const int key = c_lo + local;
-      const bool valid = key < k_hi;
-      float kf[8], vf[8];
+  auto issue = [&](int base, int stage) {
+    // all lanes take part in the shuffles; a batch never spans more than 32 pages
+    if (page_of(base + STEP - 1) - first_page >= 32) refill_table(page_of(base));
 #pragma unroll
-      for (int i = 0; i < 8; ++i) { kf[i] = 0.f; vf[i] = 0.f; }
-      if (valid && dims_ok) {
-        if (k_new != nullptr && key == pos) {
-          // the row's own key and value come straight from this step's projection; the first
-          // head of each group also puts them into the cache (the fused KV store)
-          const size_t src = (size_t)row * ld_new + (size_t)kv_head * head_dim + sub * 8;
-          Frag8<T>::load(k_new + src, kf);
-          Frag8<T>::load(v_new + src, vf);
-          if (k_store != nullptr && head % group == 0) {
-            const int page = table[key / page_size];
-            const size_t off = (((size_t)page * num_kv_heads + kv_head) * page_size +
-                                key % page_size) * head_dim + sub * 8;
-            Frag8<T>::copy(k_store + off, k_new + src);
-            Frag8<T>::copy(v_store + off, v_new + src);
-          }
-        } else {
-          Frag8<T>::load_shared(k_src + (size_t)local * head_dim + sub * 8, kf);
-          Frag8<T>::load_shared(v_src + (size_t)local * head_dim + sub * 8, vf);
-        }
+    for (int u = 0; u < BATCH; ++u) {
+      const int key = base + u * SLOTS + slot;
+      const int page = __shfl_sync(0xffffffffu, my_entry, (page_of(key) - first_page) & 31);
+      const bool valid = key < k_hi && dims_ok;
+      const bool own = patch && key == pos;  // this row's own key: from the projection
+      const size_t off = (size_t)page * page_elems + head_off + (size_t)slot_of(key) * head_dim;
+      const size_t fresh = (size_t)row * ld_new + (size_t)kv_head * head_dim + sub * 8;
+      const T* k_from = own ? k_new + fresh : k_pages + (valid ? off : 0);
+      const T* v_from = own ? v_new + fresh : v_pages + (valid ? off : 0);
+#pragma unroll
+      for (int part = 0; part < PIECES; ++part) {
+        cp_async_16(piece(stage, u, 0, part), reinterpret_cast<const uint4*>(k_from) + part,
+                    valid);
+        cp_async_16(piece(stage, u, 1, part), reinterpret_cast<const uint4*>(v_from) + part,
+                    valid);
       }
-      float s = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) s = fmaf(qf[i], kf[i], s);
-#pragma unroll
-      for (int o = TPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if (valid) {
-        const float nm = fmaxf(m, s);
-        const float corr = expf(m - nm);
-        const float p = expf(s - nm);
-        l = l * corr + p;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, vf[i], acc[i] * corr);
-        m = nm;
+      if (own && valid && k_store != nullptr && head % group == 0) {
+        // the fused KV store: the first head of a group also puts them into the cache
+        Raw8<T> kr, vr;
+        kr.fetch(k_new + fresh);
+        vr.fetch(v_new + fresh);
+        kr.store(k_store + off);
+        vr.store(v_store + off);
       }
     }
-    __syncthreads();
+    cp_async_commit_group();
+  };
+  DEC_MARK(1);
+  const int num_batches = k_hi > k_lo ? (k_hi - k_lo + STEP - 1) / STEP : 0;
+#pragma unroll
+  for (int b = 0; b < DEC_DEPTH; ++b) {
+    if (b < num_batches) issue(k_lo + b * STEP, b); else cp_async_commit_group();
   }
-  if (gave_up) {
-    // leave together, after this CTA's copies in flight have landed (bounded), and say so
-    if (tid == 0) {
-      for (int w = c; w < issued; ++w) mbar_wait(&s_full[w % DEC_STAGES], (w / DEC_STAGES) & 1);
-      atomicExch(status, AYK_WAIT_TIMEOUT);
+  for (int b = 0; b < num_batches; ++b) {
+    const int base = k_lo + b * STEP;
+    const int stage = b % (DEC_DEPTH + 1);
+    if (b + DEC_DEPTH < num_batches) {
+      issue(k_lo + (b + DEC_DEPTH) * STEP, (b + DEC_DEPTH) % (DEC_DEPTH + 1));
+    } else {
+      cp_async_commit_group();  // keeps the group count in step
     }
-    return;
+    cp_async_wait_group<DEC_DEPTH>();  // batch b has landed (this lane's own pieces)
+    float s[BATCH], vf[BATCH][8];
+#pragma unroll
+    for (int u = 0; u < BATCH; ++u) {
+      Raw8<T> kr, vr;
+      kr.from_shared(piece(stage, u, 0, 0), 32);
+      vr.from_shared(piece(stage, u, 1, 0), 32);
+      float kf[8];
+      kr.widen(kf);
+      vr.widen(vf[u]);
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dot = fmaf(qf[i], kf[i], dot);
+      s[u] = dot;
+    }
+#pragma unroll
+    for (int o = TPK / 2; o > 0; o >>= 1) {
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
+    }
+    float top = run_max;
+#pragma unroll
+    for (int u = 0; u < BATCH; ++u) {
+      if (base + u * SLOTS + slot >= k_hi) s[u] = -INFINITY;
+      top = fmaxf(top, s[u]);
+    }
+    const float ref = top == -INFINITY ? 0.f : top;
+    const float corr = expf(run_max - ref);
+    run_max = top;
+    run_sum *= corr;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] *= corr;
+#pragma unroll
+    for (int u = 0; u < BATCH; ++u) {
+      const float p = expf(s[u] - ref);  // exp(-inf) = 0 for the keys that are not there
+      run_sum += p;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = fmaf(p, vf[u][i], acc[i]);
+    }
   }
-  // merge the key slots that share `sub`: first inside the warp, then across warps
+  cp_async_wait_group<0>();
+  DEC_MARK(2);
+  // the key slots of the warp that share `sub` fold together
 #pragma unroll
   for (int o = TPK; o < 32; o <<= 1) {
-    const float om = __shfl_xor_sync(0xffffffffu, m, o);
-    const float ol = __shfl_xor_sync(0xffffffffu, l, o);
+    const float om = __shfl_xor_sync(0xffffffffu, run_max, o);
+    const float ol = __shfl_xor_sync(0xffffffffu, run_sum, o);
     float oacc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) oacc[i] = __shfl_xor_sync(0xffffffffu, acc[i], o);
-    merge_state(m, l, acc, om, ol, oacc);
+    merge_state(run_max, run_sum, acc, om, ol, oacc);
   }
   if (lane < TPK) {
-    s_m[warp][lane] = m;
-    s_l[warp][lane] = l;
+    s_m[warp][lane] = run_max;
+    s_l[warp][lane] = run_sum;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) s_acc[warp][lane][i] = acc[i];
+    for (int i = 0; i < 8; ++i) s_wacc[warp][lane][i] = acc[i];
   }
   __syncthreads();
+  DEC_MARK(4);
+  // fold the warps' shares, in warp order: c_share = (max, sum, weighted values[head_dim])
   if (tid < TPK) {
-    m = s_m[0][tid];
-    l = s_l[0][tid];
+    float m = -INFINITY, l = 0.f, total[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = s_acc[0][tid][i];
-    for (int w = 1; w < DEC_THREADS / 32; ++w) {
-      merge_state(m, l, acc, s_m[w][tid], s_l[w][tid], s_acc[w][tid]);
+    for (int i = 0; i < 8; ++i) total[i] = 0.f;
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      merge_state(m, l, total, s_m[w][tid], s_l[w][tid], s_wacc[w][tid]);
     }
-    if (splits == 1) {
-      if (sub * 8 < head_dim) {
-        const float inv = 1.f / l;
+    if (tid == 0) { c_share[0] = m; c_share[1] = l; }
+    if (tid * 8 < head_dim) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) stf(dst + tid * 8 + i, acc[i] * inv);
-      }
-    } else {
-      float* mine = partial + ((size_t)(row * num_heads + head) * splits + split) *
-                                  (head_dim + 2);
-      if (tid == 0) { mine[0] = m; mine[1] = l; }
-      if (sub * 8 < head_dim) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) mine[2 + tid * 8 + i] = acc[i];
-      }
+      for (int i = 0; i < 8; ++i) c_share[2 + tid * 8 + i] = total[i];
     }
   }
-  if (splits == 1) return;
+  __syncthreads();
+  if (splits == 1) {
+    const float inv = 1.f / c_share[1];
+    for (int d = tid; d < head_dim; d += DEC_THREADS) stf(dst + d, c_share[2 + d] * inv);
+    DEC_MARK(5);
+    return;
+  }
+  if (clustered) {
+    // the splits of one (request, head) are the CTAs of one cluster: rank 0 merges the shares
+    // through distributed shared memory, in rank order; no scratch, no tickets
+    cluster_sync_all();
+    if (split == 0) {
+      float top = -INFINITY;
+      for (int s = 0; s < splits; ++s) {
+        top = fmaxf(top, ld_cluster_f32(peer_address(&c_share[0], (uint32_t)s)));
+      }
+      float denom = 0.f;
+      for (int s = 0; s < splits; ++s) {
+        const float sm = ld_cluster_f32(peer_address(&c_share[0], (uint32_t)s));
+        if (sm != -INFINITY) {
+          denom += ld_cluster_f32(peer_address(&c_share[1], (uint32_t)s)) * expf(sm - top);
+        }
+      }
+      for (int d = tid; d < head_dim; d += DEC_THREADS) {
+        float sum = 0.f;
+        for (int s = 0; s < splits; ++s) {
+          const float sm = ld_cluster_f32(peer_address(&c_share[0], (uint32_t)s));
+          if (sm != -INFINITY) {
+            sum += ld_cluster_f32(peer_address(&c_share[2 + d], (uint32_t)s)) * expf(sm - top);
+          }
+        }
+        stf(dst + d, sum / denom);
+      }
+    }
+    cluster_sync_all();  // nobody leaves while rank 0 may still read its share
+    return;
+  }
+  // through scratch: every CTA stores its share; the last one to finish merges them
+  float* mine = partial + ((size_t)(row * num_heads + head) * splits + split) * (head_dim + 2);
+  for (int d = tid; d < head_dim + 2; d += DEC_THREADS) mine[d] = c_share[d];
   __threadfence();
   __syncthreads();
   if (tid == 0) {
@@ -316,29 +433,35 @@ int launch_decode(const void* q, int ld_q, const void* k_pages, const void* v_pa
                   const int* positions, void* out, int ld_out, int num_rows, int num_heads,
                   int num_kv_heads, int head_dim, int page_size, float scale, int window,
                   int splits, float* partial, int* tickets, const void* k_new,
-                  const void* v_new, int ld_new, int store, int* status, cudaStream_t stream) {
+                  const void* v_new, int ld_new, int store, cudaStream_t stream) {
+  constexpr int BATCH = sizeof(T) == 2 ? 4 : 2;  // keys a lane works on at a time
   dim3 grid(splits, num_heads, num_rows);
-  // keys per stage: 64 while a stage (K and V) stays within 32 KB, never fewer than a pass
-  int chunk_keys = 64;
-  while (chunk_keys > DEC_THREADS / TPK && (size_t)chunk_keys * head_dim * sizeof(T) * 2 > 32768) {
-    chunk_keys >>= 1;
+  // up to 8 splits given no scratch run as one thread-block cluster and merge on chip; with
+  // scratch (needed beyond 8 splits) the shares go through global memory and a ticket
+  const int clustered = (splits > 1 && splits <= 8 && partial == nullptr) ? 1 : 0;
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0) {
+    page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
   }
-  if (chunk_keys < DEC_THREADS / TPK) chunk_keys = DEC_THREADS / TPK;
-  const size_t smem = (size_t)DEC_STAGES * 2 * chunk_keys * head_dim * sizeof(T);
+  // every lane's strip: (depth + 1) stages x batch keys x (K, V) x 16 or 32 bytes
+  const size_t smem = (size_t)DEC_THREADS * (DEC_DEPTH + 1) * BATCH * 2 * 8 * sizeof(T);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<T, TPK>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 140 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<T, TPK, BATCH>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return launch_kernel(attention_decode_kernel<T, TPK>, grid, dim3(DEC_THREADS), smem, stream, 1,
-                       (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table,
-                       table_stride, request_of_row, positions, (T*)out, ld_out, num_kv_heads,
-                       num_heads / num_kv_heads, head_dim, page_size, scale, window, partial,
-                       tickets, (const T*)k_new, (const T*)v_new, ld_new,
-                       store ? (T*)const_cast<void*>(k_pages) : (T*)nullptr,
-                       store ? (T*)const_cast<void*>(v_pages) : (T*)nullptr, chunk_keys, status);
+  return launch_kernel_x(attention_decode_kernel<T, TPK, BATCH>, grid, dim3(DEC_THREADS), smem,
+                         stream, clustered ? splits : 1, (const T*)q, ld_q, (const T*)k_pages,
+                         (const T*)v_pages, block_table, table_stride, request_of_row, positions,
+                         (T*)out, ld_out, num_kv_heads, num_heads / num_kv_heads, head_dim,
+                         page_size, scale, window, partial, tickets, (const T*)k_new,
+                         (const T*)v_new, ld_new,
+                         store ? (T*)const_cast<void*>(k_pages) : (T*)nullptr,
+                         store ? (T*)const_cast<void*>(v_pages) : (T*)nullptr, clustered,
+                         page_shift);
 }
 
 template <typename T>
@@ -349,8 +472,8 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
                      int splits, float* partial, int* tickets, const void* k_new,
                      const void* v_new, int ld_new, int store, int* status,
                      cudaStream_t stream) {
+  (void)status;  // this kernel has no wait that could run out
   if (num_rows == 0) return AYK_OK;
-  if (status == nullptr) return AYK_BAD_ARGUMENT;
   if ((k_new == nullptr) != (v_new == nullptr) || (store && k_new == nullptr)) {
     return AYK_BAD_ARGUMENT;
   }
@@ -363,13 +486,14 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
       page_size < 1 || table_stride < 1 || window < 0 || splits < 1) {
     return AYK_BAD_ARGUMENT;
   }
-  if (head_dim < 8 || head_dim % 8) return AYK_BAD_ARGUMENT;
+  if (head_dim < 16 || head_dim % 16) return AYK_BAD_ARGUMENT;
   if (head_dim > 256 || num_heads > 65535 || num_rows > 65535 || splits > 1024) {
     return AYK_TOO_LARGE;
   }
-  if (splits > 1 && (partial == nullptr || tickets == nullptr)) return AYK_BAD_ARGUMENT;
+  if ((partial == nullptr) != (tickets == nullptr)) return AYK_BAD_ARGUMENT;
+  if (splits > 8 && partial == nullptr) return AYK_BAD_ARGUMENT;
   const size_t vec = 8 * sizeof(T);
-  if (((uintptr_t)k_pages % vec) || ((uintptr_t)v_pages % vec) || ((uintptr_t)q % vec) ||
+  if (((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16) || ((uintptr_t)q % vec) ||
       ((size_t)ld_q * sizeof(T)) % vec) {
     return AYK_BAD_ALIGNMENT;
   }
@@ -378,8 +502,7 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
   return launch_decode<T, TPK>(q, ld_q, k_pages, v_pages, block_table, table_stride,          \
                                request_of_row, positions, out, ld_out, num_rows, num_heads,   \
                                num_kv_heads, head_dim, page_size, scale, window, splits,      \
-                               partial, tickets, k_new, v_new, ld_new, store, status,    \
-                               stream)
+                               partial, tickets, k_new, v_new, ld_new, store, stream)
   if (frags <= 2) AYK_DECODE(2);
   if (frags <= 4) AYK_DECODE(4);
   if (frags <= 8) AYK_DECODE(8);
@@ -392,12 +515,20 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
 
 AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
 
-// type: 0 = float32, 1 = bfloat16. `partial` holds num_rows * num_heads * splits *
-// (head_dim + 2) floats and `tickets` num_rows * num_heads zeroed ints (both unused when
-// splits == 1). With k_new/v_new ([rows, kv_heads * head_dim], row stride ld_new) each row's
-// own key and value are read from there instead of the cache, and with `store` they are also
-// written into the row's cache slot (the step's KV store, fused). `status` is one device int
-// that a CTA sets to AYK_WAIT_TIMEOUT if a wait on its copies ran out.
+#ifdef AYK_DEC_TRACE
+// Development aid: cycle stamps of CTA (0, 0, 0) of the last launch.
+AYK_API int ayk_decode_trace(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, ayk::dec_trace, sizeof(long long) * 64);
+}
+#endif
+
+// type: 0 = float32, 1 = bfloat16. Up to 8 splits need no scratch (pass null for `partial`
+// and `tickets`); with scratch, `partial` holds num_rows * num_heads * splits * (head_dim + 2)
+// floats and `tickets` num_rows * num_heads zeroed ints. With k_new/v_new ([rows, kv_heads *
+// head_dim], row stride ld_new) each row's own key and value are read from there instead of
+// the cache, and with `store` they are also written into the row's cache slot (the step's KV
+// store, fused). `status` is unused (the kernel has no wait that could run out); it is kept
+// so that every attention entry point has the same tail of arguments.
 AYK_API int ayk_attention_decode(const void* q, int ld_q, const void* k_pages,
                                  const void* v_pages, const int* block_table, int table_stride,
                                  const int* request_of_row, const int* positions, void* out,

@@ -97,8 +97,8 @@ inline int& pdl_enabled() {
 }
 
 template <typename... KArgs, typename... Args>
-inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                         cudaStream_t stream, int cluster_y, Args... args) {
+inline int launch_kernel_dims(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, int cluster_x, int cluster_y, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
@@ -106,10 +106,10 @@ inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
   config.stream = stream;
   cudaLaunchAttribute attrs[2];
   int n = 0;
-  if (cluster_y > 1) {
+  if (cluster_x > 1 || cluster_y > 1) {
     attrs[n].id = cudaLaunchAttributeClusterDimension;
-    attrs[n].val.clusterDim.x = 1;
-    attrs[n].val.clusterDim.y = cluster_y;
+    attrs[n].val.clusterDim.x = cluster_x > 1 ? cluster_x : 1;
+    attrs[n].val.clusterDim.y = cluster_y > 1 ? cluster_y : 1;
     attrs[n].val.clusterDim.z = 1;
     ++n;
   }
@@ -124,6 +124,19 @@ inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
   if (e != cudaSuccess) return (int)e;
   e = cudaGetLastError();
   return e == cudaSuccess ? AYK_OK : (int)e;
+}
+
+// cluster of `cluster_y` CTAs along grid.y (1: no cluster)
+template <typename... KArgs, typename... Args>
+inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                         cudaStream_t stream, int cluster_y, Args... args) {
+  return launch_kernel_dims(kernel, grid, block, smem, stream, 1, cluster_y, args...);
+}
+// cluster of `cluster_x` CTAs along grid.x
+template <typename... KArgs, typename... Args>
+inline int launch_kernel_x(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                           cudaStream_t stream, int cluster_x, Args... args) {
+  return launch_kernel_dims(kernel, grid, block, smem, stream, cluster_x, 1, args...);
 }
 
 inline int launch_status() {

@@ -335,10 +335,15 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
 
 
 def decode_splits(num_rows: int, num_heads: int, max_kv_len: int) -> int:
-    """How many CTAs share one (request, head) of a decode step: enough to fill the GPU a few
-    times over, never less than 64 keys each."""
-    want = -(-592 // max(1, num_rows * num_heads))
-    return max(1, min(want, -(-max_kv_len // 64), 64))
+    """How many CTAs share one (request, head) of a decode step. Measured on a B200: the grid
+    should fill the GPU once (about 444 CTAs of this kernel are resident), a cluster merges
+    up to 8 shares on chip, and a warp wants at least 32 keys."""
+    fill = 444 // max(1, num_rows * num_heads)
+    enough_keys = max(1, max_kv_len // 128)
+    splits = max(1, min(fill, enough_keys, 8))
+    while splits & (splits - 1):  # a power of two
+        splits -= 1
+    return splits
 
 
 def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -349,9 +354,10 @@ def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
                      tickets: torch.Tensor | None = None, k_new: torch.Tensor | None = None,
                      v_new: torch.Tensor | None = None, store: bool = False) -> None:
     """Attention for steps whose every request brings one row (same contract as
-    :func:`attention`). ``splits`` CTAs share each (request, head); with more than one,
-    ``partial`` (float32, at least rows * heads * splits * (head_dim + 2)) and ``tickets``
-    (int32 zeros, at least rows * heads; left zero) are scratch. With ``k_new``/``v_new``
+    :func:`attention`). ``splits`` CTAs share each (request, head). Up to 8 splits merge on
+    chip (a thread-block cluster); given ``partial`` (float32, at least rows * heads * splits
+    * (head_dim + 2)) and ``tickets`` (int32 zeros, at least rows * heads; left zero) the
+    shares go through that scratch instead, which more than 8 splits require. With ``k_new``/``v_new``
     (``[rows, kv_heads * head_dim]``, column ranges of the projection output) each row's own
     key and value are taken from there, and with ``store`` the kernel also writes them into
     the row's cache slot, so no separate KV store runs."""
@@ -371,9 +377,11 @@ def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
             or n > request_of_row.shape[0] or n > positions.shape[0] or \
             v_pages.shape != k_pages.shape:
         raise BackendError(f"{op}: shapes do not fit")
-    if splits > 1:
-        if partial is None or tickets is None:
-            raise BackendError(f"{op}: more than one split needs scratch")
+    if splits > 8 and partial is None:
+        raise BackendError(f"{op}: more than 8 splits need scratch")
+    if (partial is None) != (tickets is None):
+        raise BackendError(f"{op}: partial and tickets come together")
+    if partial is not None and tickets is not None:
         _need(op, "partial", partial, torch.float32)
         _need(op, "tickets", tickets, torch.int32)
         if partial.numel() < n * num_heads * splits * (head_dim + 2) or \

@@ -113,7 +113,7 @@ class Attention(Mixer):
             reach = min(step.max_kv_len, self.window) if self.window else step.max_kv_len
             splits = ops.decode_splits(n, self.num_heads, reach)
             partial = tickets = None
-            if splits > 1:
+            if splits > 8:  # beyond a cluster's size the shares are merged through scratch
                 # rows * heads * splits never exceeds 592 + rows * heads (see decode_splits)
                 pairs = step.workspace.max_rows * self.num_heads
                 partial = step.workspace.buffer(
