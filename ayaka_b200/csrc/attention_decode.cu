@@ -22,6 +22,8 @@
 // Scratch: partial [requests * heads * splits * (head_dim + 2)] floats and one int ticket
 // per (request, head), zero before the first launch and left zero by every launch.
 // Cache layout: [page][kv_head][slot][head_dim]; block-table entry 0 = no page.
+#include <mutex>
+
 #include "tc_common.cuh"
 
 namespace ayk {
@@ -549,6 +551,87 @@ AYK_API int ayk_attention_decode(const void* q, int ld_q, const void* k_pages,
         q, ld_q, k_pages, v_pages, block_table, table_stride, request_of_row, positions, out,
         ld_out, num_rows, num_heads, num_kv_heads, head_dim, page_size, scale, window, splits,
         partial, tickets, k_new, v_new, ld_new, store, status, (cudaStream_t)stream);
+  }
+  return AYK_BAD_ARGUMENT;
+}
+
+// ---- an entry point that allocates nothing (see attention_decode_noalloc.h) ---------------
+#include "attention_decode_noalloc.h"
+
+namespace ayk {
+
+constexpr size_t NOALLOC_PARTIAL_FLOATS = size_t(1) << 20;  // 4 MiB of partial results
+constexpr size_t NOALLOC_TICKETS = size_t(1) << 14;         // one int per (row, head)
+constexpr size_t NOALLOC_BYTES = NOALLOC_PARTIAL_FLOATS * sizeof(float) +
+                                 NOALLOC_TICKETS * sizeof(int);
+
+// The scratch itself: part of the library's device image, so loading the library is what
+// reserves it. In host code this name is only a handle for cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char decode_scratch[NOALLOC_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+
+// The array's address on the current device, looked up once per device.
+static int noalloc_scratch(unsigned char** out) {
+  static std::mutex mu;
+  static unsigned char* address[NOALLOC_MAX_DEVICES] = {};
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= NOALLOC_MAX_DEVICES) return AYK_TOO_LARGE;
+  std::lock_guard<std::mutex> lock(mu);
+  if (address[device] == nullptr) {
+    void* found = nullptr;
+    e = cudaGetSymbolAddress(&found, decode_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (found == nullptr) return AYK_DRIVER;
+    address[device] = static_cast<unsigned char*>(found);
+  }
+  *out = address[device];
+  return AYK_OK;
+}
+
+}  // namespace ayk
+
+AYK_API void ayk_attention_decode_noalloc_limits(size_t* partial_floats, size_t* tickets) {
+  if (partial_floats != nullptr) *partial_floats = ayk::NOALLOC_PARTIAL_FLOATS;
+  if (tickets != nullptr) *tickets = ayk::NOALLOC_TICKETS;
+}
+
+AYK_API int ayk_attention_decode_noalloc(const void* q, int ld_q, const void* k_pages,
+                                         const void* v_pages, const int* block_table,
+                                         int table_stride, const int* request_of_row,
+                                         const int* positions, void* out, int ld_out,
+                                         int num_rows, int num_heads, int num_kv_heads,
+                                         int head_dim, int page_size, float scale, int window,
+                                         int splits, int type, void* stream) {
+  using namespace ayk;
+  if (num_rows == 0) return AYK_OK;
+  if (num_rows < 0 || num_heads < 1 || head_dim < 1 || splits < 1) return AYK_BAD_ARGUMENT;
+  const size_t pairs = (size_t)num_rows * (size_t)num_heads;
+  const size_t floats = pairs * (size_t)splits * (size_t)(head_dim + 2);
+  if (pairs > NOALLOC_TICKETS || floats > NOALLOC_PARTIAL_FLOATS) return AYK_TOO_LARGE;
+  unsigned char* base = nullptr;
+  const int found = noalloc_scratch(&base);
+  if (found != AYK_OK) return found;
+  float* partial = reinterpret_cast<float*>(base);
+  int* tickets = reinterpret_cast<int*>(base + NOALLOC_PARTIAL_FLOATS * sizeof(float));
+  cudaStream_t s = (cudaStream_t)stream;
+  // the tickets must start at zero whatever an earlier call (perhaps one that failed) left
+  cudaError_t e = cudaMemsetAsync(tickets, 0, pairs * sizeof(int), s);
+  if (e != cudaSuccess) return (int)e;
+  int unused_status = 0;  // the kernel never touches it
+  if (type == 0) {
+    return attention_decode<float>(q, ld_q, k_pages, v_pages, block_table, table_stride,
+                                   request_of_row, positions, out, ld_out, num_rows, num_heads,
+                                   num_kv_heads, head_dim, page_size, scale, window, splits,
+                                   partial, tickets, nullptr, nullptr, 0, 0, &unused_status, s);
+  }
+  if (type == 1) {
+    return attention_decode<__nv_bfloat16>(
+        q, ld_q, k_pages, v_pages, block_table, table_stride, request_of_row, positions, out,
+        ld_out, num_rows, num_heads, num_kv_heads, head_dim, page_size, scale, window, splits,
+        partial, tickets, nullptr, nullptr, 0, 0, &unused_status, s);
   }
   return AYK_BAD_ARGUMENT;
 }

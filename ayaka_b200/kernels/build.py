@@ -63,7 +63,7 @@ def _digest(name: str, defines: dict[str, int] | None = None) -> str:
     h = hashlib.sha256()
     h.update(" ".join([*_FLAGS, *_defines(defines)]).encode())
     h.update((CSRC / f"{name}.cu").read_bytes())
-    for header in sorted(CSRC.glob("*.cuh")):
+    for header in sorted([*CSRC.glob("*.cuh"), *CSRC.glob("*.h")]):
         h.update(header.name.encode())
         h.update(header.read_bytes())
     return h.hexdigest()[:16]
