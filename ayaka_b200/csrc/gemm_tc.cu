@@ -214,6 +214,228 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------
+// The same product as a persistent kernel: one CTA per SM walks over output tiles, with two
+// accumulators in tensor memory so that the epilogue of one tile runs under the main loop of
+// the next. Six warps: warp 0's elected thread feeds the shared-memory ring by TMA without
+// pausing between tiles, warp 1's issues the MMAs into accumulator (tile & 1), warps 2-5 are
+// the epilogue (warp w reads tensor-memory lanes 32 * (w % 4) ..). Barriers: full/empty per
+// ring stage, acc_full/acc_empty per accumulator. K is still walked 0 upward in blocks of 64
+// for every tile, so results equal the one-tile-per-CTA kernel's bit for bit.
+template <int BN, int STAGES>
+struct PersistentSmem {
+  static constexpr int B_BYTES = BN * TC_BK * 2;
+  static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], then the tmem slot and the flag
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
+  static constexpr int DYNAMIC = TOTAL + 1024;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                          const __grid_constant__ CUtensorMap map_w,
+                          const float* __restrict__ bias, void* __restrict__ out, int ldo, int M,
+                          int N, int K, int act, int mode, int vec_ok,
+                          int* __restrict__ status) {
+  using L = PersistentSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + TC_BK - 1) / TC_BK;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators (a power of two for BN = 64..256)
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // the four epilogue warps
+    }
+    *failed = 0;
+    mbar_fence_init();
+    tma_prefetch_map(&map_a);
+    tma_prefetch_map(&map_w);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+
+  // tile t -> (m tile, n tile): consecutive tiles share the weight tile and walk down the rows
+  auto tile_origin = [&](int t, int& m0, int& n0) {
+    n0 = (t / tiles_m) * BN;
+    m0 = (t % tiles_m) * TC_BM;
+  };
+
+  if (warp == 0 && lane == 0) {
+    // ---- producer: one continuous stream of k-blocks over all of this CTA's tiles
+    pdl_wait();
+    int it = 0;  // k-blocks issued so far
+    for (int t = blockIdx.x; t < num_tiles && *failed == 0; t += gridDim.x) {
+      int m0, n0;
+      tile_origin(t, m0, n0);
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) {
+          *failed = 1;
+          break;
+        }
+        uint8_t* a_tile = smem + s * L::STAGE_BYTES;
+        mbar_expect_tx(&full[s], L::STAGE_BYTES);
+        tma_load_2d(a_tile, &map_a, &full[s], kb * TC_BK, m0);
+        tma_load_2d(a_tile + TC_A_BYTES, &map_w, &full[s], kb * TC_BK, n0);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer
+    constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, BN);
+    int it = 0, local = 0;
+    for (int t = blockIdx.x; t < num_tiles && *failed == 0; t += gridDim.x, ++local) {
+      const int buf = local & 1;
+      // the accumulator must have been drained by the epilogue of two tiles ago
+      if (local >= 2 && !mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1)) {
+        *failed = 1;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(&full[s], (it / STAGES) & 1)) {
+          *failed = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint8_t* a_tile = smem + s * L::STAGE_BYTES;
+        const uint8_t* b_tile = a_tile + TC_A_BYTES;
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; ++k) {
+          umma_f16(acc, umma_desc_k128(a_tile, k * 32), umma_desc_k128(b_tile, k * 32), idesc,
+                   (kb | k) != 0);
+        }
+        umma_commit(&empty[s]);
+      }
+      if (!ok) break;
+      umma_commit(&acc_full[buf]);
+    }
+  } else if (warp >= 2) {
+    // ---- epilogue: four warps, each on its quarter of the tensor-memory lanes
+    pdl_wait();
+    const int quarter = warp & 3;
+    int local = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+      const int buf = local & 1;
+      int m0, n0;
+      tile_origin(t, m0, n0);
+      bool have = true;
+      if (lane == 0) have = mbar_wait(&acc_full[buf], (local >> 1) & 1);
+      have = __shfl_sync(0xffffffffu, have, 0);
+      if (!have || *failed != 0) {
+        if (lane == 0) *failed = 1;
+        break;
+      }
+      tc_fence_after();
+      const int m = m0 + quarter * 32 + lane;
+      const bool row_ok = m < M;
+      const uint32_t acc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int n = n0 + c * 32;
+        if (n >= N) break;  // uniform over the warp
+        uint32_t raw[32];
+        tmem_ld_32x32(acc + (uint32_t)(c * 32), raw);
+        tmem_ld_wait();
+        if (row_ok) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = __uint_as_float(raw[j]);
+            if (bias != nullptr && n + j < N) v[j] += __ldg(bias + n + j);
+          }
+          const bool full_chunk = n + 32 <= N;
+          if (mode == OUT_BF16) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = activate(v[j], act);
+            if (vec_ok && full_chunk) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 packed;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                packed.x = *reinterpret_cast<uint32_t*>(&h0);
+                packed.y = *reinterpret_cast<uint32_t*>(&h1);
+                packed.z = *reinterpret_cast<uint32_t*>(&h2);
+                packed.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(dst + j) = packed;
+              }
+            } else {
+              for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+            }
+          } else {
+            float* dst = reinterpret_cast<float*>(out) + (size_t)m * ldo + n;
+            if (mode == OUT_F32) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = activate(v[j], act);
+            }
+            if (vec_ok && full_chunk) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (mode == OUT_RESIDUAL_F32) {
+                  const float4 r = *reinterpret_cast<const float4*>(dst + j);
+                  o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+                }
+                *reinterpret_cast<float4*>(dst + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && n + j < N; ++j) {
+                dst[j] = mode == OUT_RESIDUAL_F32 ? dst[j] + v[j] : v[j];
+              }
+            }
+          }
+        }
+        __syncwarp();  // the next tcgen05.ld needs the whole warp
+      }
+      // this warp has read its lanes of the accumulator: hand it back
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  // ---- teardown ---------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*failed != 0 && threadIdx.x == 0) atomicExch(status, AYK_WAIT_TIMEOUT);
+  if (warp == 0) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // Few rows (decode): the weight is the 128-row operand and the tokens are the narrow one
 // ("swap A and B"): D[n, m] = sum_k W[n, k] * A[m, k], with m padded to MP in {16, 32, 64}.
 // A step with a handful of tokens is pure weight streaming, and N / 128 CTAs are too few to
@@ -626,6 +848,39 @@ int launch_gemm_tc(const void* a, int lda, const void* w, int ldw, const float* 
                        map_w, bias, out, ldo, M, N, K, act, mode, vec_ok, status);
 }
 
+template <int BN, int STAGES>
+int launch_gemm_tc_persistent(const void* a, int lda, const void* w, int ldw, const float* bias,
+                              void* out, int ldo, int M, int N, int K, int act, int mode,
+                              int* status, cudaStream_t stream) {
+  using L = PersistentSmem<BN, STAGES>;
+  CUtensorMap map_a, map_w;
+  int r = cached_map(a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BM, &map_a);
+  if (r != AYK_OK) return r;
+  r = cached_map(w, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN, &map_w);
+  if (r != AYK_OK) return r;
+  static bool configured = false;
+  static int num_sms = 0;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYNAMIC);
+    if (e != cudaSuccess) return (int)e;
+    int device = 0;
+    e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const size_t elem = mode == OUT_BF16 ? 2 : 4;
+  const int vec_ok = (((uintptr_t)out % 16) == 0 && ((size_t)ldo * elem) % 16 == 0) ? 1 : 0;
+  const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
+  if (tiles > 0x7fffffffLL) return AYK_TOO_LARGE;
+  const int grid = tiles < num_sms ? (int)tiles : num_sms;
+  return launch_kernel(gemm_tc_persistent_kernel<BN, STAGES>, dim3(grid), dim3(192), L::DYNAMIC,
+                       stream, 1, map_a, map_w, bias, out, ldo, M, N, K, act, mode, vec_ok,
+                       status);
+}
+
 template <int MP, int STAGES, bool LN, int MAXKB>
 int launch_gemm_tc_small(const void* a, int lda, const void* w, int ldw, const float* bias,
                          void* out, int ldo, int M, int N, int K, int act, int mode, int splits,
@@ -679,7 +934,8 @@ inline int pick_splits(int tile_n, int N, int M) {
 AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
 
 // mode: 0 = bf16 out with activation, 1 = fp32 out with activation, 2 = fp32 out += (residual).
-// tile_n: 64, 128 or 256 (0 = choose). `status` is one device int that a CTA sets to
+// tile_n: 0 = choose; 64, 128, 256 = one tile of that width per CTA; 1128, 1256 = the
+// persistent kernel with tiles 128 or 256 wide; negative = the few-rows kernel (see below). `status` is one device int that a CTA sets to
 // AYK_WAIT_TIMEOUT if a wait ran out; the host reads it when it checks a step.
 AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, const float* bias,
                              void* out, int ldo, int M, int N, int K, int act, int mode,
@@ -713,8 +969,28 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
     return launch_gemm_tc_small<64, 4, false, 0>(a, lda, w, ldw, bias, out, ldo, M, N, K, act,
                                                  mode, splits, status, none, s);
   }
-  if (tile_n == 0) tile_n = 256;  // measured best at GPT-2 XL's shapes (fewest smem bytes per flop)
+  if (tile_n == 0) {
+    // measured at GPT-2 XL's shapes: with more 128 x 256 tiles than SMs the persistent kernel
+    // wins (its epilogues hide under the next tile's main loop); with fewer, one tile per CTA
+    static int num_sms = 0;
+    if (num_sms == 0) {
+      int device = 0;
+      if (cudaGetDevice(&device) != cudaSuccess ||
+          cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device) !=
+              cudaSuccess) {
+        num_sms = 148;
+      }
+    }
+    const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + 255) / 256);
+    tile_n = tiles > num_sms ? 1256 : 256;
+  }
   switch (tile_n) {
+    case 1128:
+      return launch_gemm_tc_persistent<128, 6>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
+                                               status, s);
+    case 1256:
+      return launch_gemm_tc_persistent<256, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
+                                               status, s);
     case 64:
       return launch_gemm_tc<64, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
     case 128:
