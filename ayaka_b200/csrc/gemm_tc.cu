@@ -748,21 +748,31 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
       for (int p = 0; p < 8; ++p) {
         peer_base[p] = p < splits ? peer_address(partial + t, (uint32_t)p) : 0u;
       }
-      for (int j = 0; j < cols; ++j) {
-        const int m = rank * cols + j;
-        if (m >= M) break;
-        // all loads first (they are independent), then the sum in rank order
-        float v[8];
+      // four rows at a time: all of their loads are issued before the first sum, so the
+      // distributed-shared-memory latency is paid once per group, not once per load
+      for (int j0 = 0; j0 < cols; j0 += 4) {
+        float v[4][8];
 #pragma unroll
-        for (int p = 0; p < 8; ++p) {
-          v[p] = p < splits ? ld_cluster_f32(peer_base[p] + (uint32_t)(m * TC_BM * 4)) : 0.f;
-        }
-        float sum = v[0];
+        for (int jj = 0; jj < 4; ++jj) {
+          const int m = rank * cols + j0 + jj;
 #pragma unroll
-        for (int p = 1; p < 8; ++p) {
-          if (p < splits) sum += v[p];
+          for (int p = 0; p < 8; ++p) {
+            v[jj][p] = (p < splits && j0 + jj < cols && m < M)
+                           ? ld_cluster_f32(peer_base[p] + (uint32_t)(m * TC_BM * 4)) : 0.f;
+          }
         }
-        store_output(out, ldo, m, n, sum + b, mode, act);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const int m = rank * cols + j0 + jj;
+          if (j0 + jj < cols && m < M) {
+            float sum = v[jj][0];
+#pragma unroll
+            for (int p = 1; p < 8; ++p) {
+              if (p < splits) sum += v[jj][p];
+            }
+            store_output(out, ldo, m, n, sum + b, mode, act);
+          }
+        }
       }
     }
     cluster_sync_all();  // nobody leaves while a peer may still read its tile
@@ -963,10 +973,10 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
                                                    mode, splits, status, none, s);
     }
     if (M <= 32) {
-      return launch_gemm_tc_small<32, 5, false, 0>(a, lda, w, ldw, bias, out, ldo, M, N, K, act,
+      return launch_gemm_tc_small<32, 6, false, 0>(a, lda, w, ldw, bias, out, ldo, M, N, K, act,
                                                    mode, splits, status, none, s);
     }
-    return launch_gemm_tc_small<64, 4, false, 0>(a, lda, w, ldw, bias, out, ldo, M, N, K, act,
+    return launch_gemm_tc_small<64, 6, false, 0>(a, lda, w, ldw, bias, out, ldo, M, N, K, act,
                                                  mode, splits, status, none, s);
   }
   if (tile_n == 0) {
@@ -991,6 +1001,10 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
     case 1256:
       return launch_gemm_tc_persistent<256, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
                                                status, s);
+    case 16:
+      return launch_gemm_tc<16, 8>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
+    case 32:
+      return launch_gemm_tc<32, 8>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
     case 64:
       return launch_gemm_tc<64, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
     case 128:
