@@ -63,6 +63,59 @@ argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restri
   if (threadIdx.x == 0) out[blockIdx.x] = best;
 }
 
+// Two-stage argmax for steps where one CTA per row is too slow (a vocabulary of 50k floats is
+// 200 KB per row): stage 1 splits every row over `parts` CTAs that each leave (value, id) of
+// their slice; stage 2 folds the parts of a row. Ties go to the smaller id in both stages.
+__global__ void __launch_bounds__(256)
+argmax_parts_kernel(const float* __restrict__ logits, int ld, int vocab, int parts,
+                    float* __restrict__ part_value, int* __restrict__ part_id) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x, part = blockIdx.y;
+  const int span = (vocab + parts - 1) / parts;
+  const int lo = part * span;
+  const int hi = lo + span < vocab ? lo + span : vocab;
+  const float* src = logits + (size_t)row * ld;
+  float bv = -INFINITY;
+  int bi = vocab;
+  for (int c = lo + threadIdx.x; c < hi; c += blockDim.x) better(bv, bi, src[c], c);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    better(bv, bi, ov, oi);
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) better(bv, bi, sv[w], si[w]);
+    part_value[row * parts + part] = bv;
+    part_id[row * parts + part] = bi;
+  }
+}
+
+__global__ void __launch_bounds__(32)
+argmax_fold_kernel(const float* __restrict__ part_value, const int* __restrict__ part_id,
+                   int parts, int vocab, int* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  float bv = -INFINITY;
+  int bi = vocab;
+  for (int p = threadIdx.x; p < parts; p += 32) {
+    better(bv, bi, part_value[row * parts + p], part_id[row * parts + p]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    better(bv, bi, ov, oi);
+  }
+  if (threadIdx.x == 0) out[row] = bi < vocab ? bi : 0;
+}
+
 // ---- Philox-4x32-10 -------------------------------------------------------------------
 __device__ __forceinline__ uint32_t philox_word0(uint64_t seed, uint64_t position,
                                                  uint32_t stream, uint32_t sequence) {
@@ -367,6 +420,24 @@ AYK_API int ayk_argmax(const float* logits, int ld, int rows, int vocab, int* ou
   if (rows < 0 || vocab < 1 || ld < vocab) return AYK_BAD_ARGUMENT;
   return ayk::launch_kernel(ayk::argmax_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream,
                             1, logits, ld, vocab, out);
+}
+
+// The same result through two small kernels: `parts` CTAs per row, then a fold. `part_value`
+// and `part_id` hold rows * parts entries each (scratch, any contents).
+AYK_API int ayk_argmax_split(const float* logits, int ld, int rows, int vocab, int parts,
+                             float* part_value, int* part_id, int* out, void* stream) {
+  if (rows == 0) return AYK_OK;
+  if (rows < 0 || vocab < 1 || ld < vocab || parts < 1 || part_value == nullptr ||
+      part_id == nullptr) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (parts > 65535 || rows > 0x7fffffff / parts) return AYK_TOO_LARGE;
+  cudaStream_t s = (cudaStream_t)stream;
+  int r = ayk::launch_kernel(ayk::argmax_parts_kernel, dim3(rows, parts), dim3(256), 0, s, 1,
+                             logits, ld, vocab, parts, part_value, part_id);
+  if (r != AYK_OK) return r;
+  return ayk::launch_kernel(ayk::argmax_fold_kernel, dim3(rows), dim3(32), 0, s, 1,
+                            (const float*)part_value, (const int*)part_id, parts, vocab, out);
 }
 
 // temperature [rows] fp32; top_k [rows] int32 (<= 0: off) or null; top_p, min_p [rows] fp32 or

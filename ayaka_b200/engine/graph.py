@@ -75,12 +75,17 @@ class _Bucket:
             workspace=core.runner.workspace, bad_index=core.runner._bad_index,
             max_kv_len=core.model.spec.max_positions, decode_only=True)
         self.want_rows = view(self.o_want, size)
-        self.graph: torch.cuda.CUDAGraph | None = None
+        self.argmax_scratch = torch.zeros(2 * size * ops.ARGMAX_PARTS, device=core.device)
+        # one graph for steps whose rows are all greedy (argmax), one for any other step
+        self.graphs: dict[bool, torch.cuda.CUDAGraph] = {}
         self.kernels = 0
 
-    def launch_body(self, core: EngineCore) -> None:
+    def launch_body(self, core: EngineCore, greedy: bool) -> None:
         size, meta = self.size, self.meta
         logits = core.model.forward(self.step, core.runner.caches, self.want_rows, size)
+        if greedy:
+            ops.argmax(logits, self.out, rows=size, scratch=self.argmax_scratch)
+            return
         ops.sample(logits, meta[self.o_temperature:self.o_temperature + size].view(torch.float32),
                    meta[self.o_top_k:self.o_top_k + size],
                    meta[self.o_top_p:self.o_top_p + size].view(torch.float32),
@@ -132,31 +137,32 @@ class DecodeGraphs:
         bucket = self.bucket_for(count)
         self._fill(bucket, entries, rows)
         bucket.meta.copy_(bucket.staging, non_blocking=True)
-        if bucket.graph is None:
-            self._capture(bucket)
-        bucket.graph.replay()  # type: ignore[union-attr]
+        greedy = all(row.params.greedy for row in rows)
+        if greedy not in bucket.graphs:
+            self._capture(bucket, greedy)
+        bucket.graphs[greedy].replay()
         bucket.out_host.copy_(bucket.out, non_blocking=True)
         torch.cuda.current_stream(self.core.device).synchronize()
         self.replays += 1
         return bucket.out_host[:count].tolist()
 
-    def _capture(self, bucket: _Bucket) -> None:
+    def _capture(self, bucket: _Bucket, greedy: bool) -> None:
         core = self.core
         with torch.cuda.device(core.device):
             # twice without capture: allocates the workspace, builds and configures kernels
             side = torch.cuda.Stream(core.device)
             side.wait_stream(torch.cuda.current_stream(core.device))
             with torch.cuda.stream(side):
-                bucket.launch_body(core)
-                bucket.launch_body(core)
+                bucket.launch_body(core, greedy)
+                bucket.launch_body(core, greedy)
             torch.cuda.current_stream(core.device).wait_stream(side)
             torch.cuda.synchronize(core.device)
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
             with torch.cuda.graph(graph):
-                bucket.launch_body(core)
+                bucket.launch_body(core, greedy)
             bucket.kernels = ops.launch_count() - before
-            bucket.graph = graph
+            bucket.graphs[greedy] = graph
 
     def _fill(self, bucket: _Bucket, entries: object, rows: list[SampleRow]) -> None:
         manager = self.core.manager

@@ -39,6 +39,7 @@ class Sampler:
         self._dev = torch.zeros(8 * max_rows, dtype=torch.int32, device=device)
         self._out = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self._out_host = torch.empty(max_rows, dtype=torch.int32).pin_memory()
+        self._argmax_scratch = torch.zeros(2 * max_rows * ops.ARGMAX_PARTS, device=device)
 
     def sample(self, logits: torch.Tensor, rows: Sequence[SampleRow]) -> list[int]:
         """Pick one token per row of ``logits`` (``[len(rows), vocab]`` fp32)."""
@@ -48,7 +49,7 @@ class Sampler:
         if count > self.max_rows or logits.shape[0] < count:
             raise ValueError("more rows than the sampler was built for")
         if all(row.params.greedy for row in rows):
-            ops.argmax(logits, self._out, rows=count)
+            ops.argmax(logits, self._out, rows=count, scratch=self._argmax_scratch)
         else:
             n = self.max_rows
             host = self._host.numpy()

@@ -540,3 +540,10 @@ def test_argmax_smallest_id_on_ties():
     expected = [plain.argmax_smallest_id(torch.nan_to_num(row, nan=-1e30)) for row in logits.cpu()]
     assert out.tolist() == expected
     assert out.tolist()[:4] == [77, 50256, 0, 0]
+    split = torch.full((6,), -1, dtype=torch.int32, device=DEV)
+    scratch = torch.full((2 * 6 * ops.ARGMAX_PARTS,), float("nan"), device=DEV)
+    ops.argmax(logits, split, scratch=scratch)  # the two-stage version
+    assert split.tolist() == expected
+    tiny = torch.tensor([[3.0, 5.0, 5.0]], device=DEV)  # fewer columns than parts
+    ops.argmax(tiny, split, rows=1, scratch=scratch)
+    assert int(split[0]) == 1
