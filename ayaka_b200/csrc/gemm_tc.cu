@@ -28,6 +28,11 @@ constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;
 
 enum OutMode : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_RESIDUAL_F32 = 2 };
 
+// tensor-memory columns to allocate for an accumulator `n` wide: a power of two, at least 32
+__host__ __device__ constexpr uint32_t tc_tmem_cols(int n) {
+  return n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : (n <= 256 ? 256 : 512)));
+}
+
 template <int BN, int STAGES>
 struct TcSmem {
   static constexpr int B_BYTES = BN * TC_BK * 2;
@@ -68,7 +73,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tma_prefetch_map(&map_w);
   }
   if (warp == 0) {
-    tmem_alloc(tmem_slot, BN < 32 ? 32 : BN);
+    tmem_alloc(tmem_slot, tc_tmem_cols(BN));
     tmem_relinquish();
   }
   tc_fence_before();
@@ -210,7 +215,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     __syncthreads();
   }
-  if (warp == 0) tmem_dealloc(tmem_base, BN < 32 ? 32 : BN);
+  if (warp == 0) tmem_dealloc(tmem_base, tc_tmem_cols(BN));
 }
 
 // ---------------------------------------------------------------------------------------
@@ -252,7 +257,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
   const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + TC_BK - 1) / TC_BK;
-  constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators (a power of two for BN = 64..256)
+  // two accumulators; the allocation is a power of two, the second starts at column BN
+  constexpr uint32_t TMEM_COLS = 2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512));
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -285,7 +291,19 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
   };
 
   if (warp == 0 && lane == 0) {
-    // ---- producer: one continuous stream of k-blocks over all of this CTA's tiles
+    // ---- producer: one continuous stream of k-blocks over all of this CTA's tiles. The
+    // weight tiles of the first stages do not depend on the kernel ahead: they start before
+    // the dependency wait, the activations after it.
+    int ahead = 0;
+    if (blockIdx.x < num_tiles) {
+      int m0, n0;
+      tile_origin(blockIdx.x, m0, n0);
+      ahead = num_kb < STAGES ? num_kb : STAGES;
+      for (int kb = 0; kb < ahead; ++kb) {
+        mbar_expect_tx(&full[kb], L::STAGE_BYTES);
+        tma_load_2d(smem + kb * L::STAGE_BYTES + TC_A_BYTES, &map_w, &full[kb], kb * TC_BK, n0);
+      }
+    }
     pdl_wait();
     int it = 0;  // k-blocks issued so far
     for (int t = blockIdx.x; t < num_tiles && *failed == 0; t += gridDim.x) {
@@ -293,14 +311,16 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
       tile_origin(t, m0, n0);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % STAGES;
-        if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) {
-          *failed = 1;
-          break;
-        }
         uint8_t* a_tile = smem + s * L::STAGE_BYTES;
-        mbar_expect_tx(&full[s], L::STAGE_BYTES);
+        if (it >= ahead) {
+          if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) {
+            *failed = 1;
+            break;
+          }
+          mbar_expect_tx(&full[s], L::STAGE_BYTES);
+          tma_load_2d(a_tile + TC_A_BYTES, &map_w, &full[s], kb * TC_BK, n0);
+        }
         tma_load_2d(a_tile, &map_a, &full[s], kb * TC_BK, m0);
-        tma_load_2d(a_tile + TC_A_BYTES, &map_w, &full[s], kb * TC_BK, n0);
       }
     }
   } else if (warp == 1 && lane == 0) {
@@ -944,8 +964,8 @@ inline int pick_splits(int tile_n, int N, int M) {
 AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
 
 // mode: 0 = bf16 out with activation, 1 = fp32 out with activation, 2 = fp32 out += (residual).
-// tile_n: 0 = choose; 64, 128, 256 = one tile of that width per CTA; 1128, 1256 = the
-// persistent kernel with tiles 128 or 256 wide; negative = the few-rows kernel (see below). `status` is one device int that a CTA sets to
+// tile_n: 0 = choose; 32, 64, 128, 192, 256 = one tile of that width per CTA; 1128, 1192, 1256 = the
+// persistent kernel with tiles 128, 192 or 256 wide; negative = the few-rows kernel (see below). `status` is one device int that a CTA sets to
 // AYK_WAIT_TIMEOUT if a wait ran out; the host reads it when it checks a step.
 AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, const float* bias,
                              void* out, int ldo, int M, int N, int K, int act, int mode,
@@ -991,18 +1011,34 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
         num_sms = 148;
       }
     }
-    const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + 255) / 256);
-    tile_n = tiles > num_sms ? 1256 : 256;
+    // tile width 256, 192 or 128: the one that needs the least (rounds over the SMs) x (work
+    // of a tile); one tile per CTA while everything fits one round, else the persistent kernel
+    const long long tiles_m = (M + TC_BM - 1) / TC_BM;
+    long long best_cost = -1;
+    int best_bn = 256;
+    for (int bn : {256, 192, 128}) {
+      const long long tiles = tiles_m * ((N + bn - 1) / bn);
+      const long long cost = ((tiles + num_sms - 1) / num_sms) * bn;
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        best_bn = bn;
+      }
+    }
+    const long long tiles = tiles_m * ((N + best_bn - 1) / best_bn);
+    tile_n = tiles > num_sms ? 1000 + best_bn : best_bn;
   }
   switch (tile_n) {
+    case 192:
+      return launch_gemm_tc<192, 5>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
+    case 1192:
+      return launch_gemm_tc_persistent<192, 5>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
+                                               status, s);
     case 1128:
       return launch_gemm_tc_persistent<128, 6>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
                                                status, s);
     case 1256:
       return launch_gemm_tc_persistent<256, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
                                                status, s);
-    case 16:
-      return launch_gemm_tc<16, 8>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
     case 32:
       return launch_gemm_tc<32, 8>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
     case 64:

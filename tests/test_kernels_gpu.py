@@ -136,7 +136,7 @@ def test_linear_bfloat16(kernel, m, n, k):
         gemm_tc.check_status(a.device)
 
 
-@pytest.mark.parametrize("tile_n", [64, 128, 256, 1128, 1256])
+@pytest.mark.parametrize("tile_n", [32, 64, 128, 192, 256, 1128, 1192, 1256])
 def test_linear_tcgen05_tiles_and_strides(tile_n):
     """Every tile width, operands that are column ranges of wider buffers, rows limited."""
     ops = _ops()
