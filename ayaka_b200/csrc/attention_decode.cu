@@ -171,7 +171,9 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
 
   DEC_MARK(0);
   pdl_launch_dependents();
-  pdl_wait();
+  // Before the wait for the kernel ahead, only what no kernel of this step writes is touched:
+  // the step's metadata (copied in before the step's first kernel) and the keys and values
+  // of earlier steps. The queries, the step's own key and value, and every store come after.
   const int split = blockIdx.x, splits = gridDim.x;
   const int head = blockIdx.y, num_heads = gridDim.y;
   const int row = blockIdx.z;
@@ -179,14 +181,11 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
   const int sub = lane % TPK;   // which 8 elements of head_dim
   const int slot = lane / TPK;  // which key of a pass
   const bool dims_ok = sub * 8 < head_dim;
-  // the three loads every CTA starts with, issued together
   const int req = request_of_row[row];
   const int pos = positions[row];
-  Raw8<T> q_raw;
-  q_raw.zero();
-  if (dims_ok) q_raw.fetch(q + (size_t)row * ld_q + (size_t)head * head_dim + sub * 8);
   T* dst = out + (size_t)row * ld_out + (size_t)head * head_dim;
   if (req < 0) {  // a padding row: zeros, no scratch, no ticket
+    pdl_wait();
     if (split == 0) {
       for (int d = tid; d < head_dim; d += DEC_THREADS) stf(dst + d, 0.f);
     }
@@ -203,10 +202,6 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
   const int k_hi = k_lo + share < pos + 1 ? k_lo + share : pos + 1;
   const int* table = block_table + (size_t)req * table_stride;
 
-  float qf[8];
-  q_raw.widen(qf);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) qf[i] *= scale;
   // key -> (page index, slot): a shift and a mask when the page size is a power of two (an
   // integer division costs more instructions than all the arithmetic on a key)
   const int page_mask = page_size - 1;
@@ -275,10 +270,29 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
   };
   DEC_MARK(1);
   const int num_batches = k_hi > k_lo ? (k_hi - k_lo + STEP - 1) / STEP : 0;
+  // The first batches start before the wait. This step's token (position pos, the last key of
+  // the share that holds it, so in that share's last batch) is written during this step, by
+  // this kernel or by the one that fills the cache this run reads: its batch waits.
+  const bool newest_here = pos >= k_lo && pos < k_hi;
+  const int early = newest_here ? num_batches - 1 : num_batches;
 #pragma unroll
   for (int b = 0; b < DEC_DEPTH; ++b) {
-    if (b < num_batches) issue(k_lo + b * STEP, b); else cp_async_commit_group();
+    if (b < early) issue(k_lo + b * STEP, b);
   }
+  pdl_wait();
+  Raw8<T> q_raw;
+  q_raw.zero();
+  if (dims_ok) q_raw.fetch(q + (size_t)row * ld_q + (size_t)head * head_dim + sub * 8);
+#pragma unroll
+  for (int b = 0; b < DEC_DEPTH; ++b) {
+    if (b >= early) {
+      if (b < num_batches) issue(k_lo + b * STEP, b); else cp_async_commit_group();
+    }
+  }
+  float qf[8];
+  q_raw.widen(qf);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) qf[i] *= scale;
   for (int b = 0; b < num_batches; ++b) {
     const int base = k_lo + b * STEP;
     const int stage = b % (DEC_DEPTH + 1);

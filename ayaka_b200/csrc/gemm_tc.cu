@@ -465,20 +465,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
 // r*MP/S .. (r+1)*MP/S over all peers through distributed shared memory in rank order 0..S-1
 // (a fixed order: the result does not change from run to run), applies the epilogue and
 // stores. Thread t owns output column n0 + t, so a warp's stores are contiguous.
-// With LN (the fused LayerNorm): the activation tile is not copied by TMA but computed by the
-// CTA from the fp32 residual stream — mean and variance of each row over the whole width,
-// then (x - mean) * rstd * gamma + beta for the CTA's own K range, rounded to bf16 and written
-// into shared memory in the same 128-byte-swizzled layout TMA would have produced. The
-// stages then hold weight tiles only, and the CTA's whole K range of activations (at most
-// MAXKB blocks of 64) stays resident.
-template <int MP, int STAGES, bool LN = false, int MAXKB = 0>
+template <int MP, int STAGES>
 struct SmallSmem {
   static constexpr int W_BYTES = TC_BM * TC_BK * 2;
   static constexpr int A_BYTES = MP * TC_BK * 2;
-  static constexpr int STAGE_BYTES = LN ? W_BYTES : W_BYTES + A_BYTES;
-  static constexpr int A_REGION_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int A_REGION_BYTES = LN ? MAXKB * A_BYTES : 0;
-  static constexpr int PARTIAL_OFFSET = A_REGION_OFFSET + A_REGION_BYTES;
+  static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
+  static constexpr int PARTIAL_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int PARTIAL_BYTES = MP * TC_BM * 4;
   static constexpr int BAR_OFFSET = PARTIAL_OFFSET + PARTIAL_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16;
@@ -498,24 +490,13 @@ __device__ __forceinline__ void store_output(void* out, int ldo, int m, int n, f
   }
 }
 
-constexpr int LN_MAX_K = 2048;  // widest row the fused LayerNorm holds in registers
-
-struct LnArgs {
-  const float* x;      // fp32 rows to normalise
-  int ld_x;
-  const int* rows;     // row m of the product normalises x[rows[m]] (null: x[m])
-  const float* gamma;
-  const float* beta;   // may be null
-  float eps;
-};
-
-template <int MP, int STAGES, bool LN, int MAXKB>
+template <int MP, int STAGES>
 __global__ void __launch_bounds__(128)
 gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
                      const __grid_constant__ CUtensorMap map_a, const float* __restrict__ bias,
                      void* __restrict__ out, int ldo, int M, int N, int K, int act, int mode,
-                     int kb_per_split, int* __restrict__ status, LnArgs ln) {
-  using L = SmallSmem<MP, STAGES, LN, MAXKB>;
+                     int kb_per_split, int* __restrict__ status) {
+  using L = SmallSmem<MP, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
   float* partial = reinterpret_cast<float*>(smem + L::PARTIAL_OFFSET);
@@ -565,127 +546,19 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
       mbar_expect_tx(&full[i], L::STAGE_BYTES);
       tma_load_2d(w_tile, &map_w, &full[i], (kb_lo + i) * TC_BK, n0);
     }
-    if (!LN) {
-      pdl_wait();
-      for (int i = 0; i < my_kb; ++i) {
-        const int s = i % STAGES;
-        uint8_t* w_tile = smem + s * L::STAGE_BYTES;
-        if (i >= STAGES) {
-          if (!mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) {
-            *failed = 1;
-            break;
-          }
-          mbar_expect_tx(&full[s], L::STAGE_BYTES);
-          tma_load_2d(w_tile, &map_w, &full[s], (kb_lo + i) * TC_BK, n0);
-        }
-        tma_load_2d(w_tile + L::W_BYTES, &map_a, &full[s], (kb_lo + i) * TC_BK, 0);
-        issued = i + 1;
-      }
-    } else {
-      issued = ahead;
-    }
-  }
-  if (LN) {
-    // every thread: wait for the kernel ahead, then normalise this CTA's K range into shared
     pdl_wait();
-    uint8_t* a_region = smem + L::A_REGION_OFFSET;
-    const int k_lo = kb_lo * TC_BK;
-    const int k_hi = kb_hi * TC_BK;  // may pass K: the tail is zero-filled
-    // One warp per row. The row (at most LN_MAX_K = 2048 wide) is fetched once, all loads in
-    // flight together, and stays in registers for the mean, the variance about that mean and
-    // the normalised values: one memory round trip per row on the kernel's critical path.
-    for (int m = warp; m < M; m += 4) {
-      const float* src = ln.x + (size_t)(ln.rows != nullptr ? ln.rows[m] : m) * ln.ld_x;
-      float4 held[LN_MAX_K / 128];
-#pragma unroll
-      for (int i = 0; i < LN_MAX_K / 128; ++i) {
-        const int c = i * 128 + lane * 4;
-        held[i] = c < K ? *reinterpret_cast<const float4*>(src + c)
-                        : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-      float sum = 0.f;
-#pragma unroll
-      for (int i = 0; i < LN_MAX_K / 128; ++i) {
-        sum += (held[i].x + held[i].y) + (held[i].z + held[i].w);
-      }
-      const float mean = warp_sum(sum) / (float)K;
-      float sq = 0.f;
-#pragma unroll
-      for (int i = 0; i < LN_MAX_K / 128; ++i) {
-        if (i * 128 + lane * 4 < K) {
-          const float a = held[i].x - mean, b = held[i].y - mean;
-          const float c = held[i].z - mean, d = held[i].w - mean;
-          sq += (a * a + b * b) + (c * c + d * d);
-        }
-      }
-      const float rstd = rsqrtf(warp_sum(sq) / (float)K + ln.eps);
-      // this CTA's K range: lane pairs own 16-byte chunks (8 elements = two float4)
-#pragma unroll
-      for (int i = 0; i < LN_MAX_K / 128; ++i) {
-        const int c = i * 128 + lane * 4;  // this lane's 4 elements
-        // partner lane (lane ^ 1) holds the other half of the 8-element chunk
-        const float4 mine = held[i];
-        float4 other;
-        other.x = __shfl_xor_sync(0xffffffffu, mine.x, 1);
-        other.y = __shfl_xor_sync(0xffffffffu, mine.y, 1);
-        other.z = __shfl_xor_sync(0xffffffffu, mine.z, 1);
-        other.w = __shfl_xor_sync(0xffffffffu, mine.w, 1);
-        const int k = c & ~7;  // start of the chunk
-        if ((lane & 1) == 0 && k >= k_lo && k < k_hi) {
-          uint4 packed = make_uint4(0u, 0u, 0u, 0u);
-          if (k < K) {
-            const float4 g0 = __ldg(reinterpret_cast<const float4*>(ln.gamma + k));
-            const float4 g1 = __ldg(reinterpret_cast<const float4*>(ln.gamma + k + 4));
-            float v[8];
-            v[0] = (mine.x - mean) * rstd * g0.x; v[1] = (mine.y - mean) * rstd * g0.y;
-            v[2] = (mine.z - mean) * rstd * g0.z; v[3] = (mine.w - mean) * rstd * g0.w;
-            v[4] = (other.x - mean) * rstd * g1.x; v[5] = (other.y - mean) * rstd * g1.y;
-            v[6] = (other.z - mean) * rstd * g1.z; v[7] = (other.w - mean) * rstd * g1.w;
-            if (ln.beta != nullptr) {
-              const float4 b0 = __ldg(reinterpret_cast<const float4*>(ln.beta + k));
-              const float4 b1 = __ldg(reinterpret_cast<const float4*>(ln.beta + k + 4));
-              v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-              v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
-            }
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
-            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
-            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
-            packed.x = *reinterpret_cast<uint32_t*>(&h0);
-            packed.y = *reinterpret_cast<uint32_t*>(&h1);
-            packed.z = *reinterpret_cast<uint32_t*>(&h2);
-            packed.w = *reinterpret_cast<uint32_t*>(&h3);
-          }
-          const int local = k - k_lo;
-          const int kb = local / TC_BK, chunk = (local % TC_BK) / 8;
-          uint8_t* dst = a_region + kb * L::A_BYTES + m * 128 + ((chunk ^ (m & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = packed;
-        }
-      }
-      // columns of this CTA's last block that lie past K (K is no multiple of 64): zeros
-      for (int k = ((K + 7) & ~7) + lane * 8; k < k_hi; k += 256) {
-        if (k >= k_lo) {
-          const int local = k - k_lo;
-          const int kb = local / TC_BK, chunk = (local % TC_BK) / 8;
-          *reinterpret_cast<uint4*>(a_region + kb * L::A_BYTES + m * 128 +
-                                    ((chunk ^ (m & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
-        }
-      }
-    }
-    // make the generic-proxy writes visible to the tensor core's (async proxy) reads
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-  }
-  if (LN && warp == 0 && lane == 0) {
-    // the rest of the weight tiles, as stages come free
-    for (int i = issued; i < my_kb; ++i) {
+    for (int i = 0; i < my_kb; ++i) {
       const int s = i % STAGES;
-      if (!mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) {
-        *failed = 1;
-        break;
+      uint8_t* w_tile = smem + s * L::STAGE_BYTES;
+      if (i >= STAGES) {
+        if (!mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) {
+          *failed = 1;
+          break;
+        }
+        mbar_expect_tx(&full[s], L::STAGE_BYTES);
+        tma_load_2d(w_tile, &map_w, &full[s], (kb_lo + i) * TC_BK, n0);
       }
-      mbar_expect_tx(&full[s], L::STAGE_BYTES);
-      tma_load_2d(smem + s * L::STAGE_BYTES, &map_w, &full[s], (kb_lo + i) * TC_BK, n0);
+      tma_load_2d(w_tile + L::W_BYTES, &map_a, &full[s], (kb_lo + i) * TC_BK, 0);
       issued = i + 1;
     }
   }
@@ -701,8 +574,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
       }
       tc_fence_after();
       const uint8_t* w_tile = smem + s * L::STAGE_BYTES;
-      const uint8_t* a_tile = LN ? smem + L::A_REGION_OFFSET + i * L::A_BYTES
-                                 : w_tile + L::W_BYTES;
+      const uint8_t* a_tile = w_tile + L::W_BYTES;
 #pragma unroll
       for (int k = 0; k < TC_BK / 16; ++k) {
         umma_f16(tmem_base, umma_desc_k128(w_tile, k * 32), umma_desc_k128(a_tile, k * 32),
@@ -911,23 +783,19 @@ int launch_gemm_tc_persistent(const void* a, int lda, const void* w, int ldw, co
                        status);
 }
 
-template <int MP, int STAGES, bool LN, int MAXKB>
+template <int MP, int STAGES>
 int launch_gemm_tc_small(const void* a, int lda, const void* w, int ldw, const float* bias,
                          void* out, int ldo, int M, int N, int K, int act, int mode, int splits,
-                         int* status, LnArgs ln, cudaStream_t stream) {
-  using L = SmallSmem<MP, STAGES, LN, MAXKB>;
+                         int* status, cudaStream_t stream) {
+  using L = SmallSmem<MP, STAGES>;
   CUtensorMap map_a, map_w;
   int r = cached_map(w, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, TC_BM, &map_w);
   if (r != AYK_OK) return r;
-  if (LN) {
-    map_a = map_w;  // unused by the kernel
-  } else {
-    r = cached_map(a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, MP, &map_a);
-    if (r != AYK_OK) return r;
-  }
+  r = cached_map(a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, MP, &map_a);
+  if (r != AYK_OK) return r;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_small_kernel<MP, STAGES, LN, MAXKB>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_small_kernel<MP, STAGES>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYNAMIC);
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -935,15 +803,11 @@ int launch_gemm_tc_small(const void* a, int lda, const void* w, int ldw, const f
   const int num_kb = (K + TC_BK - 1) / TC_BK;
   if (splits < 1) splits = 1;
   while (splits > 1 && (splits > num_kb || splits > 8 || MP % splits)) splits >>= 1;
-  if (LN) {  // the CTA's whole K range of activations must fit its shared-memory region
-    while (splits < 8 && (num_kb + splits - 1) / splits > MAXKB) splits <<= 1;
-    if ((num_kb + splits - 1) / splits > MAXKB || MP % splits) return AYK_TOO_LARGE;
-  }
   const int kb_per_split = (num_kb + splits - 1) / splits;
-  return launch_kernel(gemm_tc_small_kernel<MP, STAGES, LN, MAXKB>,
+  return launch_kernel(gemm_tc_small_kernel<MP, STAGES>,
                        dim3((N + TC_BM - 1) / TC_BM, splits, 1), dim3(128), L::DYNAMIC, stream,
                        splits, map_w, map_a, bias, out, ldo, M, N, K, act, mode, kb_per_split,
-                       status, ln);
+                       status);
 }
 
 inline int pick_splits(int tile_n, int N, int M) {
@@ -987,17 +851,16 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
   if (tile_n < 0) {
     if (M > 64) return AYK_BAD_ARGUMENT;
     const int splits = pick_splits(tile_n, N, M);
-    const LnArgs none = {nullptr, 0, nullptr, nullptr, nullptr, 0.f};
     if (M <= 16) {
-      return launch_gemm_tc_small<16, 5, false, 0>(a, lda, w, ldw, bias, out, ldo, M, N, K, act,
-                                                   mode, splits, status, none, s);
+      return launch_gemm_tc_small<16, 5>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
+                                         splits, status, s);
     }
     if (M <= 32) {
-      return launch_gemm_tc_small<32, 6, false, 0>(a, lda, w, ldw, bias, out, ldo, M, N, K, act,
-                                                   mode, splits, status, none, s);
+      return launch_gemm_tc_small<32, 6>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
+                                         splits, status, s);
     }
-    return launch_gemm_tc_small<64, 6, false, 0>(a, lda, w, ldw, bias, out, ldo, M, N, K, act,
-                                                 mode, splits, status, none, s);
+    return launch_gemm_tc_small<64, 6>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
+                                       splits, status, s);
   }
   if (tile_n == 0) {
     // measured at GPT-2 XL's shapes: with more 128 x 256 tiles than SMs the persistent kernel
@@ -1050,35 +913,4 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
     default:
       return AYK_BAD_ARGUMENT;
   }
-}
-
-// The same product for at most 16 rows of width at most 2048 with the LayerNorm of the input
-// fused in (more rows would make every CTA repeat too much of the norm):
-// out = act(LayerNorm(x[rows]) @ W^T + bias). x is the fp32 residual stream (row stride ld_x, a
-// multiple of 4), rows an optional gather index, gamma/beta fp32 [K]. K must be a multiple of
-// 8 (AYK_TOO_LARGE beyond the limits: run the norm as its own kernel). splits: 0 = choose, else the number of K splits (1, 2, 4 or 8).
-AYK_API int ayk_gemm_bf16_tc_ln(const float* x, int ld_x, const int* rows, const float* gamma,
-                                const float* beta, float eps, const void* w, int ldw,
-                                const float* bias, void* out, int ldo, int M, int N, int K,
-                                int act, int mode, int splits, int* status, void* stream) {
-  using namespace ayk;
-  if (M == 0 || N == 0) return AYK_OK;
-  if (M < 0 || N < 0 || K < 1 || ld_x < K || ldw < K || ldo < N || status == nullptr ||
-      x == nullptr || gamma == nullptr || !(eps > 0.f)) {
-    return AYK_BAD_ARGUMENT;
-  }
-  if (M > 16 || K > LN_MAX_K) return AYK_TOO_LARGE;
-  if (mode < OUT_BF16 || mode > OUT_RESIDUAL_F32 || act < ACT_NONE || act > ACT_GELU_ERF ||
-      (mode == OUT_RESIDUAL_F32 && act != ACT_NONE)) {
-    return AYK_BAD_ARGUMENT;
-  }
-  if (((uintptr_t)w % 16) || (ldw % 8) || (K % 8) || ((uintptr_t)x % 16) || (ld_x % 4) ||
-      ((uintptr_t)gamma % 16) || ((uintptr_t)beta % 16)) {
-    return AYK_BAD_ALIGNMENT;
-  }
-  const LnArgs ln = {x, ld_x, rows, gamma, beta, eps};
-  const int want = splits > 0 ? splits : pick_splits(-1, N, M);
-  cudaStream_t s = (cudaStream_t)stream;
-  return launch_gemm_tc_small<16, 4, true, 13>(nullptr, 0, w, ldw, bias, out, ldo, M, N, K, act,
-                                               mode, want, status, ln, s);
 }

@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_int, c_void_p
 
 import torch
 
@@ -61,44 +61,3 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
                 c_void_p(status_word(a.device).data_ptr()),
                 c_void_p(torch.cuda.current_stream().cuda_stream))
     check(status, "linear (tcgen05)")
-
-
-#: the fused-LayerNorm kernel's limits: rows of a step, width of a row
-LN_MAX_ROWS, LN_MAX_WIDTH = 4, 2048
-
-
-def can_fuse_norm(x: torch.Tensor, weight: torch.Tensor, gamma: torch.Tensor,
-                  beta: torch.Tensor | None, rows: int) -> bool:
-    """Whether ``linear_normed_bf16`` should take these operands: the kernel allows 16 rows no
-    wider than 2048, but every CTA normalises all rows itself and, measured on a B200, that
-    beats a separate norm kernel only up to 4 rows; plus the alignments of its vector loads."""
-    if not 0 < rows <= LN_MAX_ROWS or weight.dtype != torch.bfloat16 or \
-            x.dtype != torch.float32:
-        return False
-    k = weight.shape[1]
-    return (k % 8 == 0 and k <= LN_MAX_WIDTH and x.stride(0) % 4 == 0
-            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
-            and weight.stride(0) % 8 == 0 and gamma.data_ptr() % 16 == 0
-            and (beta is None or beta.data_ptr() % 16 == 0))
-
-
-def linear_normed_bf16(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor | None,
-                       eps: float, weight: torch.Tensor, bias: torch.Tensor | None,
-                       out: torch.Tensor, rows: int, activation: int,
-                       row_index: torch.Tensor | None = None, splits: int = 0) -> None:
-    """``out = act(LayerNorm(x[row_index]) @ weight.T + bias)`` in one kernel (few rows)."""
-    from ayaka_b200.kernels import ops
-
-    n, k = weight.shape
-    mode = 0 if out.dtype == torch.bfloat16 else 1
-    ops._launches += 1
-    fn = library("gemm_tc").ayk_gemm_bf16_tc_ln
-    status = fn(c_void_p(x.data_ptr()), c_int(x.stride(0)),
-                c_void_p(0 if row_index is None else row_index.data_ptr()),
-                c_void_p(gamma.data_ptr()), c_void_p(0 if beta is None else beta.data_ptr()),
-                c_float(eps), c_void_p(weight.data_ptr()), c_int(weight.stride(0)),
-                c_void_p(0 if bias is None else bias.data_ptr()), c_void_p(out.data_ptr()),
-                c_int(out.stride(0)), c_int(rows), c_int(n), c_int(k), c_int(activation),
-                c_int(mode), c_int(splits), c_void_p(status_word(x.device).data_ptr()),
-                c_void_p(torch.cuda.current_stream().cuda_stream))
-    check(status, "linear with fused norm (tcgen05)")

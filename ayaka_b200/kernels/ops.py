@@ -207,27 +207,14 @@ def linear_normed(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor | Non
                   scratch: torch.Tensor, count: int, activation: str = "none",
                   row_index: torch.Tensor | None = None) -> None:
     """``out = act(LayerNorm(x) @ weight.T + bias)`` for ``count`` rows (``x[row_index]`` with
-    a gather index). With bfloat16 weights and at most 64 rows the norm is computed inside the
-    matrix product's kernel; otherwise it runs first, into ``scratch`` (``[>= count, K]`` in
-    the weight's dtype), and the product follows. Same arithmetic either way: statistics and
-    the affine map in fp32, one rounding to the weight's dtype."""
-    op = "linear_normed"
+    a gather index): the norm into ``scratch`` (``[>= count, K]`` in the weight's dtype), then
+    the product. Two kernels on purpose. A variant that computed the norm inside the few-rows
+    product's kernel (statistics carried along by the kernel that last wrote the rows) was
+    measured on a B200 in a 48-layer decode chain and lost at every row count, 59.7 against
+    53.8 microseconds a layer at 8 rows: with programmatic dependent launch a kernel boundary
+    costs less than the extra dependent phases inside the product's kernel."""
     if activation not in ACTIVATIONS:
-        raise BackendError(f"{op}: unknown activation {activation!r}")
-    if weight.dtype == torch.bfloat16 and BF16_GEMM == "tcgen05":
-        from ayaka_b200.kernels import gemm_tc
-
-        _need(op, "x", x, torch.float32, 2)
-        _need(op, "weight", weight, torch.bfloat16, 2)
-        _need(op, "out", out, ndim=2)
-        if gemm_tc.can_fuse_norm(x, weight, gamma, beta, count):
-            n, k = weight.shape
-            if x.shape[1] != k or out.shape[1] != n or out.shape[0] < count or \
-                    gamma.shape[0] != k or (bias is not None and bias.shape[0] != n):
-                raise BackendError(f"{op}: shapes do not fit")
-            gemm_tc.linear_normed_bf16(x, gamma, beta, eps, weight, bias, out, count,
-                                       ACTIVATIONS[activation], row_index)
-            return
+        raise BackendError(f"linear_normed: unknown activation {activation!r}")
     layer_norm(x, gamma, beta, eps, scratch, rows=row_index, count=count)
     linear(scratch, weight, bias, out, activation=activation, rows=count)
 

@@ -105,8 +105,7 @@ class LinearHead(Part):
 
     def forward_normed(self, norm: Part, residual: torch.Tensor, rows: torch.Tensor,
                        scratch: torch.Tensor, logits: torch.Tensor, *, count: int) -> None:
-        """``logits = LayerNorm(residual[rows]) @ weight.T`` with the norm fused where the
-        kernel allows it."""
+        """``logits = LayerNorm(residual[rows]) @ weight.T``: only the wanted rows are normed."""
         ops.linear_normed(residual, norm.weight, norm.bias, norm.eps,  # type: ignore
                           self.weight, None, logits, scratch=scratch, count=count,
                           row_index=rows)

@@ -179,59 +179,27 @@ def test_linear_tcgen05_few_rows(m, splits):
     gemm_tc.check_status(a.device)
 
 
-@pytest.mark.parametrize("m", [1, 3, 8, 16])
-@pytest.mark.parametrize("n,k", [(4800, 1600), (300, 96), (50257, 160), (136, 840), (64, 2048)])
-def test_linear_with_fused_layer_norm(m, n, k):
-    """LayerNorm computed inside the few-rows matrix product: against float64, and against
-    the two-kernel path it replaces (same roundings: the results agree to the last bf16 bit
-    except where an fp32 sum lands on a rounding boundary)."""
+@pytest.mark.parametrize("m", [1, 8, 40])
+@pytest.mark.parametrize("n,k", [(300, 96), (136, 840)])
+def test_linear_normed(m, n, k):
+    """Norm, then product, then activation, with a gather of the rows: against float64."""
     ops = _ops()
-    from ayaka_b200.kernels import gemm_tc
-    x = _randn(m + 3, k, seed=40, scale=2.0) + 0.5
-    gamma, beta = _randn(k, seed=41) * 0.2 + 1.0, _randn(k, seed=42) * 0.3
-    w = _randn(n, k, seed=43, dtype=torch.bfloat16, scale=1 / math.sqrt(k))
-    bias = _randn(n, seed=44)
-    index = torch.arange(m + 2, 2, -1, dtype=torch.int32, device=DEV)  # rows m+2 .. 3
-    assert gemm_tc.can_fuse_norm(x, w, gamma, beta, min(m, gemm_tc.LN_MAX_ROWS))
-    normed = plain.layer_norm(x.double()[index.long()], gamma.double(), beta.double(), 1e-5)
-    exact = normed.to(torch.bfloat16).double() @ w.double().t() + bias.double()
-    out = torch.full((m + 1, n), float("nan"), device=DEV)
-    scratch = torch.zeros(m, k, dtype=torch.bfloat16, device=DEV)
-    gemm_tc.linear_normed_bf16(x, gamma, beta, 1e-5, w, bias, out, m, 0, index)
-    gemm_tc.check_status(x.device)
-    torch.testing.assert_close(out[:m].double(), exact, rtol=2e-3, atol=2e-3)
-    assert torch.isnan(out[m:]).all()
-    two = torch.zeros(m, n, device=DEV)
-    ops.layer_norm(x, gamma, beta, 1e-5, scratch, rows=index, count=m)
-    ops.linear(scratch, w, bias, two, rows=m)
-    torch.testing.assert_close(out[:m], two, rtol=2e-3, atol=2e-3)
-    half = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
-    gemm_tc.linear_normed_bf16(x, gamma, None, 1e-5, w, bias, half, m, 1)
-    routed = torch.zeros(m, n, device=DEV)  # the public op picks a path by the row count
-    ops.linear_normed(x, gamma, beta, 1e-5, w, bias, routed, scratch=scratch, count=m,
-                      row_index=index)
-    torch.testing.assert_close(routed, two, rtol=2e-3, atol=2e-3)
-    plain_normed = plain.layer_norm(x.double()[:m], gamma.double(), torch.zeros(k).double().to(DEV),
-                                    1e-5)
-    want = plain.gelu(plain_normed.to(torch.bfloat16).double() @ w.double().t() + bias.double(),
-                      "gelu_new")
-    torch.testing.assert_close(half.double(), want, rtol=2e-2, atol=2e-2)
-
-
-def test_linear_normed_falls_back_when_it_cannot_fuse():
-    ops = _ops()
-    # float32 weights, and more than 16 rows in bfloat16: the norm runs as its own kernel
-    for dtype, m in ((torch.float32, 9), (torch.bfloat16, 17)):
-        x = _randn(m, 96, seed=45)
-        gamma, beta = _randn(96, seed=46) + 1.0, _randn(96, seed=47)
-        w = _randn(40, 96, seed=48, dtype=dtype, scale=0.1)
-        out = torch.zeros(m, 40, device=DEV)
-        scratch = torch.zeros(m, 96, dtype=dtype, device=DEV)
-        ops.linear_normed(x, gamma, beta, 1e-6, w, None, out, scratch=scratch, count=m)
-        normed = plain.layer_norm(x.double(), gamma.double(), beta.double(), 1e-6)
-        assert float(scratch.float().abs().sum()) > 0
-        torch.testing.assert_close(out.double(), normed.to(dtype).double() @ w.double().t(),
-                                   rtol=1e-4, atol=1e-4)
+    for dtype in (torch.float32, torch.bfloat16):
+        x = _randn(m + 3, k, seed=40, scale=2.0) + 0.5
+        gamma, beta = _randn(k, seed=41) * 0.2 + 1.0, _randn(k, seed=42) * 0.3
+        w = _randn(n, k, seed=43, dtype=dtype, scale=1 / math.sqrt(k))
+        bias = _randn(n, seed=44)
+        index = torch.arange(m + 2, 2, -1, dtype=torch.int32, device=DEV)  # rows m+2 .. 3
+        normed = plain.layer_norm(x.double()[index.long()], gamma.double(), beta.double(), 1e-5)
+        exact = plain.gelu(normed.to(dtype).double() @ w.double().t() + bias.double(),
+                           "gelu_new")
+        out = torch.full((m + 1, n), float("nan"), device=DEV)
+        scratch = torch.zeros(m, k, dtype=dtype, device=DEV)
+        ops.linear_normed(x, gamma, beta, 1e-5, w, bias, out, scratch=scratch, count=m,
+                          activation="gelu_tanh", row_index=index)
+        tol = 1e-4 if dtype == torch.float32 else 2e-3
+        torch.testing.assert_close(out[:m].double(), exact, rtol=tol, atol=tol)
+        assert torch.isnan(out[m:]).all()
 
 
 def test_linear_tcgen05_few_rows_is_reproducible():
