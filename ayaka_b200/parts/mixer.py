@@ -114,10 +114,10 @@ class Attention(Mixer):
             splits = ops.decode_splits(n, self.num_heads, reach)
             partial = tickets = None
             if splits > 8:  # beyond a cluster's size the shares are merged through scratch
-                # rows * heads * splits never exceeds 592 + rows * heads (see decode_splits)
+                # rows * heads * splits never exceeds 1036 + rows * heads (see decode_splits)
                 pairs = step.workspace.max_rows * self.num_heads
                 partial = step.workspace.buffer(
-                    "attention.partial", (592 + pairs) * (self.head_dim + 2), torch.float32,
+                    "attention.partial", (1036 + pairs) * (self.head_dim + 2), torch.float32,
                     rows=1)
                 tickets = step.workspace.buffer("attention.tickets", pairs, torch.int32, rows=1)
             ops.attention_decode(q, cache.k_pages, cache.v_pages, group.block_table,
