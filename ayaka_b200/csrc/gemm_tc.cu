@@ -33,20 +33,201 @@ __host__ __device__ constexpr uint32_t tc_tmem_cols(int n) {
   return n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : (n <= 256 ? 256 : 512)));
 }
 
+// Shared memory the epilogue stages output boxes in: 32 rows x 128 bytes per epilogue warp.
+constexpr int EPI_WARP_BYTES = 32 * 128;
+constexpr int EPI_BYTES = 4 * EPI_WARP_BYTES;
+// ... and each epilogue warp's copy of the tile's bias (BN floats), fetched before the warp
+// waits for the accumulator: a load of the bias after the wait would put a trip through the
+// (busy) memory system into every 32 columns of the epilogue.
+constexpr int epi_bias_bytes(int bn) { return 4 * bn * 4; }
+
 template <int BN, int STAGES>
 struct TcSmem {
   static constexpr int B_BYTES = BN * TC_BK * 2;
   static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int BIAS_OFFSET = EPI_OFFSET + EPI_BYTES;
+  static constexpr int BAR_OFFSET = BIAS_OFFSET + epi_bias_bytes(BN);
   // full[STAGES], empty[STAGES], accum, then the tmem slot and the failure flag
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16;
   static constexpr int DYNAMIC = TOTAL + 1024;  // room to align the base to 1024 bytes
 };
 
+// One output row's 32 consecutive columns n .. n + 31 (fp32 accumulators as raw bits): bias,
+// activation or residual sum, and the store; `vec_ok` says that rows start on 16 bytes.
+__device__ __forceinline__ void store_row_chunk(const uint32_t* raw, int m, int n, int N,
+                                                const float* __restrict__ bias,
+                                                void* __restrict__ out, int ldo, int mode,
+                                                int act, int vec_ok) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    v[j] = __uint_as_float(raw[j]);
+    if (bias != nullptr && n + j < N) v[j] += __ldg(bias + n + j);
+  }
+  const bool full_chunk = n + 32 <= N;
+  if (mode == OUT_BF16) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = activate(v[j], act);
+    if (vec_ok && full_chunk) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 packed;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+        __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+        packed.x = *reinterpret_cast<uint32_t*>(&h0);
+        packed.y = *reinterpret_cast<uint32_t*>(&h1);
+        packed.z = *reinterpret_cast<uint32_t*>(&h2);
+        packed.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(dst + j) = packed;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {  // unrolled: v[] must stay in registers
+        if (n + j < N) dst[j] = __float2bfloat16_rn(v[j]);
+      }
+    }
+  } else {
+    float* dst = reinterpret_cast<float*>(out) + (size_t)m * ldo + n;
+    if (mode == OUT_F32) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = activate(v[j], act);
+    }
+    if (vec_ok && full_chunk) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        if (mode == OUT_RESIDUAL_F32) {
+          const float4 r = *reinterpret_cast<const float4*>(dst + j);
+          o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+        }
+        *reinterpret_cast<float4*>(dst + j) = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (n + j < N) dst[j] = mode == OUT_RESIDUAL_F32 ? dst[j] + v[j] : v[j];
+      }
+    }
+  }
+}
+
+// One epilogue warp's 32 rows of a tile, BN columns from tensor-memory address `acc` (lane
+// base included): bias, activation, rounding, then out to global memory. With `vec_ok` (the
+// output's base and row stride are multiples of 16 bytes, `map_out` describes it) the rows
+// are staged in `staging` (this warp's 32 x 128 bytes, 128-byte swizzle: lane r writes its
+// 16-byte piece c at piece c ^ (r & 7), free of bank conflicts) and leave as one TMA store per
+// box of 128 bytes x 32 rows — or one TMA reduce-add for the residual sum, which adds in the
+// memory system and so never reads the old rows into the SM. TMA clips at the matrix edges.
+// A lane storing its own row directly touches 32 different lines per instruction; measured
+// on a B200 that made the epilogue of a 128 x 192 tile take 11 microseconds against 8.5 for
+// its main loop. Without `vec_ok` that direct path is what remains.
+// This warp's copy of the tile's bias (zeros where there is none) into shared memory.
+template <int BN>
+__device__ __forceinline__ void stage_bias(float* bias_s, const float* __restrict__ bias, int n0,
+                                           int N, int lane) {
+  for (int i = lane; i < BN; i += 32) {
+    bias_s[i] = (bias != nullptr && n0 + i < N) ? __ldg(bias + n0 + i) : 0.f;
+  }
+  __syncwarp();
+}
+
+template <int BN>
+__device__ __forceinline__ void epilogue_warp(uint32_t acc, int lane, int m_warp, int n0, int M,
+                                              int N, const float* __restrict__ bias,
+                                              const float* bias_s, void* __restrict__ out,
+                                              int ldo, int mode, int act, int vec_ok,
+                                              const CUtensorMap* map_out, uint8_t* staging) {
+  if (!vec_ok) {
+    const int m = m_warp + lane;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int n = n0 + c * 32;
+      if (n >= N) break;  // uniform over the warp
+      uint32_t raw[32];
+      tmem_ld_32x32(acc + (uint32_t)(c * 32), raw);
+      tmem_ld_wait();
+      if (m < M) store_row_chunk(raw, m, n, N, bias, out, ldo, mode, act, 0);
+      __syncwarp();  // the next tcgen05.ld needs the whole warp
+    }
+    return;
+  }
+  if (m_warp >= M) return;  // nothing of this warp's rows exists (uniform over the warp)
+  uint8_t* row = staging + lane * 128;
+  const int swz = lane & 7;
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    const int n = n0 + c * 32;
+    if (n >= N) break;
+    // a box is 64 bf16 columns (two passes of this loop) or 32 fp32 columns (one)
+    const bool opens_box = mode != OUT_BF16 || (c & 1) == 0;
+    if (opens_box) {
+      if (lane == 0) bulk_wait_read_all();  // the box before has left the staging rows
+      __syncwarp();
+    }
+    uint32_t raw[32];
+    tmem_ld_32x32(acc + (uint32_t)(c * 32), raw);
+    tmem_ld_wait();
+    float v[32];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {  // the bias: the same shared-memory words for every lane
+      const float4 b = *reinterpret_cast<const float4*>(bias_s + c * 32 + q * 4);
+      v[q * 4] = __uint_as_float(raw[q * 4]) + b.x;
+      v[q * 4 + 1] = __uint_as_float(raw[q * 4 + 1]) + b.y;
+      v[q * 4 + 2] = __uint_as_float(raw[q * 4 + 2]) + b.z;
+      v[q * 4 + 3] = __uint_as_float(raw[q * 4 + 3]) + b.w;
+    }
+    if (mode != OUT_RESIDUAL_F32) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = activate(v[j], act);
+    }
+    if (mode == OUT_BF16) {
+      const int piece0 = (c & 1) * 4;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 packed;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(v[q * 8], v[q * 8 + 1]);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]);
+        __nv_bfloat162 h3 = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
+        packed.x = *reinterpret_cast<uint32_t*>(&h0);
+        packed.y = *reinterpret_cast<uint32_t*>(&h1);
+        packed.z = *reinterpret_cast<uint32_t*>(&h2);
+        packed.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(row + (((piece0 + q) ^ swz) << 4)) = packed;
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        *reinterpret_cast<float4*>(row + ((q ^ swz) << 4)) =
+            make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+      }
+    }
+    const bool closes_box = mode != OUT_BF16 || (c & 1) == 1 || c + 1 == BN / 32 ||
+                            n + 32 >= N;
+    if (closes_box) {
+      fence_proxy_async_shared();
+      __syncwarp();
+      if (lane == 0) {
+        const int x = mode == OUT_BF16 ? n0 + (c & ~1) * 32 : n;
+        if (mode == OUT_RESIDUAL_F32) {
+          tma_reduce_add_2d(map_out, staging, x, m_warp);
+        } else {
+          tma_store_2d(map_out, staging, x, m_warp);
+        }
+        bulk_commit_group();
+      }
+    }
+  }
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(128)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const float* __restrict__ bias, void* __restrict__ out, int ldo, int M, int N,
+               const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias, void* __restrict__ out, int ldo, int M, int N,
                int K, int act, int mode, int vec_ok, int* __restrict__ status) {
   using L = TcSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
@@ -132,74 +313,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   // ---- epilogue: all four warps -----------------------------------------------------
   __syncwarp();
+  float* bias_s = reinterpret_cast<float*>(smem + L::BIAS_OFFSET) + warp * BN;
+  stage_bias<BN>(bias_s, bias, n0, N, lane);
   pdl_wait();
   bool have = mbar_wait(accum, 0);
   if (!have) *failed = 1;
   tc_fence_after();
   if (have && *failed == 0) {
-    const int m = m0 + warp * 32 + lane;
-    const bool row_ok = m < M;
-#pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
-      const int n = n0 + c * 32;
-      if (n >= N) break;  // uniform over the CTA
-      uint32_t raw[32];
-      tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), raw);
-      tmem_ld_wait();
-      if (row_ok) {
-      float v[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        v[j] = __uint_as_float(raw[j]);
-        if (bias != nullptr && n + j < N) v[j] += __ldg(bias + n + j);
-      }
-      const bool full_chunk = n + 32 <= N;
-      if (mode == OUT_BF16) {
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = activate(v[j], act);
-        if (vec_ok && full_chunk) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint4 packed;
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-            packed.x = *reinterpret_cast<uint32_t*>(&h0);
-            packed.y = *reinterpret_cast<uint32_t*>(&h1);
-            packed.z = *reinterpret_cast<uint32_t*>(&h2);
-            packed.w = *reinterpret_cast<uint32_t*>(&h3);
-            *reinterpret_cast<uint4*>(dst + j) = packed;
-          }
-        } else {
-          for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
-        }
-      } else {
-        float* dst = reinterpret_cast<float*>(out) + (size_t)m * ldo + n;
-        if (mode == OUT_F32) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = activate(v[j], act);
-        }
-        if (vec_ok && full_chunk) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            if (mode == OUT_RESIDUAL_F32) {
-              const float4 r = *reinterpret_cast<const float4*>(dst + j);
-              o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
-            }
-            *reinterpret_cast<float4*>(dst + j) = o;
-          }
-        } else {
-          for (int j = 0; j < 32 && n + j < N; ++j) {
-            dst[j] = mode == OUT_RESIDUAL_F32 ? dst[j] + v[j] : v[j];
-          }
-        }
-      }
-      }  // row_ok
-      __syncwarp();  // the next tcgen05.ld needs the whole warp
-    }
+    epilogue_warp<BN>(tmem_base + ((uint32_t)(warp * 32) << 16), lane, m0 + warp * 32, n0, M, N,
+                      bias, bias_s, out, ldo, mode, act, vec_ok, &map_out,
+                      smem + L::EPI_OFFSET + warp * EPI_WARP_BYTES);
+    if (lane == 0) bulk_wait_all();  // the stores are done before the CTA says it is
   }
 
   // ---- teardown ---------------------------------------------------------------------
@@ -230,7 +354,9 @@ template <int BN, int STAGES>
 struct PersistentSmem {
   static constexpr int B_BYTES = BN * TC_BK * 2;
   static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int BIAS_OFFSET = EPI_OFFSET + EPI_BYTES;
+  static constexpr int BAR_OFFSET = BIAS_OFFSET + epi_bias_bytes(BN);
   // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], then the tmem slot and the flag
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
   static constexpr int DYNAMIC = TOTAL + 1024;
@@ -240,6 +366,7 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(192)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                           const __grid_constant__ CUtensorMap map_w,
+                          const __grid_constant__ CUtensorMap map_out,
                           const float* __restrict__ bias, void* __restrict__ out, int ldo, int M,
                           int N, int K, int act, int mode, int vec_ok,
                           int* __restrict__ status) {
@@ -366,6 +493,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
       const int buf = local & 1;
       int m0, n0;
       tile_origin(t, m0, n0);
+      float* bias_s = reinterpret_cast<float*>(smem + L::BIAS_OFFSET) + quarter * BN;
+      stage_bias<BN>(bias_s, bias, n0, N, lane);
       bool have = true;
       if (lane == 0) have = mbar_wait(&acc_full[buf], (local >> 1) & 1);
       have = __shfl_sync(0xffffffffu, have, 0);
@@ -374,75 +503,16 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         break;
       }
       tc_fence_after();
-      const int m = m0 + quarter * 32 + lane;
-      const bool row_ok = m < M;
-      const uint32_t acc = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quarter * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int n = n0 + c * 32;
-        if (n >= N) break;  // uniform over the warp
-        uint32_t raw[32];
-        tmem_ld_32x32(acc + (uint32_t)(c * 32), raw);
-        tmem_ld_wait();
-        if (row_ok) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            v[j] = __uint_as_float(raw[j]);
-            if (bias != nullptr && n + j < N) v[j] += __ldg(bias + n + j);
-          }
-          const bool full_chunk = n + 32 <= N;
-          if (mode == OUT_BF16) {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = activate(v[j], act);
-            if (vec_ok && full_chunk) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 packed;
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                packed.x = *reinterpret_cast<uint32_t*>(&h0);
-                packed.y = *reinterpret_cast<uint32_t*>(&h1);
-                packed.z = *reinterpret_cast<uint32_t*>(&h2);
-                packed.w = *reinterpret_cast<uint32_t*>(&h3);
-                *reinterpret_cast<uint4*>(dst + j) = packed;
-              }
-            } else {
-              for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(v[j]);
-            }
-          } else {
-            float* dst = reinterpret_cast<float*>(out) + (size_t)m * ldo + n;
-            if (mode == OUT_F32) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = activate(v[j], act);
-            }
-            if (vec_ok && full_chunk) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                if (mode == OUT_RESIDUAL_F32) {
-                  const float4 r = *reinterpret_cast<const float4*>(dst + j);
-                  o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
-                }
-                *reinterpret_cast<float4*>(dst + j) = o;
-              }
-            } else {
-              for (int j = 0; j < 32 && n + j < N; ++j) {
-                dst[j] = mode == OUT_RESIDUAL_F32 ? dst[j] + v[j] : v[j];
-              }
-            }
-          }
-        }
-        __syncwarp();  // the next tcgen05.ld needs the whole warp
-      }
+      epilogue_warp<BN>(tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quarter * 32) << 16), lane,
+                        m0 + quarter * 32, n0, M, N, bias, bias_s, out, ldo, mode, act, vec_ok,
+                        &map_out,
+                        smem + L::EPI_OFFSET + quarter * EPI_WARP_BYTES);
       // this warp has read its lanes of the accumulator: hand it back
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
+    if (lane == 0) bulk_wait_all();  // the stores are done before the CTA says it is
   }
 
   // ---- teardown ---------------------------------------------------------------------
@@ -452,6 +522,199 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 0) {
     __syncwarp();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// The same persistent kernel for CTA pairs (tcgen05 cta_group::2): the two CTAs of a cluster
+// work on one 256 x BN tile. Each loads its own 128 rows of the activations and its own half
+// (BN / 2 rows) of the weight tile, so a stage of the ring is a third smaller than for a
+// 128 x BN tile while the pair's MMA does twice the work: shared-memory traffic per FLOP,
+// which bounds the single-CTA kernels, drops by a third. Only the even CTA (rank 0) issues
+// MMAs; its `full` barriers count the bytes of both CTAs' copies (the odd CTA's copies name
+// the even CTA's barrier), its commits arrive on the `empty` and `acc_full` barriers of both,
+// and both CTAs' epilogue warps arrive on its `acc_empty`. Each CTA's epilogue reads its own
+// 128 lanes of tensor memory. No copy is multicast. K is walked as in the other kernels, so
+// the results are the same bit for bit.
+template <int BN, int STAGES>
+struct PairSmem {
+  static constexpr int B_BYTES = (BN / 2) * TC_BK * 2;
+  static constexpr int STAGE_BYTES = TC_A_BYTES + B_BYTES;
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int BIAS_OFFSET = EPI_OFFSET + EPI_BYTES;
+  static constexpr int BAR_OFFSET = BIAS_OFFSET + epi_bias_bytes(BN);
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
+  static constexpr int DYNAMIC = TOTAL + 1024;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                    const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias,
+                    void* __restrict__ out, int ldo, int M, int N, int K, int act, int mode,
+                    int vec_ok, int* __restrict__ status) {
+  using L = PairSmem<BN, STAGES>;
+  static_assert(BN % 32 == 0 && BN <= 256, "tile width");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = (int)cluster_rank();  // 0 issues the MMAs
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  constexpr int PAIR_BM = 2 * TC_BM;
+  const int tiles_m = (M + PAIR_BM - 1) / PAIR_BM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + TC_BK - 1) / TC_BK;
+  constexpr uint32_t TMEM_COLS = 2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512));
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);  // four epilogue warps in each CTA (used in rank 0 only)
+    }
+    *failed = 0;
+    mbar_fence_init();
+    tma_prefetch_map(&map_a);
+    tma_prefetch_map(&map_w);
+  }
+  if (warp == 0) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+
+  auto tile_origin = [&](int t, int& m0, int& n0) {
+    n0 = (t / tiles_m) * BN;
+    m0 = (t % tiles_m) * PAIR_BM;
+  };
+
+  if (warp == 0 && lane == 0) {
+    // ---- producer (in both CTAs): this CTA's rows of A and its half of the weight tile
+    const uint32_t leader_full = peer_address(&full[0], 0);
+    int ahead = 0;
+    if (pair < num_tiles) {
+      int m0, n0;
+      tile_origin(pair, m0, n0);
+      ahead = num_kb < STAGES ? num_kb : STAGES;
+      for (int kb = 0; kb < ahead; ++kb) {
+        if (rank == 0) mbar_expect_tx(&full[kb], 2 * L::STAGE_BYTES);
+        tma_load_2d_pair(smem + kb * L::STAGE_BYTES + TC_A_BYTES, &map_w,
+                         leader_full + 8u * (uint32_t)kb, kb * TC_BK, n0 + rank * (BN / 2));
+      }
+    }
+    pdl_wait();
+    int it = 0;
+    for (int t = pair; t < num_tiles && *failed == 0; t += num_pairs) {
+      int m0, n0;
+      tile_origin(t, m0, n0);
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        uint8_t* a_tile = smem + s * L::STAGE_BYTES;
+        if (it >= ahead) {
+          if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) {
+            *failed = 1;
+            break;
+          }
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * L::STAGE_BYTES);
+          tma_load_2d_pair(a_tile + TC_A_BYTES, &map_w, leader_full + 8u * (uint32_t)s,
+                           kb * TC_BK, n0 + rank * (BN / 2));
+        }
+        tma_load_2d_pair(a_tile, &map_a, leader_full + 8u * (uint32_t)s, kb * TC_BK,
+                         m0 + rank * TC_BM);
+      }
+    }
+  } else if (warp == 1 && lane == 0 && rank == 0) {
+    // ---- MMA issuer: the even CTA, for both
+    constexpr uint32_t idesc = umma_idesc_bf16(PAIR_BM, BN);
+    int it = 0, local = 0;
+    for (int t = pair; t < num_tiles && *failed == 0; t += num_pairs, ++local) {
+      const int buf = local & 1;
+      if (local >= 2 && !mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1)) {
+        *failed = 1;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(&full[s], (it / STAGES) & 1)) {
+          *failed = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint8_t* a_tile = smem + s * L::STAGE_BYTES;
+        const uint8_t* b_tile = a_tile + TC_A_BYTES;
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; ++k) {
+          umma_f16_pair(acc, umma_desc_k128(a_tile, k * 32), umma_desc_k128(b_tile, k * 32),
+                        idesc, (kb | k) != 0);
+        }
+        umma_commit_pair(&empty[s], 3);
+      }
+      if (!ok) break;
+      umma_commit_pair(&acc_full[buf], 3);
+    }
+  } else if (warp >= 2) {
+    // ---- epilogue (in both CTAs): this CTA's 128 rows of the tile
+    pdl_wait();
+    const int quarter = warp & 3;
+    int local = 0;
+    for (int t = pair; t < num_tiles; t += num_pairs, ++local) {
+      const int buf = local & 1;
+      int m0, n0;
+      tile_origin(t, m0, n0);
+      float* bias_s = reinterpret_cast<float*>(smem + L::BIAS_OFFSET) + quarter * BN;
+      stage_bias<BN>(bias_s, bias, n0, N, lane);
+      bool have = true;
+      if (lane == 0) have = mbar_wait(&acc_full[buf], (local >> 1) & 1);
+      have = __shfl_sync(0xffffffffu, have, 0);
+      if (!have || *failed != 0) {
+        if (lane == 0) *failed = 1;
+        break;
+      }
+      tc_fence_after();
+      epilogue_warp<BN>(tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quarter * 32) << 16), lane,
+                        m0 + rank * TC_BM + quarter * 32, n0, M, N, bias, bias_s, out, ldo, mode,
+                        act, vec_ok, &map_out, smem + L::EPI_OFFSET + quarter * EPI_WARP_BYTES);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) {
+          mbar_arrive(&acc_empty[buf]);
+        } else {
+          mbar_arrive_cluster(peer_address(&acc_empty[buf], 0));
+        }
+      }
+    }
+    if (lane == 0) bulk_wait_all();  // the stores are done before the CTA says it is
+  }
+
+  // ---- teardown: nobody leaves while the peer may still signal it or read its operands
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (*failed != 0 && threadIdx.x == 0) atomicExch(status, AYK_WAIT_TIMEOUT);
+  if (warp == 0) {
+    __syncwarp();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 
@@ -689,10 +952,10 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
 struct MapKey {
   const void* base;
   uint64_t rows, cols, ld;
-  uint32_t box_rows;
+  uint32_t box_rows, elem_bytes;
   bool operator==(const MapKey& o) const {
     return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld &&
-           box_rows == o.box_rows;
+           box_rows == o.box_rows && elem_bytes == o.elem_bytes;
   }
 };
 struct MapKeyHash {
@@ -702,26 +965,38 @@ struct MapKeyHash {
     h = h * 1000003u ^ k.cols;
     h = h * 1000003u ^ k.ld;
     h = h * 1000003u ^ k.box_rows;
+    h = h * 1000003u ^ k.elem_bytes;
     return h;
   }
 };
 
 static int cached_map(const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
-                      uint32_t box_rows, CUtensorMap* out) {
+                      uint32_t box_rows, CUtensorMap* out, int elem_bytes = 2) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   std::lock_guard<std::mutex> lock(mu);
-  const MapKey key{base, rows, cols, ld, box_rows};
+  const MapKey key{base, rows, cols, ld, box_rows, (uint32_t)elem_bytes};
   auto it = cache.find(key);
   if (it == cache.end()) {
     CUtensorMap map;
-    const int r = make_map_bf16_k64(&map, base, rows, cols, ld, box_rows);
+    const int r = make_map_128b(&map, base, rows, cols, ld, box_rows, elem_bytes);
     if (r != AYK_OK) return r;
     if (cache.size() > 4096) cache.clear();
     it = cache.emplace(key, map).first;
   }
   *out = it->second;
   return AYK_OK;
+}
+
+// The output's map for the epilogue's TMA stores (boxes of 32 rows x 128 bytes), when its base
+// and row stride allow one; otherwise `vec_ok` = 0 and the kernel stores row by row.
+static int output_map(void* out, int ldo, int M, int N, int mode, const CUtensorMap& fallback,
+                      CUtensorMap* map_out, int* vec_ok) {
+  const size_t elem = mode == OUT_BF16 ? 2 : 4;
+  *vec_ok = (((uintptr_t)out % 16) == 0 && ((size_t)ldo * elem) % 16 == 0) ? 1 : 0;
+  *map_out = fallback;  // unused without vec_ok
+  if (!*vec_ok) return AYK_OK;
+  return cached_map(out, (uint64_t)M, (uint64_t)N, (uint64_t)ldo, 32, map_out, (int)elem);
 }
 
 template <int BN, int STAGES>
@@ -741,13 +1016,15 @@ int launch_gemm_tc(const void* a, int lda, const void* w, int ldw, const float* 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const size_t elem = mode == OUT_BF16 ? 2 : 4;
-  const int vec_ok = (((uintptr_t)out % 16) == 0 && ((size_t)ldo * elem) % 16 == 0) ? 1 : 0;
+  CUtensorMap map_out;
+  int vec_ok = 0;
+  r = output_map(out, ldo, M, N, mode, map_a, &map_out, &vec_ok);
+  if (r != AYK_OK) return r;
   const long long gy = (M + TC_BM - 1) / TC_BM;
   if (gy > 65535) return AYK_TOO_LARGE;
   dim3 grid((N + BN - 1) / BN, (unsigned)gy);
   return launch_kernel(gemm_tc_kernel<BN, STAGES>, grid, dim3(128), L::DYNAMIC, stream, 1, map_a,
-                       map_w, bias, out, ldo, M, N, K, act, mode, vec_ok, status);
+                       map_w, map_out, bias, out, ldo, M, N, K, act, mode, vec_ok, status);
 }
 
 template <int BN, int STAGES>
@@ -773,14 +1050,51 @@ int launch_gemm_tc_persistent(const void* a, int lda, const void* w, int ldw, co
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const size_t elem = mode == OUT_BF16 ? 2 : 4;
-  const int vec_ok = (((uintptr_t)out % 16) == 0 && ((size_t)ldo * elem) % 16 == 0) ? 1 : 0;
+  CUtensorMap map_out;
+  int vec_ok = 0;
+  r = output_map(out, ldo, M, N, mode, map_a, &map_out, &vec_ok);
+  if (r != AYK_OK) return r;
   const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
   if (tiles > 0x7fffffffLL) return AYK_TOO_LARGE;
   const int grid = tiles < num_sms ? (int)tiles : num_sms;
   return launch_kernel(gemm_tc_persistent_kernel<BN, STAGES>, dim3(grid), dim3(192), L::DYNAMIC,
-                       stream, 1, map_a, map_w, bias, out, ldo, M, N, K, act, mode, vec_ok,
-                       status);
+                       stream, 1, map_a, map_w, map_out, bias, out, ldo, M, N, K, act, mode,
+                       vec_ok, status);
+}
+
+template <int BN, int STAGES>
+int launch_gemm_tc_pair(const void* a, int lda, const void* w, int ldw, const float* bias,
+                        void* out, int ldo, int M, int N, int K, int act, int mode, int* status,
+                        cudaStream_t stream) {
+  using L = PairSmem<BN, STAGES>;
+  CUtensorMap map_a, map_w;
+  int r = cached_map(a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BM, &map_a);
+  if (r != AYK_OK) return r;
+  r = cached_map(w, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN / 2, &map_w);
+  if (r != AYK_OK) return r;
+  static bool configured = false;
+  static int num_sms = 0;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYNAMIC);
+    if (e != cudaSuccess) return (int)e;
+    int device = 0;
+    e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  CUtensorMap map_out;
+  int vec_ok = 0;
+  r = output_map(out, ldo, M, N, mode, map_a, &map_out, &vec_ok);
+  if (r != AYK_OK) return r;
+  const long long tiles = (long long)((M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((N + BN - 1) / BN);
+  if (tiles > 0x7fffffffLL) return AYK_TOO_LARGE;
+  const int pairs = tiles < num_sms / 2 ? (int)tiles : num_sms / 2;
+  return launch_kernel_x(gemm_tc_pair_kernel<BN, STAGES>, dim3(2 * pairs), dim3(192), L::DYNAMIC,
+                         stream, 2, map_a, map_w, map_out, bias, out, ldo, M, N, K, act, mode,
+                         vec_ok, status);
 }
 
 template <int MP, int STAGES>
@@ -828,9 +1142,12 @@ inline int pick_splits(int tile_n, int N, int M) {
 AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
 
 // mode: 0 = bf16 out with activation, 1 = fp32 out with activation, 2 = fp32 out += (residual).
-// tile_n: 0 = choose; 32, 64, 128, 192, 256 = one tile of that width per CTA; 1128, 1192, 1256 = the
-// persistent kernel with tiles 128, 192 or 256 wide; negative = the few-rows kernel (see below). `status` is one device int that a CTA sets to
-// AYK_WAIT_TIMEOUT if a wait ran out; the host reads it when it checks a step.
+// tile_n: 0 = choose; 32, 64, 128, 192, 256 = one tile of that width per CTA; 1128, 1192,
+// 1256 = the persistent kernel with tiles 128, 192 or 256 wide; 2192, 2256 = the persistent
+// kernel for CTA pairs (256-row tiles, 192 or 256 wide; measured level with 1192 / 1256 at
+// GPT-2 XL's shapes, so the choice never picks it); negative = the few-rows kernel (see
+// pick_splits). `status` is one device int that a CTA sets to AYK_WAIT_TIMEOUT if a wait ran
+// out; the host reads it when it checks a step.
 AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, const float* bias,
                              void* out, int ldo, int M, int N, int K, int act, int mode,
                              int tile_n, int* status, void* stream) {
@@ -874,14 +1191,17 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
         num_sms = 148;
       }
     }
-    // tile width 256, 192 or 128: the one that needs the least (rounds over the SMs) x (work
-    // of a tile); one tile per CTA while everything fits one round, else the persistent kernel
+    // tile width 256, 192 or 128: the one with the least (rounds over the SMs) x (time of a
+    // round). Measured at K = 1600: a round of 256-wide tiles takes only 7 % longer than one
+    // of 192-wide tiles (9.8 against 9.2 microseconds), i.e. about (width + 768) units, so
+    // the number of rounds decides and the width breaks ties. One tile per CTA while
+    // everything fits one round, else the persistent kernel.
     const long long tiles_m = (M + TC_BM - 1) / TC_BM;
     long long best_cost = -1;
     int best_bn = 256;
     for (int bn : {256, 192, 128}) {
       const long long tiles = tiles_m * ((N + bn - 1) / bn);
-      const long long cost = ((tiles + num_sms - 1) / num_sms) * bn;
+      const long long cost = ((tiles + num_sms - 1) / num_sms) * (bn + 768);
       if (best_cost < 0 || cost < best_cost) {
         best_cost = cost;
         best_bn = bn;
@@ -902,6 +1222,12 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
     case 1256:
       return launch_gemm_tc_persistent<256, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
                                                status, s);
+    case 2192:
+      return launch_gemm_tc_pair<192, 7>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
+                                         status, s);
+    case 2256:
+      return launch_gemm_tc_pair<256, 6>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
+                                         status, s);
     case 32:
       return launch_gemm_tc<32, 8>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
     case 64:

@@ -129,6 +129,94 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                    "r"(smem_u32(bar))
                : "memory");
 }
+// ---- stores through TMA: a tile staged in shared memory goes to global memory as one
+// coalesced bulk copy, clipped at the tensor's edges. x * element size must be a multiple
+// of 16 bytes; never start at a negative coordinate.
+__device__ __forceinline__ void fence_proxy_async_shared() {
+  // generic-proxy writes to shared memory become visible to the async proxy (TMA, tcgen05)
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x,
+                                             int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::
+                   "l"(map), "r"(smem_u32(src)), "r"(x), "r"(y)
+               : "memory");
+}
+// global[tile] += shared[tile], element by element (fp32 adds done by the memory system).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src,
+                                                  int x, int y) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+      ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// This thread's bulk stores have finished reading shared memory (it may be overwritten) ...
+__device__ __forceinline__ void bulk_wait_read_all() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// ... and have finished altogether (their writes are done).
+__device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster, on neighbouring SMs, run one MMA of
+// 256 rows. Each holds its own 128 rows of A and half of the rows of B in shared memory and
+// its own 128 lanes of the accumulator in tensor memory; the even CTA of the pair issues.
+// One warp of each CTA allocates (same warp index, same shared-memory slot in both).
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::
+                   "r"(smem_u32(slot)), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t base, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols)
+               : "memory");
+}
+// The descriptors name shared-memory offsets that hold this CTA's operand parts; the peer's
+// parts lie at the same offsets of its shared memory.
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One arrival on the barrier at this shared-memory offset in every CTA of `cta_mask` when all
+// MMAs issued so far by this thread have finished (an arrival sent to several CTAs, not a
+// copy of data: no load is multicast).
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(smem_u32(bar)),
+      "h"(cta_mask)
+      : "memory");
+}
+// 2-D tiled load into this CTA's shared memory whose bytes are counted on a barrier that may
+// lie in the peer CTA (`bar_cluster_address` from peer_address()). No multicast: every CTA
+// fetches its own tile.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map,
+                                                 uint32_t bar_cluster_address, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(map), "r"(bar_cluster_address), "r"(x), "r"(y)
+      : "memory");
+}
+// One arrival on a barrier of another CTA of the cluster.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_address) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::
+                   "r"(bar_cluster_address)
+               : "memory");
+}
 // 32 lanes x 32 columns of 32-bit cells: thread i of the warp gets lane (base lane + i).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t* v) {
   asm volatile(
@@ -231,21 +319,30 @@ inline EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// Map of a row-major bf16 matrix [rows, cols] with row stride ld (elements); box = box_rows x
-// 64 columns, 128-byte swizzle, zero fill outside. Needs a 16-byte aligned base and ld % 8 == 0.
-inline int make_map_bf16_k64(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                             uint64_t ld, uint32_t box_rows) {
+// Map of a row-major matrix [rows, cols] of 2-byte (bf16) or 4-byte (fp32) elements with row
+// stride ld (elements); box = box_rows x 128 bytes (64 or 32 columns), 128-byte swizzle, zero
+// fill outside on loads, clipping on stores. Needs a 16-byte aligned base and row stride.
+inline int make_map_128b(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                         uint64_t ld, uint32_t box_rows, int elem_bytes) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return AYK_DRIVER;
-  if (((uintptr_t)base & 15) || (ld % 8)) return AYK_BAD_ALIGNMENT;
+  if (elem_bytes != 2 && elem_bytes != 4) return AYK_BAD_ARGUMENT;
+  if (((uintptr_t)base & 15) || ((ld * elem_bytes) % 16)) return AYK_BAD_ALIGNMENT;
   const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {ld * 2};
-  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint64_t strides[1] = {ld * (uint64_t)elem_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), box_rows};
   const cuuint32_t elem[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
-                  strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                       : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                  2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? AYK_OK : AYK_DRIVER;
+}
+
+inline int make_map_bf16_k64(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                             uint64_t ld, uint32_t box_rows) {
+  return make_map_128b(map, base, rows, cols, ld, box_rows, 2);
 }
 
 }  // namespace ayk

@@ -136,7 +136,7 @@ def test_linear_bfloat16(kernel, m, n, k):
         gemm_tc.check_status(a.device)
 
 
-@pytest.mark.parametrize("tile_n", [32, 64, 128, 192, 256, 1128, 1192, 1256])
+@pytest.mark.parametrize("tile_n", [32, 64, 128, 192, 256, 1128, 1192, 1256, 2192, 2256])
 def test_linear_tcgen05_tiles_and_strides(tile_n):
     """Every tile width, operands that are column ranges of wider buffers, rows limited."""
     ops = _ops()
@@ -151,6 +151,44 @@ def test_linear_tcgen05_tiles_and_strides(tile_n):
     torch.testing.assert_close(out[:m].double(), a[:m].double() @ w.double().t(),
                                rtol=1e-4, atol=1e-4)
     assert torch.isnan(out[m:]).all()
+
+
+@pytest.mark.parametrize("tile_n", [1192, 1256, 2192, 2256])
+@pytest.mark.parametrize("m,n,k", [(600, 700, 520), (2048, 1600, 1600), (257, 4800, 64),
+                                   (300, 712, 136)])
+def test_linear_tcgen05_many_tiles(tile_n, m, n, k):
+    """The persistent kernels (one CTA per tile, and CTA pairs on 256-row tiles) over more
+    tiles than fit one round, every epilogue: equal to the one-tile-per-CTA kernel bit for
+    bit (the same order of K), and close to float64."""
+    from ayaka_b200.kernels import gemm_tc
+    a = _randn(m, k, seed=20, dtype=torch.bfloat16)
+    w = _randn(n, k, seed=21, dtype=torch.bfloat16, scale=1 / math.sqrt(k))
+    bias = _randn(n, seed=22)
+    exact = a.double() @ w.double().t() + bias.double()
+    for mode in ("bf16", "f32", "residual"):
+        outs = []
+        for tile in (128, tile_n):
+            # three rows more than the product has: they must stay as they are
+            if mode == "bf16":
+                out = torch.full((m + 3, n), 7.0, dtype=torch.bfloat16, device=DEV)
+                gemm_tc.linear_bf16(a, w, bias, out, m, 1, False, tile_n=tile)
+            elif mode == "f32":
+                out = torch.full((m + 3, n), 7.0, device=DEV)
+                gemm_tc.linear_bf16(a, w, bias, out, m, 0, False, tile_n=tile)
+            else:
+                out = torch.ones(m + 3, n, device=DEV)
+                gemm_tc.linear_bf16(a, w, bias, out, m, 0, True, tile_n=tile)
+            assert bool((out[m:] == (1.0 if mode == "residual" else 7.0)).all())
+            outs.append(out[:m])
+        gemm_tc.check_status(a.device)
+        assert torch.equal(outs[0], outs[1])
+        if mode == "bf16":
+            want = plain.gelu(exact, "gelu_new")
+            torch.testing.assert_close(outs[1].double(), want, rtol=2e-2, atol=2e-2)
+        if mode == "f32":
+            torch.testing.assert_close(outs[1].double(), exact, rtol=1e-4, atol=1e-4)
+        if mode == "residual":
+            torch.testing.assert_close(outs[1].double(), exact + 1.0, rtol=1e-4, atol=1e-4)
 
 
 @pytest.mark.parametrize("splits", [-100, -2, -4, -8, 0])
