@@ -800,6 +800,10 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
   const uint32_t tmem_base = *tmem_slot;
 
   pdl_launch_dependents();
+  // this thread's output column and its bias: a weight, so fetched before any wait
+  const int t = threadIdx.x;
+  const int n = n0 + t;
+  const float b = (bias != nullptr && n < N) ? __ldg(bias + n) : 0.f;
   int issued = 0;
   if (warp == 0 && lane == 0) {
     // the weight tiles of the first stages start before the kernel ahead has finished
@@ -849,6 +853,18 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
   }
   __syncwarp();
   pdl_wait();
+  // The residual rows this CTA will add to (its share of the rows after a K split, when that
+  // is at most 8): requested now, so that they arrive while the MMAs finish instead of
+  // after the reduction.
+  const int cols = MP / splits;  // the host picks splits that divide MP
+  const bool early_rows = mode == OUT_RESIDUAL_F32 && splits > 1 && cols <= 8;
+  float old_row[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int m = rank * cols + j;
+    old_row[j] = (early_rows && j < cols && m < M && n < N)
+                     ? reinterpret_cast<const float*>(out)[(size_t)m * ldo + n] : 0.f;
+  }
   bool have = true;
   if (my_kb > 0) {
     have = mbar_wait(accum, 0);
@@ -857,8 +873,6 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
   tc_fence_after();
 
   // this CTA's partial sums: thread t holds output column n0 + t for every padded row
-  const int t = threadIdx.x;
-  const int n = n0 + t;
   if (splits == 1) {
     if (have && *failed == 0) {
 #pragma unroll
@@ -867,7 +881,6 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
         tmem_ld_32x16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 16), raw);
         tmem_ld_wait();
         if (n < N) {
-          const float b = bias != nullptr ? __ldg(bias + n) : 0.f;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int m = c * 16 + j;
@@ -894,9 +907,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
     }
     __syncthreads();
     cluster_sync_all();
-    const int cols = MP / splits;  // the host picks splits that divide MP
     if (*failed == 0 && n < N) {
-      const float b = bias != nullptr ? __ldg(bias + n) : 0.f;
       // remote addresses of this thread's column in every peer's tile
       uint32_t peer_base[8];
 #pragma unroll
@@ -905,7 +916,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
       }
       // four rows at a time: all of their loads are issued before the first sum, so the
       // distributed-shared-memory latency is paid once per group, not once per load
-      for (int j0 = 0; j0 < cols; j0 += 4) {
+      auto group = [&](int j0, const float* old4) {
         float v[4][8];
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
@@ -925,9 +936,19 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
             for (int p = 1; p < 8; ++p) {
               if (p < splits) sum += v[jj][p];
             }
-            store_output(out, ldo, m, n, sum + b, mode, act);
+            if (old4 != nullptr) {
+              reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = old4[jj] + (sum + b);
+            } else {
+              store_output(out, ldo, m, n, sum + b, mode, act);
+            }
           }
         }
+      };
+      if (early_rows) {
+        group(0, old_row);
+        if (cols > 4) group(4, old_row + 4);
+      } else {
+        for (int j0 = 0; j0 < cols; j0 += 4) group(j0, nullptr);
       }
     }
     cluster_sync_all();  // nobody leaves while a peer may still read its tile

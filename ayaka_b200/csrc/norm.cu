@@ -34,6 +34,18 @@ __global__ void layer_norm_kernel(const float* __restrict__ x, int ld_x,
   }
 }
 
+// four consecutive outputs as one store (the address is a multiple of 4 elements)
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 packed;
+  packed.x = *reinterpret_cast<uint32_t*>(&lo);
+  packed.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = packed;
+}
+
 // The same with the row held in registers: one pass over global memory (all loads in flight
 // at once), mean and variance from the registers. For rows of at most 256 * 4 * VEC floats
 // whose addresses allow 16-byte loads.
@@ -41,12 +53,26 @@ template <typename TOut, int VEC>
 __global__ void __launch_bounds__(256)
 layer_norm_held_kernel(const float* __restrict__ x, int ld_x, const int* __restrict__ rows,
                        const float* __restrict__ gamma, const float* __restrict__ beta,
-                       float eps, TOut* __restrict__ out, int ld_out, int width) {
+                       float eps, TOut* __restrict__ out, int ld_out, int width,
+                       int wide_out) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
-  pdl_wait();
+  // the norm's weights (and the gather index, part of the step's metadata) do not depend on
+  // the kernel ahead: they are fetched before the wait, the rows after it
   const int r = blockIdx.x;
-  const float* src = x + (size_t)(rows != nullptr ? rows[r] : r) * ld_x;
+  const int row = rows != nullptr ? rows[r] : r;
+  float4 g[VEC], b[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int c = (i * 256 + threadIdx.x) * 4;
+    g[i] = b[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < width) {
+      g[i] = __ldg(reinterpret_cast<const float4*>(gamma + c));
+      if (beta != nullptr) b[i] = __ldg(reinterpret_cast<const float4*>(beta + c));
+    }
+  }
+  pdl_wait();
+  const float* src = x + (size_t)row * ld_x;
   float4 held[VEC];
   float s = 0.f;
 #pragma unroll
@@ -61,9 +87,9 @@ layer_norm_held_kernel(const float* __restrict__ x, int ld_x, const int* __restr
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
     if ((i * 256 + threadIdx.x) * 4 < width) {
-      const float a = held[i].x - mean, b = held[i].y - mean;
+      const float a = held[i].x - mean, bb = held[i].y - mean;
       const float c = held[i].z - mean, d = held[i].w - mean;
-      q += (a * a + b * b) + (c * c + d * d);
+      q += (a * a + bb * bb) + (c * c + d * d);
     }
   }
   const float inv = rsqrtf(block_sum(q, scratch) / (float)width + eps);
@@ -72,14 +98,15 @@ layer_norm_held_kernel(const float* __restrict__ x, int ld_x, const int* __restr
   for (int i = 0; i < VEC; ++i) {
     const int c = (i * 256 + threadIdx.x) * 4;
     if (c < width) {
-      const float4 g = __ldg(reinterpret_cast<const float4*>(gamma + c));
-      float v0 = (held[i].x - mean) * inv * g.x, v1 = (held[i].y - mean) * inv * g.y;
-      float v2 = (held[i].z - mean) * inv * g.z, v3 = (held[i].w - mean) * inv * g.w;
-      if (beta != nullptr) {
-        const float4 b = __ldg(reinterpret_cast<const float4*>(beta + c));
-        v0 += b.x; v1 += b.y; v2 += b.z; v3 += b.w;
+      const float v0 = (held[i].x - mean) * inv * g[i].x + b[i].x;
+      const float v1 = (held[i].y - mean) * inv * g[i].y + b[i].y;
+      const float v2 = (held[i].z - mean) * inv * g[i].z + b[i].z;
+      const float v3 = (held[i].w - mean) * inv * g[i].w + b[i].w;
+      if (wide_out) {
+        store4(dst + c, v0, v1, v2, v3);
+      } else {
+        stf(dst + c, v0); stf(dst + c + 1, v1); stf(dst + c + 2, v2); stf(dst + c + 3, v3);
       }
-      stf(dst + c, v0); stf(dst + c + 1, v1); stf(dst + c + 2, v2); stf(dst + c + 3, v3);
     }
   }
 }
@@ -93,10 +120,12 @@ int layer_norm(const float* x, int ld_x, const int* rows, const float* gamma, co
   }
   const bool vector_ok = width % 4 == 0 && ld_x % 4 == 0 && ((uintptr_t)x % 16) == 0 &&
                          ((uintptr_t)gamma % 16) == 0 && ((uintptr_t)beta % 16) == 0;
+  // whole groups of four outputs can be stored at once when the rows start on such groups
+  const int wide_out = (ld_out % 4 == 0 && ((uintptr_t)out % (4 * sizeof(TOut))) == 0) ? 1 : 0;
   if (vector_ok && width <= 8192 && width >= 256) {
 #define AYK_LN_HELD(VEC)                                                                       \
   return launch_kernel(layer_norm_held_kernel<TOut, VEC>, dim3(n), dim3(256), 0, stream, 1, x,  \
-                       ld_x, rows, gamma, beta, eps, (TOut*)out, ld_out, width)
+                       ld_x, rows, gamma, beta, eps, (TOut*)out, ld_out, width, wide_out)
     if (width <= 1024) AYK_LN_HELD(1);
     if (width <= 2048) AYK_LN_HELD(2);
     if (width <= 4096) AYK_LN_HELD(4);
