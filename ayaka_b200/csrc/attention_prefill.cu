@@ -74,7 +74,7 @@ __device__ __forceinline__ void load_kv_block(__nv_bfloat16* tile,
                                               const __nv_bfloat16* __restrict__ pages,
                                               const int* __restrict__ table, int key0,
                                               int first_key, int last_key, int num_kv_heads,
-                                              int kv_head, int page_size) {
+                                              int kv_head, int page_size, int page_shift) {
   // keys outside [first_key, last_key] are zero-filled: their pages may be gone (a window)
   // or hold anything, and 0 * NaN would poison the sum
   for (int i = threadIdx.x; i < PF_BN * PF_CHUNKS; i += 128) {
@@ -83,9 +83,12 @@ __device__ __forceinline__ void load_kv_block(__nv_bfloat16* tile,
     const bool valid = key >= first_key && key <= last_key;
     const __nv_bfloat16* src = pages;
     if (valid) {
-      const int page = table[key / page_size];
-      src = pages + (((size_t)page * num_kv_heads + kv_head) * page_size + key % page_size) *
-                        PF_HD + c * 8;
+      // a shift and a mask when the page size is a power of two: a division costs more
+      // instructions than the rest of the address
+      const int index = page_shift >= 0 ? key >> page_shift : key / page_size;
+      const int slot = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+      const int page = table[index];
+      src = pages + (((size_t)page * num_kv_heads + kv_head) * page_size + slot) * PF_HD + c * 8;
     }
     cp_async16(tile + r * PF_STRIDE + c * 8, src, valid);
   }
@@ -98,7 +101,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
                          const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ row_start, const int* __restrict__ kv_len,
                          __nv_bfloat16* __restrict__ out, int ld_out, int num_requests,
-                         int num_kv_heads, int group, int page_size, float scale, int window) {
+                         int num_kv_heads, int group, int page_size, float scale, int window,
+                         int total_tiles, int page_shift) {
   extern __shared__ __align__(16) unsigned char pf_smem[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(pf_smem);
   __nv_bfloat16* k_s = q_s + PF_TILE;       // two stages
@@ -106,8 +110,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
 
   pdl_launch_dependents();
   pdl_wait();
-  // which request and which 64-row tile of it
-  int tile = blockIdx.x, req = 0, rows_b = 0;
+  // Which request and which 64-row tile of it. Heads run along grid.x and tiles along grid.y
+  // from the last tile down: a tile's work grows with its position in the sequence, and the
+  // longest tiles must start first or they finish alone at the end.
+  int tile = total_tiles - 1 - (int)blockIdx.y, req = 0, rows_b = 0;
   for (; req < num_requests; ++req) {
     rows_b = row_start[req + 1] - row_start[req];
     const int tiles = (rows_b + PF_BM - 1) / PF_BM;
@@ -115,7 +121,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
     tile -= tiles;
   }
   if (req >= num_requests) return;
-  const int head = blockIdx.y;
+  const int head = blockIdx.x;
   const int kv_head = head / group;
   const int first_row = row_start[req] + tile * PF_BM;
   const int nrows = rows_b - tile * PF_BM < PF_BM ? rows_b - tile * PF_BM : PF_BM;
@@ -144,9 +150,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
     cp_async16(q_s + r * PF_STRIDE + c * 8, src, valid);
   }
   load_kv_block(k_s, k_pages, table, block_lo * PF_BN, lo_min, last_key, num_kv_heads,
-                kv_head, page_size);
+                kv_head, page_size, page_shift);
   load_kv_block(v_s, v_pages, table, block_lo * PF_BN, lo_min, last_key, num_kv_heads,
-                kv_head, page_size);
+                kv_head, page_size, page_shift);
   cp_async_commit();
 
   float o[PF_HD / 8][4];
@@ -162,9 +168,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
     const int stage = (block - block_lo) & 1;
     if (block < block_hi) {  // prefetch the next block into the other stage
       load_kv_block(k_s + (stage ^ 1) * PF_TILE, k_pages, table, (block + 1) * PF_BN, lo_min,
-                    last_key, num_kv_heads, kv_head, page_size);
+                    last_key, num_kv_heads, kv_head, page_size, page_shift);
       load_kv_block(v_s + (stage ^ 1) * PF_TILE, v_pages, table, (block + 1) * PF_BN, lo_min,
-                    last_key, num_kv_heads, kv_head, page_size);
+                    last_key, num_kv_heads, kv_head, page_size, page_shift);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -199,19 +205,32 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
         mma_bf16(s[2 * t + 1], q_frag[kk], kf[2], kf[3]);
       }
     }
-    // mask, online softmax (rows row_a and row_a + 8)
+    // mask, online softmax (rows row_a and row_a + 8). A block that lies wholly before the
+    // warp's first row (and no window) has nothing to mask: only the scaling remains.
     const int key_base = block * PF_BN + (lane & 3) * 2;
+    const bool all_seen = window == 0 && block * PF_BN + PF_BN - 1 <= pos0 + warp * 16;
     float block_max[2] = {-INFINITY, -INFINITY};
+    if (all_seen) {
 #pragma unroll
-    for (int t = 0; t < PF_BN / 8; ++t) {
+      for (int t = 0; t < PF_BN / 8; ++t) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = key_base + t * 8 + (e & 1);
-        const int pos = row_a + (e >> 1) * 8;
-        const bool seen = key <= pos && (window == 0 || key > pos - window);
-        const float v = seen ? s[t][e] * scale2 : -INFINITY;
-        s[t][e] = v;
-        block_max[e >> 1] = fmaxf(block_max[e >> 1], v);
+        for (int e = 0; e < 4; ++e) {
+          s[t][e] *= scale2;
+          block_max[e >> 1] = fmaxf(block_max[e >> 1], s[t][e]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int t = 0; t < PF_BN / 8; ++t) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = key_base + t * 8 + (e & 1);
+          const int pos = row_a + (e >> 1) * 8;
+          const bool seen = key <= pos && (window == 0 || key > pos - window);
+          const float v = seen ? s[t][e] * scale2 : -INFINITY;
+          s[t][e] = v;
+          block_max[e >> 1] = fmaxf(block_max[e >> 1], v);
+        }
       }
     }
     float corr[2], ref[2];
@@ -310,7 +329,6 @@ AYK_API int ayk_attention_prefill(const void* q, int ld_q, const void* k_pages,
       num_heads % num_kv_heads || page_size < 1 || table_stride < 1 || window < 0) {
     return AYK_BAD_ARGUMENT;
   }
-  if (num_heads > 65535) return AYK_TOO_LARGE;
   if (((uintptr_t)q % 16) || ((uintptr_t)out % 16) || ((uintptr_t)k_pages % 16) ||
       ((uintptr_t)v_pages % 16) || (ld_q % 8) || (ld_out % 8)) {
     return AYK_BAD_ALIGNMENT;
@@ -323,9 +341,16 @@ AYK_API int ayk_attention_prefill(const void* q, int ld_q, const void* k_pages,
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return launch_kernel(attention_prefill_kernel, dim3(total_tiles, num_heads), dim3(128),
+  if (total_tiles > 65535) return AYK_TOO_LARGE;
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0) {
+    page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+  }
+  return launch_kernel(attention_prefill_kernel, dim3(num_heads, total_tiles), dim3(128),
                        PF_SMEM_BYTES, (cudaStream_t)stream, 1, (const __nv_bfloat16*)q, ld_q,
                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table,
                        table_stride, row_start, kv_len, (__nv_bfloat16*)out, ld_out, num_requests,
-                       num_kv_heads, num_heads / num_kv_heads, page_size, scale, window);
+                       num_kv_heads, num_heads / num_kv_heads, page_size, scale, window,
+                       total_tiles, page_shift);
 }
