@@ -148,6 +148,48 @@ __global__ void kv_store_kernel(const T* __restrict__ k, const T* __restrict__ v
   }
 }
 
+// The same in 16-byte pieces (8 bfloat16 or 4 float32), for rows and pages that start on 16
+// bytes: a piece never straddles two heads because head_dim is a multiple of 8. One CTA per
+// row; a thread's key and value pieces are all requested before the first is stored.
+template <typename T>
+__global__ void __launch_bounds__(256)
+kv_store_wide_kernel(const T* __restrict__ k, const T* __restrict__ v, int ld_kv,
+                     const int* __restrict__ slot_mapping, T* __restrict__ k_pages,
+                     T* __restrict__ v_pages, int num_kv_heads, int head_dim, int page_size) {
+  constexpr int EL = 16 / sizeof(T);
+  pdl_launch_dependents();
+  const int row = blockIdx.x;
+  const int slot = slot_mapping[row];  // the step's metadata: not written by the kernel ahead
+  pdl_wait();
+  if (slot < 0) return;
+  const int page = slot / page_size, within = slot % page_size;
+  const int pieces = num_kv_heads * head_dim / EL;
+  const int per_head = head_dim / EL;
+  const uint4* k_row = reinterpret_cast<const uint4*>(k + (size_t)row * ld_kv);
+  const uint4* v_row = reinterpret_cast<const uint4*>(v + (size_t)row * ld_kv);
+  const size_t base = ((size_t)page * num_kv_heads * page_size + within) * per_head;
+  const size_t head_step = (size_t)page_size * per_head;
+  uint4* k_dst = reinterpret_cast<uint4*>(k_pages);
+  uint4* v_dst = reinterpret_cast<uint4*>(v_pages);
+  for (int p0 = threadIdx.x; p0 < pieces; p0 += 2 * 256) {
+    const int p1 = p0 + 256;
+    const uint4 ka = k_row[p0], va = v_row[p0];
+    uint4 kb = ka, vb = va;
+    if (p1 < pieces) {
+      kb = k_row[p1];
+      vb = v_row[p1];
+    }
+    const size_t d0 = base + (size_t)(p0 / per_head) * head_step + p0 % per_head;
+    k_dst[d0] = ka;
+    v_dst[d0] = va;
+    if (p1 < pieces) {
+      const size_t d1 = base + (size_t)(p1 / per_head) * head_step + p1 % per_head;
+      k_dst[d1] = kb;
+      v_dst[d1] = vb;
+    }
+  }
+}
+
 template <typename T>
 int attention_simt(const void* q, int ld_q, const void* k_pages, const void* v_pages,
                    const int* block_table, int table_stride, const int* request_of_row,
@@ -179,6 +221,15 @@ int kv_store(const void* k, const void* v, int ld_kv, const int* slot_mapping, v
   if (num_rows < 0 || num_kv_heads < 1 || head_dim < 1 || page_size < 1 ||
       ld_kv < num_kv_heads * head_dim) {
     return AYK_BAD_ARGUMENT;
+  }
+  const size_t el = 16 / sizeof(T);
+  const bool wide = head_dim % 8 == 0 && ((uintptr_t)k % 16) == 0 && ((uintptr_t)v % 16) == 0 &&
+                    (size_t)ld_kv % el == 0 && ((uintptr_t)k_pages % 16) == 0 &&
+                    ((uintptr_t)v_pages % 16) == 0;
+  if (wide) {
+    return launch_kernel(kv_store_wide_kernel<T>, dim3(num_rows), dim3(256), 0, stream, 1,
+                         (const T*)k, (const T*)v, ld_kv, slot_mapping, (T*)k_pages,
+                         (T*)v_pages, num_kv_heads, head_dim, page_size);
   }
   return launch_kernel(kv_store_kernel<T>, dim3(num_rows), dim3(256), 0, stream, 1,
                        (const T*)k, (const T*)v, ld_kv, slot_mapping, (T*)k_pages, (T*)v_pages,

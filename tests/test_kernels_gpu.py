@@ -386,6 +386,33 @@ def test_attention_finds_a_far_key_among_hundreds(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,head_dim,page", [(25, 64, 16), (3, 12, 5), (2, 72, 8)])
+def test_kv_store_scatters_rows(dtype, heads, head_dim, page):
+    """Rows go to their slots and nowhere else, in 16-byte pieces where the shapes allow
+    (and element by element where they do not: a head size of 12)."""
+    ops = _ops()
+    rows, pages = 300, 80
+    width = heads * head_dim
+    qkv = _randn(rows, 3 * width, seed=23, dtype=dtype)
+    order = torch.randperm(pages * page, generator=torch.Generator().manual_seed(5))[:rows]
+    order[::7] = -1  # some rows store nothing
+    slots = order.to(torch.int32).to(DEV)
+    k_pages = torch.full((pages, heads, page, head_dim), float("nan"), dtype=dtype, device=DEV)
+    v_pages = torch.full_like(k_pages, float("nan"))
+    ops.kv_store(qkv[:, width:2 * width], qkv[:, 2 * width:], slots, k_pages, v_pages)
+    want_k = torch.full_like(k_pages, float("nan"))
+    want_v = torch.full_like(v_pages, float("nan"))
+    for r, slot in enumerate(order.tolist()):
+        if slot >= 0:
+            want_k[slot // page, :, slot % page] = qkv[r, width:2 * width].view(heads, head_dim)
+            want_v[slot // page, :, slot % page] = qkv[r, 2 * width:].view(heads, head_dim)
+    assert torch.equal(torch.nan_to_num(k_pages.float(), nan=-7.0),
+                       torch.nan_to_num(want_k.float(), nan=-7.0))
+    assert torch.equal(torch.nan_to_num(v_pages.float(), nan=-7.0),
+                       torch.nan_to_num(want_v.float(), nan=-7.0))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_kv_store_then_attend(dtype):
     """The store writes exactly the slots it is given; a padding row stores nothing and a
     padding request's rows come out zero."""
