@@ -395,26 +395,34 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
     // through distributed shared memory, in rank order; no scratch, no tickets
     cluster_sync_all();
     if (split == 0) {
+      // every remote value is requested before the first is used: the merge costs two trips
+      // through distributed shared memory (maxima and sums, then the values), not one per load
+      float m[8], l[8];
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        m[s] = s < splits ? ld_cluster_f32(peer_address(&c_share[0], (uint32_t)s)) : -INFINITY;
+        l[s] = s < splits ? ld_cluster_f32(peer_address(&c_share[1], (uint32_t)s)) : 0.f;
+      }
       float top = -INFINITY;
-      for (int s = 0; s < splits; ++s) {
-        top = fmaxf(top, ld_cluster_f32(peer_address(&c_share[0], (uint32_t)s)));
+#pragma unroll
+      for (int s = 0; s < 8; ++s) top = fmaxf(top, m[s]);
+      float w[8], denom = 0.f;
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {  // rank order: the sum does not change from run to run
+        w[s] = m[s] == -INFINITY ? 0.f : expf(m[s] - top);
+        denom += l[s] * w[s];
       }
-      float denom = 0.f;
-      for (int s = 0; s < splits; ++s) {
-        const float sm = ld_cluster_f32(peer_address(&c_share[0], (uint32_t)s));
-        if (sm != -INFINITY) {
-          denom += ld_cluster_f32(peer_address(&c_share[1], (uint32_t)s)) * expf(sm - top);
-        }
-      }
+      const float inv = 1.f / denom;
       for (int d = tid; d < head_dim; d += DEC_THREADS) {
-        float sum = 0.f;
-        for (int s = 0; s < splits; ++s) {
-          const float sm = ld_cluster_f32(peer_address(&c_share[0], (uint32_t)s));
-          if (sm != -INFINITY) {
-            sum += ld_cluster_f32(peer_address(&c_share[2 + d], (uint32_t)s)) * expf(sm - top);
-          }
+        float v[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          v[s] = s < splits ? ld_cluster_f32(peer_address(&c_share[2 + d], (uint32_t)s)) : 0.f;
         }
-        stf(dst + d, sum / denom);
+        float sum = 0.f;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) sum += v[s] * w[s];
+        stf(dst + d, sum * inv);
       }
     }
     cluster_sync_all();  // nobody leaves while rank 0 may still read its share
