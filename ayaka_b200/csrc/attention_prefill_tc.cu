@@ -1,0 +1,595 @@
+// Causal attention for prompt portions in bfloat16 over the paged cache, head size 64, with
+// both products on the 5th-generation tensor cores (tcgen05) and their accumulators in tensor
+// memory.
+//
+// A CTA owns 256 consecutive query rows of one request and one head, as two groups of 128,
+// and walks that request's keys 128 at a time from position 0 (or the window's first block)
+// up to the tile's last row. Seventeen warps, by role:
+//   warps 0-3, 4-7  softmax of group 0 and of group 1: a thread owns one query row. For every
+//              block it reads its row of S = Q K^T from tensor memory (twice: once for the row
+//              maximum, once to exponentiate), keeps the running reference maximum and sum in
+//              fp32 registers, writes P = exp2(S * scale * log2e - reference) as bf16 into
+//              shared memory in the layout the tensor core reads (128-byte swizzle), and
+//              rescales its group's output accumulator in tensor memory when the reference
+//              moved;
+//   warp 8     one thread issues the MMAs: S = Q K^T (4 x 128x128x16 per group) and O += P V
+//              (8 x 128x64x16 per group; V is read as stored, [key][64], as an MN-major
+//              operand), in the order PV0(j), S0(j+1), PV1(j), S1(j+1): while one group's
+//              softmax runs, the tensor core works for the other;
+//   warps 9-12, 13-16  gather Q and the K blocks, and the V blocks, from the pages with
+//              16-byte cp.async copies into a ring of three shared-memory stages (both groups
+//              share them).
+// mbarriers connect the roles; every wait is bounded (tc_common.cuh) and a wait that runs out
+// sets the status word. One CTA per SM: 192 KB of shared memory, 384 of the 512 tensor-memory
+// columns (S0, S1: 128 each; O0, O1: 64 each).
+//
+// The reference maximum moves only when the block's maximum exceeds it by more than 8 (in
+// log2 units), so most blocks do not touch the accumulator; probabilities stay below 2^8 and
+// the final division by the running sum makes the result the same function of the scores. A
+// row's blocks are aligned to absolute key positions, so its result does not depend on how
+// the prompt was cut or on the rows that share its tile.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace ayk {
+
+constexpr int FA_GM = 128;                  // query rows per group
+constexpr int FA_BM = 2 * FA_GM;            // query rows per CTA
+constexpr int FA_BN = 128;                  // keys per block
+constexpr int FA_HD = 64;                   // head size: one 128-byte swizzle row
+constexpr int FA_TILE = FA_GM * FA_HD * 2;  // bytes of a [128][64] bf16 tile
+constexpr int FA_STAGES = 3;                // K and V blocks in flight
+constexpr int FA_PRODUCERS = 4;              // warps that gather K, and as many for V
+constexpr int FA_THREADS = (9 + 2 * FA_PRODUCERS) * 32;
+constexpr float FA_LAZY = 8.f;              // how far a block's maximum may exceed the reference
+
+struct FaSmem {
+  static constexpr int Q = 0;                // two groups
+  static constexpr int K = Q + 2 * FA_TILE;          // FA_STAGES stages
+  static constexpr int V = K + FA_STAGES * FA_TILE;  // FA_STAGES stages
+  static constexpr int P = V + FA_STAGES * FA_TILE;  // per group [128 rows][128 keys] = two tiles
+  static constexpr int BAR = P + 4 * FA_TILE;
+  static constexpr int NUM_BARS = 1 + 4 * FA_STAGES + 8;
+  static constexpr int DYNAMIC = BAR + NUM_BARS * 8 + 16 + 1024;  // room to align the base
+};
+
+__device__ __forceinline__ void fa_cp_async16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void fa_cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N> __device__ __forceinline__ void fa_cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// 32 lanes x 32 columns back into tensor memory (the inverse of tmem_ld_32x32).
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(
+          taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]),
+      "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]),
+      "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]),
+      "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+// 2^x in one special-function instruction (2 ulp; exp2(-inf) = 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// Descriptor of an MN-major operand stored as rows of 128 bytes (64 bf16 along MN) with the
+// 128-byte swizzle, one row per K index: groups of 8 rows (8 values of K) are 1024 bytes
+// apart. `tile` points at the first of the 16 rows one MMA reads.
+__device__ __forceinline__ uint64_t umma_desc_mn128(const void* tile) {
+  const uint32_t addr = smem_u32(tile);
+  uint64_t desc = 0;
+  desc |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  desc |= (uint64_t)1 << 16;            // leading offset: between 64-wide MN groups (one here)
+  desc |= (uint64_t)(1024 >> 4) << 32;  // stride offset: between groups of 8 rows
+  desc |= (uint64_t)1 << 46;
+  desc |= (uint64_t)2 << 61;
+  return desc;
+}
+
+// FA_PRODUCERS warps (this one is number `part`) gather a block of 128 keys (or values) of one
+// head into a [128][64] tile: a warp's copies complete one after the other, at about one
+// 512-byte instruction per memory round trip (measured: 32 of them took 4.7 microseconds), so
+// several warps share a block. Row =
+// key, 16-byte piece c of row r at piece c ^ (r & 7). Keys outside [first_key, last_key] are
+// zero-filled: their pages may be gone (a window) or hold anything, and 0 * NaN would poison
+// the sum.
+__device__ __forceinline__ void fa_gather_block(uint8_t* tile,
+                                                const __nv_bfloat16* __restrict__ pages,
+                                                const int* __restrict__ table, int key0,
+                                                int first_key, int last_key, int num_kv_heads,
+                                                int kv_head, int page_size, int page_shift,
+                                                int lane, int part) {
+  const int piece = lane & 7;
+#pragma unroll 4
+  for (int t = part; t < FA_BN / 4; t += FA_PRODUCERS) {
+    const int r = t * 4 + (lane >> 3);
+    const int key = key0 + r;
+    const bool valid = key >= first_key && key <= last_key;
+    const __nv_bfloat16* src = pages;
+    if (valid) {
+      const int index = page_shift >= 0 ? key >> page_shift : key / page_size;
+      const int slot = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+      const int page = table[index];
+      src = pages + (((size_t)page * num_kv_heads + kv_head) * page_size + slot) * FA_HD +
+            piece * 8;
+    }
+    fa_cp_async16(tile + r * 128 + ((piece ^ (r & 7)) << 4), src, valid);
+  }
+}
+
+__global__ void __launch_bounds__(FA_THREADS)
+attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
+                            const __nv_bfloat16* __restrict__ k_pages,
+                            const __nv_bfloat16* __restrict__ v_pages,
+                            const int* __restrict__ block_table, int table_stride,
+                            const int* __restrict__ row_start, const int* __restrict__ kv_len,
+                            __nv_bfloat16* __restrict__ out, int ld_out, int num_requests,
+                            int num_kv_heads, int group, int page_size, float scale, int window,
+                            int total_tiles, int page_shift, int* __restrict__ status) {
+  extern __shared__ uint8_t fa_raw[];
+  uint8_t* smem = fa_raw + ((1024 - (smem_u32(fa_raw) & 1023)) & 1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FaSmem::BAR);
+  uint64_t* q_full = bars;        // one arrival per K producer warp
+  uint64_t* k_full = bars + 1;                   // [stage], one arrival per producer warp
+  uint64_t* k_empty = k_full + FA_STAGES;        // [stage], MMA commits
+  uint64_t* v_full = k_empty + FA_STAGES;        // [stage]
+  uint64_t* v_empty = v_full + FA_STAGES;        // [stage]
+  uint64_t* s_full = v_empty + FA_STAGES;        // [group] MMA commit: S is in tensor memory
+  uint64_t* s_empty = s_full + 2;   // [group] 4 arrivals: every softmax warp has read S
+  uint64_t* p_full = s_empty + 2;   // [group] 4 arrivals: P is in shared memory, O is rescaled
+  uint64_t* pv_done = p_full + 2;   // [group] MMA commit: O += P V has finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + FaSmem::NUM_BARS);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 512;  // S0: 0..127, S1: 128..255, O0: 256..319, O1: 320..383
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, FA_PRODUCERS);
+    for (int s = 0; s < FA_STAGES; ++s) {
+      mbar_init(&k_full[s], FA_PRODUCERS);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], FA_PRODUCERS);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 4);
+      mbar_init(&p_full[s], 4);
+      mbar_init(&pv_done[s], 1);
+    }
+    *failed = 0;
+    mbar_fence_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  // Which request and which 256-row tile of it: heads along grid.x, tiles along grid.y from
+  // the last one down (the longest first).
+  int tile = total_tiles - 1 - (int)blockIdx.y, req = 0, rows_b = 0;
+  for (; req < num_requests; ++req) {
+    rows_b = row_start[req + 1] - row_start[req];
+    const int tiles = (rows_b + FA_BM - 1) / FA_BM;
+    if (tile < tiles) break;
+    tile -= tiles;
+  }
+  const int head = blockIdx.x;
+  const int kv_head = head / group;
+  bool work = req < num_requests;
+  int first_row = 0, nrows = 0, length = 0;
+  if (work) {
+    first_row = row_start[req] + tile * FA_BM;
+    nrows = rows_b - tile * FA_BM < FA_BM ? rows_b - tile * FA_BM : FA_BM;
+    length = kv_len[req];
+    if (length == 0) {  // a padding request: zeros
+      for (int i = threadIdx.x; i < nrows * (FA_HD / 8); i += FA_THREADS) {
+        *reinterpret_cast<uint4*>(out + (size_t)(first_row + i / (FA_HD / 8)) * ld_out +
+                                  head * FA_HD + (i % (FA_HD / 8)) * 8) =
+            make_uint4(0u, 0u, 0u, 0u);
+      }
+      work = false;
+    }
+  }
+  if (work) {
+    const int pos0 = length - rows_b + tile * FA_BM;  // position of the tile's first row
+    const int last_key = pos0 + nrows - 1;
+    const int lo_min = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    // Each group's blocks: from the block of its first row's first visible key to the block
+    // of its last row. Group 1 has none when the tile has at most 128 rows.
+    int blo[2], bhi[2];
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      const int g_pos0 = pos0 + g * FA_GM;
+      const int g_rows = nrows - g * FA_GM < FA_GM ? nrows - g * FA_GM : FA_GM;
+      const int g_lo = (window > 0 && g_pos0 - window + 1 > 0) ? g_pos0 - window + 1 : 0;
+      blo[g] = g_lo / FA_BN;
+      bhi[g] = g_rows > 0 ? (g_pos0 + g_rows - 1) / FA_BN : blo[g] - 1;
+    }
+    const int jlo = blo[0];  // group 0 starts first and group 1 (if any) ends last
+    const int jhi = bhi[1] >= blo[1] ? bhi[1] : bhi[0];
+    const int num_blocks = jhi - jlo + 1;
+    const int* table = block_table + (size_t)req * table_stride;
+    uint8_t* q_s = smem + FaSmem::Q;
+    uint8_t* p_s = smem + FaSmem::P;
+
+    if (warp >= 9) {
+      // ---- producers: warps 9.. bring Q and the K blocks, the next FA_PRODUCERS the V blocks
+      const bool keys = warp < 9 + FA_PRODUCERS;
+      const int part = (warp - 9) % FA_PRODUCERS;
+      uint64_t* full = keys ? k_full : v_full;
+      uint64_t* empty = keys ? k_empty : v_empty;
+      uint8_t* stages = smem + (keys ? FaSmem::K : FaSmem::V);
+      const __nv_bfloat16* pages = keys ? k_pages : v_pages;
+      if (keys) {
+        const int piece = lane & 7;
+        for (int t = part; t < FA_BM / 4; t += FA_PRODUCERS) {
+          const int r = t * 4 + (lane >> 3);
+          const bool valid = r < nrows;
+          const __nv_bfloat16* src =
+              q + (size_t)(first_row + (valid ? r : 0)) * ld_q + head * FA_HD + piece * 8;
+          fa_cp_async16(q_s + r * 128 + ((piece ^ (r & 7)) << 4), src, valid);
+        }
+        // (no commit: Q lands with the first block of keys)
+      }
+      bool ok = true;
+      for (int jj = 0; jj < num_blocks && ok; ++jj) {
+        const int stage = jj % FA_STAGES;
+        if (jj >= FA_STAGES) {  // the stage's last tenant must have been read by its MMAs
+          if (lane == 0) ok = mbar_wait(&empty[stage], (uint32_t)(jj / FA_STAGES - 1) & 1u);
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
+        }
+        fa_gather_block(stages + stage * FA_TILE, pages, table, (jlo + jj) * FA_BN, lo_min,
+                        last_key, num_kv_heads, kv_head, page_size, page_shift, lane, part);
+        fa_cp_async_commit();
+        // The block before has landed once only this one is still in flight: publish it.
+        // (With three stages the wait for this block's stage, above, concerns a block the
+        // consumer finished two blocks ago, so it never holds a publication back.)
+        fa_cp_async_wait<1>();
+        fence_proxy_async_shared();
+        __syncwarp();
+        if (lane == 0 && jj > 0) {
+          mbar_arrive(&full[(jj - 1) % FA_STAGES]);
+          if (keys && jj == 1) mbar_arrive(q_full);
+        }
+      }
+      fa_cp_async_wait<0>();
+      fence_proxy_async_shared();
+      __syncwarp();
+      if (lane == 0 && ok) {
+        mbar_arrive(&full[(num_blocks - 1) % FA_STAGES]);
+        if (keys && num_blocks == 1) mbar_arrive(q_full);
+      }
+      if (!ok && lane == 0) *failed = 1;
+    } else if (warp == 8) {
+      // ---- MMA issuer ---------------------------------------------------------------------
+      if (lane == 0) {
+        constexpr uint32_t idesc_s = umma_idesc_bf16(FA_GM, FA_BN);
+        constexpr uint32_t idesc_o = umma_idesc_bf16(FA_GM, FA_HD) | (1u << 16);  // B: MN-major
+        int ns[2] = {0, 0}, npv[2] = {0, 0};  // blocks issued so far, per group
+        bool ok = mbar_wait(q_full, 0);
+        auto active = [&](int g, int j) { return j >= blo[g] && j <= bhi[g]; };
+        // S_g = Q_g K^T for block j (its K stage is known to be full)
+        auto issue_s = [&](int g, int j) {
+          if (ns[g] >= 1 && ok) ok = mbar_wait(&s_empty[g], (uint32_t)(ns[g] - 1) & 1u);
+          if (!ok) return;
+          tc_fence_after();
+          const uint8_t* k_tile = smem + FaSmem::K + ((j - jlo) % FA_STAGES) * FA_TILE;
+          const uint8_t* q_tile = q_s + g * FA_TILE;
+#pragma unroll
+          for (int k = 0; k < FA_HD / 16; ++k) {
+            umma_f16(tmem_base + (uint32_t)(g * FA_BN), umma_desc_k128(q_tile, k * 32),
+                     umma_desc_k128(k_tile, k * 32), idesc_s, k != 0);
+          }
+          umma_commit(&s_full[g]);
+          ++ns[g];
+        };
+        // O_g += P_g V for block j (its V stage is known to be full)
+        auto issue_pv = [&](int g, int j) {
+          if (ok) ok = mbar_wait(&p_full[g], (uint32_t)npv[g] & 1u);
+          if (!ok) return;
+          tc_fence_after();
+          const uint8_t* v_tile = smem + FaSmem::V + ((j - jlo) % FA_STAGES) * FA_TILE;
+          const uint8_t* p_tile = p_s + g * 2 * FA_TILE;
+#pragma unroll
+          for (int k = 0; k < FA_BN / 16; ++k) {
+            umma_f16(tmem_base + (uint32_t)(2 * FA_BN + g * FA_HD),
+                     umma_desc_k128(p_tile + (k >> 2) * FA_TILE, (k & 3) * 32),
+                     umma_desc_mn128(v_tile + k * 16 * 128), idesc_o, (npv[g] | k) != 0);
+          }
+          umma_commit(&pv_done[g]);
+          ++npv[g];
+        };
+        if (ok) ok = mbar_wait(&k_full[0], 0);
+        for (int g = 0; g < 2 && ok; ++g) {
+          if (active(g, jlo)) issue_s(g, jlo);
+        }
+        if (ok) umma_commit(&k_empty[0]);
+        for (int j = jlo; j <= jhi && ok; ++j) {
+          const int jj = j - jlo, stage = jj % FA_STAGES, after = (jj + 1) % FA_STAGES;
+          const bool next = j < jhi;
+          ok = mbar_wait(&v_full[stage], (uint32_t)(jj / FA_STAGES) & 1u);
+          if (!ok) break;
+          if (active(0, j)) issue_pv(0, j);
+          if (ok && next) ok = mbar_wait(&k_full[after], (uint32_t)((jj + 1) / FA_STAGES) & 1u);
+          if (!ok) break;
+          if (next && active(0, j + 1)) issue_s(0, j + 1);
+          if (active(1, j)) issue_pv(1, j);
+          if (!ok) break;
+          umma_commit(&v_empty[stage]);
+          if (next && active(1, j + 1)) issue_s(1, j + 1);
+          if (!ok) break;
+          if (next) umma_commit(&k_empty[after]);
+        }
+        if (!ok) *failed = 1;
+      }
+      __syncwarp();
+    } else if (bhi[warp >> 2] >= blo[warp >> 2]) {
+      // ---- softmax: warps 0-3 own the rows of group 0, warps 4-7 those of group 1 ----------
+      const int g = warp >> 2;
+      const int r = threadIdx.x & (FA_GM - 1);  // the row inside the group
+      const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+      const uint32_t s_acc = tmem_base + (uint32_t)(g * FA_BN) + lane_base;
+      const uint32_t o_acc = tmem_base + (uint32_t)(2 * FA_BN + g * FA_HD) + lane_base;
+      const int g_pos0 = pos0 + g * FA_GM;
+      const int pos = g_pos0 + r;
+      const int after = window > 0 ? pos - window : -2147483647 - 1;  // keys > after are seen
+      const float scale2 = scale * 1.4426950408889634f;  // scores in units of log2
+      float ref = -INFINITY, sum = 0.f;
+      uint8_t* p_row = p_s + g * 2 * FA_TILE + r * 128;
+      const int swz = r & 7;
+      const int my_blocks = bhi[g] - blo[g] + 1;
+      bool ok = true;
+      for (int n = 0; n < my_blocks; ++n) {
+        const int key0 = (blo[g] + n) * FA_BN;
+        if (lane == 0) ok = mbar_wait(&s_full[g], (uint32_t)n & 1u);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        tc_fence_after();
+        // A block wholly before the group's first row (and no window) has nothing to mask.
+        // The masked variant selects without branching: per element it is two integer
+        // compares and a select.
+        const bool all_seen = window == 0 && key0 + FA_BN - 1 <= g_pos0;
+        // pass 1: the row's maximum over the block (of the raw scores: the scale is positive)
+        float top = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < FA_BN / 32; ++c) {
+          uint32_t raw[32];
+          tmem_ld_32x32(s_acc + (uint32_t)(c * 32), raw);
+          tmem_ld_wait();
+          float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
+          if (all_seen) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              t0 = fmaxf(t0, __uint_as_float(raw[i]));
+              t1 = fmaxf(t1, __uint_as_float(raw[i + 1]));
+              t2 = fmaxf(t2, __uint_as_float(raw[i + 2]));
+              t3 = fmaxf(t3, __uint_as_float(raw[i + 3]));
+            }
+          } else {
+            const int key = key0 + c * 32;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const bool a0 = (key + i <= pos) & (key + i > after);
+              const bool a1 = (key + i + 1 <= pos) & (key + i + 1 > after);
+              const bool a2 = (key + i + 2 <= pos) & (key + i + 2 > after);
+              const bool a3 = (key + i + 3 <= pos) & (key + i + 3 > after);
+              t0 = fmaxf(t0, a0 ? __uint_as_float(raw[i]) : -INFINITY);
+              t1 = fmaxf(t1, a1 ? __uint_as_float(raw[i + 1]) : -INFINITY);
+              t2 = fmaxf(t2, a2 ? __uint_as_float(raw[i + 2]) : -INFINITY);
+              t3 = fmaxf(t3, a3 ? __uint_as_float(raw[i + 3]) : -INFINITY);
+            }
+          }
+          top = fmaxf(top, fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)));
+        }
+        top *= scale2;
+        // the reference moves only when the block's maximum leaves it far behind
+        float alpha = 1.f;
+        if (top > ref + FA_LAZY || (ref == -INFINITY && top > -INFINITY)) {
+          alpha = fast_exp2(ref - top);  // 0 when there was no reference yet
+          ref = top;
+        }
+        // P's shared memory and the accumulator are free once the product before has finished
+        if (n > 0) {
+          if (lane == 0) ok = mbar_wait(&pv_done[g], (uint32_t)(n - 1) & 1u);
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
+          tc_fence_after();
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+            for (int c = 0; c < FA_HD / 32; ++c) {
+              uint32_t raw[32];
+              tmem_ld_32x32(o_acc + (uint32_t)(c * 32), raw);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * alpha);
+              tmem_st_32x32(o_acc + (uint32_t)(c * 32), raw);
+            }
+            tmem_st_wait();
+          }
+        }
+        sum *= alpha;
+        const float offset = ref == -INFINITY ? 0.f : ref;
+        // pass 2: probabilities, their sum, and P as the next product's A operand
+        float part0 = 0.f, part1 = 0.f, part2 = 0.f, part3 = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < FA_BN / 32; ++c) {
+          uint32_t raw[32];
+          tmem_ld_32x32(s_acc + (uint32_t)(c * 32), raw);
+          tmem_ld_wait();
+          if (c == FA_BN / 32 - 1) {  // S has been read: the next block's scores may overwrite it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[g]);
+          }
+          float p[32];
+          if (all_seen) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              p[i] = fast_exp2(fmaf(__uint_as_float(raw[i]), scale2, -offset));
+            }
+          } else {
+            const int key = key0 + c * 32;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const bool seen = (key + i <= pos) & (key + i > after);
+              const float e = fmaf(__uint_as_float(raw[i]), scale2, -offset);
+              p[i] = fast_exp2(seen ? e : -INFINITY);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            part0 += p[i];
+            part1 += p[i + 1];
+            part2 += p[i + 2];
+            part3 += p[i + 3];
+          }
+          uint8_t* dst = p_row + (c >> 1) * FA_TILE;
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            uint4 packed;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(p[h * 8], p[h * 8 + 1]);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(p[h * 8 + 2], p[h * 8 + 3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(p[h * 8 + 4], p[h * 8 + 5]);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(p[h * 8 + 6], p[h * 8 + 7]);
+            packed.x = *reinterpret_cast<uint32_t*>(&h0);
+            packed.y = *reinterpret_cast<uint32_t*>(&h1);
+            packed.z = *reinterpret_cast<uint32_t*>(&h2);
+            packed.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(dst + ((((c & 1) * 4 + h) ^ swz) << 4)) = packed;
+          }
+        }
+        sum += (part0 + part1) + (part2 + part3);
+        fence_proxy_async_shared();  // P: generic-proxy writes, read by the tensor core
+        tc_fence_before();           // the accumulator's rescaling, before the MMA thread goes on
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[g]);
+      }
+      if (ok) {
+        if (lane == 0) ok = mbar_wait(&pv_done[g], (uint32_t)(my_blocks - 1) & 1u);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+      }
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.f / sum;
+        const int row = g * FA_GM + r;  // inside the tile
+        __nv_bfloat16* dst = out + (size_t)(first_row + row) * ld_out + head * FA_HD;
+#pragma unroll 1
+        for (int c = 0; c < FA_HD / 32; ++c) {
+          uint32_t raw[32];
+          tmem_ld_32x32(o_acc + (uint32_t)(c * 32), raw);
+          tmem_ld_wait();
+          if (row < nrows) {
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              uint4 packed;
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(raw[h * 8]) * inv,
+                                                        __uint_as_float(raw[h * 8 + 1]) * inv);
+              __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(raw[h * 8 + 2]) * inv,
+                                                        __uint_as_float(raw[h * 8 + 3]) * inv);
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(raw[h * 8 + 4]) * inv,
+                                                        __uint_as_float(raw[h * 8 + 5]) * inv);
+              __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(raw[h * 8 + 6]) * inv,
+                                                        __uint_as_float(raw[h * 8 + 7]) * inv);
+              packed.x = *reinterpret_cast<uint32_t*>(&h0);
+              packed.y = *reinterpret_cast<uint32_t*>(&h1);
+              packed.z = *reinterpret_cast<uint32_t*>(&h2);
+              packed.w = *reinterpret_cast<uint32_t*>(&h3);
+              *reinterpret_cast<uint4*>(dst + c * 32 + h * 8) = packed;
+            }
+          }
+          __syncwarp();
+        }
+      } else if (lane == 0) {
+        *failed = 1;
+      }
+    }
+  }
+
+  // ---- teardown ---------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*failed != 0 && threadIdx.x == 0) atomicExch(status, AYK_WAIT_TIMEOUT);
+  if (warp == 8) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace ayk
+
+AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
+
+// Query rows per CTA: the caller sizes the grid with it.
+AYK_API int ayk_attention_prefill_tc_rows() { return ayk::FA_BM; }
+
+// bfloat16, head size 64 and a positive scale only (AYK_BAD_ARGUMENT otherwise: use the
+// mma.sync kernel). q/out
+// rows are 16-byte aligned (ld multiples of 8 elements). `total_tiles` = sum over requests of
+// ceil(rows / 256), from the caller's host copy of the rows. `status` is one device int that
+// the kernel sets to AYK_WAIT_TIMEOUT if a wait ran out.
+AYK_API int ayk_attention_prefill_tc(const void* q, int ld_q, const void* k_pages,
+                                     const void* v_pages, const int* block_table,
+                                     int table_stride, const int* row_start, const int* kv_len,
+                                     void* out, int ld_out, int num_requests, int total_tiles,
+                                     int num_heads, int num_kv_heads, int head_dim, int page_size,
+                                     float scale, int window, int* status, void* stream) {
+  using namespace ayk;
+  if (num_requests == 0 || total_tiles == 0) return AYK_OK;
+  if (head_dim != FA_HD || status == nullptr || !(scale > 0.f)) return AYK_BAD_ARGUMENT;
+  if (num_requests < 0 || total_tiles < 0 || num_heads < 1 || num_kv_heads < 1 ||
+      num_heads % num_kv_heads || page_size < 1 || table_stride < 1 || window < 0) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (total_tiles > 65535) return AYK_TOO_LARGE;
+  if (((uintptr_t)q % 16) || ((uintptr_t)out % 16) || ((uintptr_t)k_pages % 16) ||
+      ((uintptr_t)v_pages % 16) || (ld_q % 8) || (ld_out % 8)) {
+    return AYK_BAD_ALIGNMENT;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         FaSmem::DYNAMIC);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0) {
+    page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+  }
+  return launch_kernel(attention_prefill_tc_kernel, dim3(num_heads, total_tiles),
+                       dim3(FA_THREADS), FaSmem::DYNAMIC, (cudaStream_t)stream, 1,
+                       (const __nv_bfloat16*)q, ld_q, (const __nv_bfloat16*)k_pages,
+                       (const __nv_bfloat16*)v_pages, block_table, table_stride, row_start,
+                       kv_len, (__nv_bfloat16*)out, ld_out, num_requests, num_kv_heads,
+                       num_heads / num_kv_heads, page_size, scale, window, total_tiles,
+                       page_shift, status);
+}

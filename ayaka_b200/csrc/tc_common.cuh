@@ -40,14 +40,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+// One attempt: true if the phase with the given parity has completed. The hardware may park
+// the thread for up to `suspend_ns` while the phase is pending and wakes it when the phase
+// completes, so a waiting warp does not take issue slots from the warps that work.
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity,
+                                         uint32_t suspend_ns = 4000) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(suspend_ns)
       : "memory");
   return ok != 0;
 }

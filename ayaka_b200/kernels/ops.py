@@ -283,15 +283,22 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
     check(status, op)
 
 
+#: Which kernel :func:`attention_prefill` launches for head size 64: ``"tcgen05"`` (both
+#: products on the 5th-generation tensor cores, accumulators in tensor memory) or ``"mma"``
+#: (the warp-level kernel that serves every other head size); tests switch it.
+PREFILL_ATTENTION = "tcgen05"
+
+
 def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       block_table: torch.Tensor, row_start: torch.Tensor, kv_len: torch.Tensor,
                       out: torch.Tensor, *, num_heads: int, scale: float, host_rows: list[int],
-                      window: int = 0) -> None:
+                      window: int = 0, kernel: str | None = None) -> None:
     """Causal attention of prompt portions in bfloat16 on the tensor cores.
 
     Request ``b`` owns rows ``row_start[b] .. row_start[b + 1]`` of ``q`` and ``out``, which
     are the last rows of its ``kv_len[b]`` cached tokens; ``host_rows`` is the host copy of
-    the row counts (the grid is sized from it). The library is compiled for the head size.
+    the row counts (the grid is sized from it). Head size 64 runs on tcgen05; the other head
+    sizes on a warp-level kernel compiled for the head size (``kernel`` forces one of them).
     """
     op = "attention_prefill"
     _need(op, "q", q, torch.bfloat16, 2)
@@ -311,6 +318,21 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         raise BackendError(f"{op}: shapes do not fit")
     if head_dim % 16 or not 16 <= head_dim <= 256:
         raise BackendError(f"{op}: head_dim must be a multiple of 16 in [16, 256]")
+    which = kernel or (PREFILL_ATTENTION if head_dim == 64 and scale > 0 else "mma")
+    if which == "tcgen05":
+        if head_dim != 64:
+            raise BackendError(f"{op}: the tcgen05 kernel serves head size 64, not {head_dim}")
+        lib = library("attention_prefill_tc")
+        tile_rows = lib.ayk_attention_prefill_tc_rows()
+        tiles = sum(-(-rows // tile_rows) for rows in host_rows)
+        status = lib.ayk_attention_prefill_tc(
+            _ptr(q), c_int(q.stride(0)), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+            c_int(block_table.stride(0)), _ptr(row_start), _ptr(kv_len), _ptr(out),
+            c_int(out.stride(0)), c_int(count), c_int(tiles), c_int(num_heads), c_int(kv_heads),
+            c_int(head_dim), c_int(page_size), c_float(scale), c_int(window),
+            _ptr(_status_word(q.device)), _stream())
+        check(status, op)
+        return
     tiles = sum(-(-rows // 64) for rows in host_rows)
     fn = library("attention_prefill", AYK_HEAD_DIM=head_dim).ayk_attention_prefill
     status = fn(_ptr(q), c_int(q.stride(0)), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),

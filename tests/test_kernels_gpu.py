@@ -444,18 +444,26 @@ def test_kv_store_then_attend(dtype):
     assert torch.equal(out[3].float(), torch.zeros(width, device=DEV))
 
 
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
 @pytest.mark.parametrize("case", ATTN_CASES + [
     ((1024, 1024), (1024, 1024), 25, 25, 64, 16, 0),
     ((700, 3, 200), (130, 3, 65), 4, 2, 32, 16, 0),
     ((500,), (250,), 2, 2, 64, 128, 100),
+    ((700, 3, 200, 129), (130, 3, 65, 129), 6, 2, 64, 16, 0),
+    ((3000,), (1500,), 2, 1, 64, 12, 0),
+    ((900, 260), (513, 255), 3, 3, 64, 8, 300),
 ])
-def test_attention_prefill_tensor_cores(case):
-    """The bfloat16 flash kernel for prompt portions: tiles of 64 rows, every head size class,
-    grouped heads, windows, requests of one row beside long ones, pages in scrambled order."""
+def test_attention_prefill_tensor_cores(case, kernel):
+    """The bfloat16 flash kernels for prompt portions (tcgen05 for head size 64, tiles of 128
+    rows; mma.sync for every head size, tiles of 64): every head size class, grouped heads,
+    windows, requests of one row beside long ones, page sizes that are no power of two, pages
+    in scrambled order."""
     ops = _ops()
     lengths, rows, heads, kv_heads, head_dim, page, window = case
     if head_dim % 16:
         pytest.skip("head sizes are multiples of 16")
+    if kernel == "tcgen05" and head_dim != 64:
+        pytest.skip("the tcgen05 kernel serves head size 64")
     q, k_pages, v_pages, table, req, pos, seqs = _paged_case(
         lengths, rows, heads, kv_heads, head_dim, page, torch.bfloat16, seed=25, boost=(699, 3))
     n = q.shape[0]
@@ -467,7 +475,9 @@ def test_attention_prefill_tensor_cores(case):
     out = torch.full((n + 2, heads * head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
     scale = 0.7 / math.sqrt(head_dim)
     ops.attention_prefill(q, k_pages, v_pages, table, row_start, kv_len, out, num_heads=heads,
-                          scale=scale, host_rows=list(rows), window=window)
+                          scale=scale, host_rows=list(rows), window=window, kernel=kernel)
+    from ayaka_b200.kernels import gemm_tc
+    gemm_tc.check_status(q.device)
     expected = _attention_reference(seqs, lengths, rows, heads, kv_heads, scale, window)
     torch.testing.assert_close(out[:n].double().cpu(), expected, rtol=2e-2, atol=2e-2)
     assert torch.isnan(out[n:].float()).all()
