@@ -372,56 +372,99 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
         tc_fence_after();
-        // A block wholly before the group's first row (and no window) has nothing to mask.
-        // The masked variant selects without branching: per element it is two integer
-        // compares and a select.
-        const bool all_seen = window == 0 && key0 + FA_BN - 1 <= g_pos0;
-        // pass 1: the row's maximum over the block (of the raw scores: the scale is positive)
-        float top = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < FA_BN / 32; ++c) {
-          uint32_t raw[32];
-          tmem_ld_32x32(s_acc + (uint32_t)(c * 32), raw);
-          tmem_ld_wait();
-          float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
-          if (all_seen) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              t0 = fmaxf(t0, __uint_as_float(raw[i]));
-              t1 = fmaxf(t1, __uint_as_float(raw[i + 1]));
-              t2 = fmaxf(t2, __uint_as_float(raw[i + 2]));
-              t3 = fmaxf(t3, __uint_as_float(raw[i + 3]));
-            }
-          } else {
-            const int key = key0 + c * 32;
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              const bool a0 = (key + i <= pos) & (key + i > after);
-              const bool a1 = (key + i + 1 <= pos) & (key + i + 1 > after);
-              const bool a2 = (key + i + 2 <= pos) & (key + i + 2 > after);
-              const bool a3 = (key + i + 3 <= pos) & (key + i + 3 > after);
-              t0 = fmaxf(t0, a0 ? __uint_as_float(raw[i]) : -INFINITY);
-              t1 = fmaxf(t1, a1 ? __uint_as_float(raw[i + 1]) : -INFINITY);
-              t2 = fmaxf(t2, a2 ? __uint_as_float(raw[i + 2]) : -INFINITY);
-              t3 = fmaxf(t3, a3 ? __uint_as_float(raw[i + 3]) : -INFINITY);
-            }
-          }
-          top = fmaxf(top, fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)));
-        }
-        top *= scale2;
-        // the reference moves only when the block's maximum leaves it far behind
-        float alpha = 1.f;
-        if (top > ref + FA_LAZY || (ref == -INFINITY && top > -INFINITY)) {
-          alpha = fast_exp2(ref - top);  // 0 when there was no reference yet
-          ref = top;
-        }
         // P's shared memory and the accumulator are free once the product before has finished
+        // (it was issued a whole softmax ago: this wait is almost always over already)
         if (n > 0) {
           if (lane == 0) ok = mbar_wait(&pv_done[g], (uint32_t)(n - 1) & 1u);
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) break;
           tc_fence_after();
-          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+        }
+        // A block wholly before the group's first row (and no window) has nothing to mask.
+        // The masked variant selects without branching: per element it is two integer
+        // compares and a select.
+        const bool all_seen = window == 0 && key0 + FA_BN - 1 <= g_pos0;
+        // One pass over the scores: exponentiate against the reference the row already has
+        // and find the block's maximum on the way. Only if that maximum leaves the reference
+        // more than FA_LAZY behind (the first block, and now and then an early one) does the
+        // reference move; then the accumulator is rescaled and the pass runs a second time.
+        float part = 0.f;
+        for (int attempt = 0;; ++attempt) {
+          const float offset = ref == -INFINITY ? 0.f : ref;
+          float part0 = 0.f, part1 = 0.f, part2 = 0.f, part3 = 0.f;
+          float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
+#pragma unroll 1
+          for (int c = 0; c < FA_BN / 32; ++c) {
+            uint32_t raw[32];
+            tmem_ld_32x32(s_acc + (uint32_t)(c * 32), raw);
+            tmem_ld_wait();
+            float p[32];
+            if (all_seen) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                t0 = fmaxf(t0, __uint_as_float(raw[i]));
+                t1 = fmaxf(t1, __uint_as_float(raw[i + 1]));
+                t2 = fmaxf(t2, __uint_as_float(raw[i + 2]));
+                t3 = fmaxf(t3, __uint_as_float(raw[i + 3]));
+              }
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                p[i] = fast_exp2(fmaf(__uint_as_float(raw[i]), scale2, -offset));
+              }
+            } else {
+              const int key = key0 + c * 32;
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                const bool a0 = (key + i <= pos) & (key + i > after);
+                const bool a1 = (key + i + 1 <= pos) & (key + i + 1 > after);
+                const bool a2 = (key + i + 2 <= pos) & (key + i + 2 > after);
+                const bool a3 = (key + i + 3 <= pos) & (key + i + 3 > after);
+                const float x0 = a0 ? __uint_as_float(raw[i]) : -INFINITY;
+                const float x1 = a1 ? __uint_as_float(raw[i + 1]) : -INFINITY;
+                const float x2 = a2 ? __uint_as_float(raw[i + 2]) : -INFINITY;
+                const float x3 = a3 ? __uint_as_float(raw[i + 3]) : -INFINITY;
+                t0 = fmaxf(t0, x0);
+                t1 = fmaxf(t1, x1);
+                t2 = fmaxf(t2, x2);
+                t3 = fmaxf(t3, x3);
+                p[i] = fast_exp2(fmaf(x0, scale2, -offset));  // exp2(-inf) = 0
+                p[i + 1] = fast_exp2(fmaf(x1, scale2, -offset));
+                p[i + 2] = fast_exp2(fmaf(x2, scale2, -offset));
+                p[i + 3] = fast_exp2(fmaf(x3, scale2, -offset));
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              part0 += p[i];
+              part1 += p[i + 1];
+              part2 += p[i + 2];
+              part3 += p[i + 3];
+            }
+            uint8_t* dst = p_row + (c >> 1) * FA_TILE;
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              uint4 packed;
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(p[h * 8], p[h * 8 + 1]);
+              __nv_bfloat162 h1 = __floats2bfloat162_rn(p[h * 8 + 2], p[h * 8 + 3]);
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(p[h * 8 + 4], p[h * 8 + 5]);
+              __nv_bfloat162 h3 = __floats2bfloat162_rn(p[h * 8 + 6], p[h * 8 + 7]);
+              packed.x = *reinterpret_cast<uint32_t*>(&h0);
+              packed.y = *reinterpret_cast<uint32_t*>(&h1);
+              packed.z = *reinterpret_cast<uint32_t*>(&h2);
+              packed.w = *reinterpret_cast<uint32_t*>(&h3);
+              *reinterpret_cast<uint4*>(dst + ((((c & 1) * 4 + h) ^ swz) << 4)) = packed;
+            }
+          }
+          part = (part0 + part1) + (part2 + part3);
+          const float top = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)) * scale2;
+          const bool moves = top > ref + FA_LAZY || (ref == -INFINITY && top > -INFINITY);
+          if (attempt == 1 || !__any_sync(0xffffffffu, moves)) break;
+          float alpha = 1.f;
+          if (moves) {
+            alpha = fast_exp2(ref - top);  // 0 when there was no reference yet
+            ref = top;
+          }
+          if (n > 0) {
 #pragma unroll 1
             for (int c = 0; c < FA_HD / 32; ++c) {
               uint32_t raw[32];
@@ -433,61 +476,14 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
             }
             tmem_st_wait();
           }
+          sum *= alpha;
         }
-        sum *= alpha;
-        const float offset = ref == -INFINITY ? 0.f : ref;
-        // pass 2: probabilities, their sum, and P as the next product's A operand
-        float part0 = 0.f, part1 = 0.f, part2 = 0.f, part3 = 0.f;
-#pragma unroll 1
-        for (int c = 0; c < FA_BN / 32; ++c) {
-          uint32_t raw[32];
-          tmem_ld_32x32(s_acc + (uint32_t)(c * 32), raw);
-          tmem_ld_wait();
-          if (c == FA_BN / 32 - 1) {  // S has been read: the next block's scores may overwrite it
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[g]);
-          }
-          float p[32];
-          if (all_seen) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              p[i] = fast_exp2(fmaf(__uint_as_float(raw[i]), scale2, -offset));
-            }
-          } else {
-            const int key = key0 + c * 32;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const bool seen = (key + i <= pos) & (key + i > after);
-              const float e = fmaf(__uint_as_float(raw[i]), scale2, -offset);
-              p[i] = fast_exp2(seen ? e : -INFINITY);
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            part0 += p[i];
-            part1 += p[i + 1];
-            part2 += p[i + 2];
-            part3 += p[i + 3];
-          }
-          uint8_t* dst = p_row + (c >> 1) * FA_TILE;
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            uint4 packed;
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(p[h * 8], p[h * 8 + 1]);
-            __nv_bfloat162 h1 = __floats2bfloat162_rn(p[h * 8 + 2], p[h * 8 + 3]);
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(p[h * 8 + 4], p[h * 8 + 5]);
-            __nv_bfloat162 h3 = __floats2bfloat162_rn(p[h * 8 + 6], p[h * 8 + 7]);
-            packed.x = *reinterpret_cast<uint32_t*>(&h0);
-            packed.y = *reinterpret_cast<uint32_t*>(&h1);
-            packed.z = *reinterpret_cast<uint32_t*>(&h2);
-            packed.w = *reinterpret_cast<uint32_t*>(&h3);
-            *reinterpret_cast<uint4*>(dst + ((((c & 1) * 4 + h) ^ swz) << 4)) = packed;
-          }
-        }
-        sum += (part0 + part1) + (part2 + part3);
+        sum += part;
+        // S has been read for the last time: the next block's scores may overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[g]);
         fence_proxy_async_shared();  // P: generic-proxy writes, read by the tensor core
-        tc_fence_before();           // the accumulator's rescaling, before the MMA thread goes on
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_full[g]);
       }
