@@ -318,7 +318,10 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         raise BackendError(f"{op}: shapes do not fit")
     if head_dim % 16 or not 16 <= head_dim <= 256:
         raise BackendError(f"{op}: head_dim must be a multiple of 16 in [16, 256]")
-    which = kernel or (PREFILL_ATTENTION if head_dim == 64 and scale > 0 else "mma")
+    # the tcgen05 kernel works on tiles of 256 rows: a step of short portions only is better
+    # served by the warp-level kernel's tiles of 64
+    which = kernel or (PREFILL_ATTENTION if head_dim == 64 and scale > 0
+                       and max(host_rows, default=0) >= 256 else "mma")
     if which == "tcgen05":
         if head_dim != 64:
             raise BackendError(f"{op}: the tcgen05 kernel serves head size 64, not {head_dim}")
