@@ -1,6 +1,7 @@
 """Each part alone against its plain function, a model whose order runs a layer twice and
-shares a cache, and a toy mixer with state of its own that is registered, built and stepped
-without touching the package's files."""
+shares a cache, and toy parts defined here — a mixer with state of its own, a feed-forward
+with routing, a rotary position encoding — that are registered, built and stepped without
+touching the package's files."""
 
 from __future__ import annotations
 
@@ -15,6 +16,8 @@ from ayaka_b200.engine.runner import StepEntry
 from ayaka_b200.models.decoder import DecoderModel
 from ayaka_b200.parts import (BuildContext, LayerSpec, ModelSpec, PartSpec, Run, StateNeed,
                               build_part, register_part)
+from ayaka_b200.parts.embedding import PositionEncoding
+from ayaka_b200.parts.feed_forward import FeedForward
 from ayaka_b200.parts.mixer import Mixer
 
 pytestmark = pytest.mark.gpu
@@ -36,8 +39,11 @@ def fill(part, seed=0, scale=0.3):
 
 def model_spec(layers, order, width, vocab=61, positions=96, position_kind="learned"):
     norm = PartSpec("layer_norm", width=width, eps=1e-5, bias=True)
-    position = PartSpec("learned", max_positions=positions, width=width) \
-        if position_kind == "learned" else PartSpec("none")
+    if isinstance(position_kind, PartSpec):
+        position = position_kind
+    else:
+        position = PartSpec("learned", max_positions=positions, width=width) \
+            if position_kind == "learned" else PartSpec("none")
     return ModelSpec(hidden_size=width, vocab_size=vocab, max_positions=positions,
                      embedding=PartSpec("token", vocab_size=vocab, width=width),
                      position=position, layers=tuple(layers), order=tuple(order),
@@ -259,6 +265,108 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped():
     got_c = core.step([StepEntry("c", third, list(range(9)))]).cpu()
     assert core.manager.row("c") == 0
     torch.testing.assert_close(got_c, expected_for(third), rtol=1e-4, atol=1e-4)
+
+
+# ---- a toy feed-forward with routing and a toy rotary position encoding, defined here ----------
+@register_part("feed_forward", "toy_routed")
+class ToyRoutedFeedForward(FeedForward):
+    """Top-1 routing over ``experts`` square matrices: residual += gate * (W_e h), with e the
+    arg-max of the router's fp32 logits and gate its softmax probability."""
+
+    def __init__(self, spec, ctx):
+        super().__init__(ctx)
+        self.width = int(spec.width)
+        self.experts = int(spec.experts)
+        self.router = self.add_param("router.weight", (self.experts, self.width), "matrix")
+        self.weight = self.add_param("experts.weight", (self.experts * self.width, self.width),
+                                     "matrix")
+
+    def forward(self, hidden, residual, step):
+        n = step.num_rows
+        h = hidden[:n].float()
+        prob = torch.softmax(h @ self.router.float().t(), dim=-1)
+        gate, expert = prob.max(dim=-1)
+        w = self.weight.float().view(self.experts, self.width, self.width)[expert]
+        residual[:n] += gate[:, None] * torch.einsum("noi,ni->no", w, h)
+
+
+@register_part("position", "toy_rotary")
+class ToyRotary(PositionEncoding):
+    """Rotates consecutive pairs of every head of the queries and keys by position * base **
+    (-pair / pairs), in place, before the keys are cached."""
+
+    def __init__(self, spec, ctx):
+        super().__init__(ctx)
+        self.head_dim = int(spec.head_dim)
+        self.base = float(spec.base)
+
+    def _angles(self, positions):
+        pairs = self.head_dim // 2
+        freq = self.base ** (-torch.arange(pairs, device=positions.device,
+                                           dtype=torch.float32) / pairs)
+        return positions.float()[:, None] * freq[None, :]
+
+    def on_query_key(self, q, k, step):
+        n = step.num_rows
+        angle = self._angles(step.positions[:n])
+        cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
+        for t in (q, k):
+            x = t[:n].float().reshape(n, -1, self.head_dim // 2, 2)
+            a, b = x[..., 0], x[..., 1]
+            turned = torch.stack([a * cos - b * sin, a * sin + b * cos], dim=-1)
+            t[:n] = turned.reshape(n, -1).to(t.dtype)
+
+
+def plain_rotate(x, head_dim, base):
+    """[steps, heads, head_dim] rotated as ToyRotary does, position = row index."""
+    pairs = head_dim // 2
+    freq = base ** (-torch.arange(pairs, dtype=torch.float32) / pairs)
+    angle = torch.arange(x.shape[0], dtype=torch.float32)[:, None] * freq[None, :]
+    cos, sin = angle.cos()[:, None, :], angle.sin()[:, None, :]
+    y = x.reshape(x.shape[0], x.shape[1], pairs, 2)
+    return torch.stack([y[..., 0] * cos - y[..., 1] * sin, y[..., 0] * sin + y[..., 1] * cos],
+                       dim=-1).reshape(x.shape)
+
+
+def plain_rotary_routed_layer(x, w, prefix, heads, head_dim, scale, base, experts):
+    steps, width = x.shape
+    h = plain.layer_norm(x, w[prefix + "mixer_norm.weight"], w[prefix + "mixer_norm.bias"], 1e-5)
+    qkv = h @ w[prefix + "mixer.qkv.weight"].t() + w[prefix + "mixer.qkv.bias"]
+    q, k, v = (t.reshape(steps, heads, head_dim) for t in qkv.split(heads * head_dim, dim=-1))
+    q, k = plain_rotate(q, head_dim, base), plain_rotate(k, head_dim, base)
+    attended = plain.causal_attention(q, k, v, scale, 0).reshape(steps, heads * head_dim)
+    x = x + attended @ w[prefix + "mixer.out.weight"].t() + w[prefix + "mixer.out.bias"]
+    h = plain.layer_norm(x, w[prefix + "feed_forward_norm.weight"],
+                         w[prefix + "feed_forward_norm.bias"], 1e-5)
+    prob = torch.softmax(h @ w[prefix + "feed_forward.router.weight"].t(), dim=-1)
+    gate, expert = prob.max(dim=-1)
+    mats = w[prefix + "feed_forward.experts.weight"].view(experts, width, width)
+    return x + gate[:, None] * torch.einsum("noi,ni->no", mats[expert], h)
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_rotary_encoding():
+    """Another feed-forward kind and another position encoding, registered from this file:
+    a layer with rotary attention and top-1 routing, then an ordinary layer (which the same
+    encoding also rotates), whole, in portions and token by token over the paged cache."""
+    width, heads, head_dim, experts, base = 48, 3, 16, 4, 50.0
+    norm = PartSpec("layer_norm", width=width, eps=1e-5, bias=True)
+    routed = LayerSpec("pre_norm",
+                       PartSpec("attention", width=width, num_heads=heads, num_kv_heads=heads,
+                                head_dim=head_dim, scale=0.3, window=0, bias=True),
+                       PartSpec("toy_routed", width=width, experts=experts), norm, norm)
+    spec = model_spec([routed], [Run(0)], width,
+                      position_kind=PartSpec("toy_rotary", head_dim=head_dim, base=base))
+    core, w = core_of(spec, running=2)
+    tokens = [(5 * i + 1) % 61 for i in range(41)]
+
+    x = w["embedding.weight"][tokens]
+    x = plain_rotary_routed_layer(x, w, "layers.0.", heads, head_dim, 0.3, base, experts)
+    expected = plain_head(x, w)
+    whole = feed(core, "whole", tokens, [41])
+    torch.testing.assert_close(whole, expected, rtol=1e-4, atol=1e-4)
+    core.release("whole")
+    cut = feed(core, "cut", tokens, [7, 2, 19] + [1] * 13)  # portions, then token by token
+    torch.testing.assert_close(cut, expected, rtol=1e-4, atol=1e-4)
 
 
 def test_an_unknown_part_kind_says_what_is_registered():
