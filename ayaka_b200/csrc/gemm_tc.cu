@@ -1150,9 +1150,9 @@ inline int pick_splits(int tile_n, int N, int M) {
   if (tile_n == -100) return 1;
   if (tile_n != -1) return -tile_n;
   const int tiles = (N + TC_BM - 1) / TC_BM;
-  // measured on GPT-2 XL's shapes: with more than 32 rows the cluster reduction of a
-  // [64, 128] tile costs more than it buys unless the tiles are very few
-  if (M > 32) return tiles >= 32 ? 1 : 8;
+  // measured on GPT-2 XL's shapes: with more than 16 rows the cluster reduction of a
+  // [32, 128] or [64, 128] tile costs more than it buys unless the tiles are very few
+  if (M > 16) return tiles >= 32 ? 1 : 8;
   int splits = 1;
   while (splits < 8 && tiles * splits * 2 <= 296) splits <<= 1;
   return splits;
