@@ -4,7 +4,7 @@
 //
 // A CTA owns 256 consecutive query rows of one request and one head, as two groups of 128,
 // and walks that request's keys 128 at a time from position 0 (or the window's first block)
-// up to the tile's last row. Seventeen warps, by role:
+// up to the tile's last row. Fifteen warps, by role:
 //   warps 0-3, 4-7  softmax of group 0 and of group 1: a thread owns one query row. For every
 //              block it reads its row of S = Q K^T from tensor memory (twice: once for the row
 //              maximum, once to exponentiate), keeps the running reference maximum and sum in
@@ -16,7 +16,7 @@
 //              (8 x 128x64x16 per group; V is read as stored, [key][64], as an MN-major
 //              operand), in the order PV0(j), S0(j+1), PV1(j), S1(j+1): while one group's
 //              softmax runs, the tensor core works for the other;
-//   warps 9-12, 13-16  gather Q and the K blocks, and the V blocks, from the pages with
+//   warps 9-11, 12-14  gather Q and the K blocks, and the V blocks, from the pages with
 //              16-byte cp.async copies into a ring of three shared-memory stages (both groups
 //              share them).
 // mbarriers connect the roles; every wait is bounded (tc_common.cuh) and a wait that runs out
@@ -41,7 +41,7 @@ constexpr int FA_BN = 128;                  // keys per block
 constexpr int FA_HD = 64;                   // head size: one 128-byte swizzle row
 constexpr int FA_TILE = FA_GM * FA_HD * 2;  // bytes of a [128][64] bf16 tile
 constexpr int FA_STAGES = 3;                // K and V blocks in flight
-constexpr int FA_PRODUCERS = 4;              // warps that gather K, and as many for V
+constexpr int FA_PRODUCERS = 3;              // warps that gather K, and as many for V
 constexpr int FA_THREADS = (9 + 2 * FA_PRODUCERS) * 32;
 constexpr float FA_LAZY = 8.f;              // how far a block's maximum may exceed the reference
 
@@ -135,7 +135,7 @@ __device__ __forceinline__ void fa_gather_block(uint8_t* tile,
   }
 }
 
-__global__ void __launch_bounds__(FA_THREADS)
+__global__ void __launch_bounds__(FA_THREADS, 1)
 attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
                             const __nv_bfloat16* __restrict__ k_pages,
                             const __nv_bfloat16* __restrict__ v_pages,
@@ -393,11 +393,9 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
           const float offset = ref == -INFINITY ? 0.f : ref;
           float part0 = 0.f, part1 = 0.f, part2 = 0.f, part3 = 0.f;
           float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
-#pragma unroll 1
-          for (int c = 0; c < FA_BN / 32; ++c) {
-            uint32_t raw[32];
-            tmem_ld_32x32(s_acc + (uint32_t)(c * 32), raw);
-            tmem_ld_wait();
+          // 32 columns of the row at a time; the load of the next 32 is in flight while these
+          // are exponentiated (two register buffers, the loop unrolled by two)
+          auto process = [&](const uint32_t* raw, int c) {
             float p[32];
             if (all_seen) {
 #pragma unroll
@@ -454,6 +452,17 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
               packed.w = *reinterpret_cast<uint32_t*>(&h3);
               *reinterpret_cast<uint4*>(dst + ((((c & 1) * 4 + h) ^ swz) << 4)) = packed;
             }
+          };
+          uint32_t raw_a[32], raw_b[32];
+          tmem_ld_32x32(s_acc, raw_a);
+#pragma unroll 1
+          for (int c = 0; c < FA_BN / 32; c += 2) {
+            tmem_ld_wait();
+            tmem_ld_32x32(s_acc + (uint32_t)((c + 1) * 32), raw_b);
+            process(raw_a, c);
+            tmem_ld_wait();
+            if (c + 2 < FA_BN / 32) tmem_ld_32x32(s_acc + (uint32_t)((c + 2) * 32), raw_a);
+            process(raw_b, c + 1);
           }
           part = (part0 + part1) + (part2 + part3);
           const float top = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)) * scale2;
