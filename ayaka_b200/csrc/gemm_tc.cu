@@ -180,7 +180,12 @@ __device__ __forceinline__ void epilogue_warp(uint32_t acc, int lane, int m_warp
       v[q * 4 + 2] = __uint_as_float(raw[q * 4 + 2]) + b.z;
       v[q * 4 + 3] = __uint_as_float(raw[q * 4 + 3]) + b.w;
     }
-    if (mode != OUT_RESIDUAL_F32) {
+    if (mode == OUT_BF16) {
+      // (the tanh of a GELU through the special-function unit: with tanhf the epilogue of a
+      // 128 x 256 tile took longer than its main loop)
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = activate_to_bf16(v[j], act);
+    } else if (mode == OUT_F32) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = activate(v[j], act);
     }
@@ -744,7 +749,7 @@ __device__ __forceinline__ void store_output(void* out, int ldo, int m, int n, f
                                              int act) {
   if (mode == OUT_BF16) {
     reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] =
-        __float2bfloat16_rn(activate(v, act));
+        __float2bfloat16_rn(activate_to_bf16(v, act));
   } else if (mode == OUT_F32) {
     reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = activate(v, act);
   } else {
