@@ -411,6 +411,97 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
   if (threadIdx.x == 0) out[r] = token >= 0 ? token : 0;
 }
 
+// ---------------------------------------------------------------------------------------
+// What a request may ask to have done to its logits before the token is chosen, in the
+// reference's fixed order (python/ayaka/ops/sampling.py:10-20, 166-200): a mask (only the
+// allowed ids survive; banned ids — the stop ids while fewer than min_tokens tokens exist —
+// go to -inf), then additive biases, then the three penalties from the request's own tokens:
+//   x = x > 0 ? x / r : x * r   for tokens that occur in prompt or output   (repetition)
+//   x = x - f * (occurrences in the output)                                   (frequency)
+//   x = x - s                   for tokens that occur in the output           (presence)
+// -inf stays -inf throughout. One CTA per adjusted row. A row is described by 16 int32 words
+// in `desc` followed (anywhere in `desc`) by its lists; offsets are word indices into `desc`:
+//   0 row of `logits`          1 history offset   2 history length   3 prompt length
+//   4 bias offset              5 bias count (ids, then as many float values)
+//   6 allowed offset           7 allowed count (-1: every id is allowed)
+//   8 banned offset            9 banned count
+//   10 repetition  11 frequency  12 presence (float bits)      13-15 unused
+// The history is the request's prompt followed by its output. Counting is quadratic in the
+// history (each thread looks for earlier copies of its tokens): a few microseconds at a
+// thousand tokens, and nothing is kept between steps.
+constexpr int ADJ_THREADS = 256;
+constexpr int ADJ_WORDS = 16;
+
+__global__ void __launch_bounds__(ADJ_THREADS)
+logits_adjust_kernel(float* __restrict__ logits, int ld, int vocab,
+                     const int* __restrict__ desc, unsigned* __restrict__ mask_scratch,
+                     int mask_words) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int* d = desc + blockIdx.x * ADJ_WORDS;
+  float* x = logits + (size_t)d[0] * ld;
+  const int* hist = desc + d[1];
+  const int hist_len = d[2], prompt_len = d[3];
+  const int* bias_ids = desc + d[4];
+  const int bias_n = d[5];
+  const float* bias_values = reinterpret_cast<const float*>(bias_ids + bias_n);
+  const int* allowed = desc + d[6];
+  const int allowed_n = d[7];
+  const int* banned = desc + d[8];
+  const int banned_n = d[9];
+  const float rep = __int_as_float(d[10]), freq = __int_as_float(d[11]),
+              pres = __int_as_float(d[12]);
+  const int tid = threadIdx.x;
+
+  if (allowed_n >= 0) {
+    unsigned* mask = mask_scratch + (size_t)blockIdx.x * mask_words;
+    for (int w = tid; w < mask_words; w += ADJ_THREADS) mask[w] = 0u;
+    __syncthreads();
+    for (int i = tid; i < allowed_n; i += ADJ_THREADS) {
+      const int id = allowed[i];
+      if (id >= 0 && id < vocab) atomicOr(&mask[id >> 5], 1u << (id & 31));
+    }
+    __syncthreads();
+    for (int v = tid; v < vocab; v += ADJ_THREADS) {
+      if (((mask[v >> 5] >> (v & 31)) & 1u) == 0u) x[v] = -INFINITY;
+    }
+    __syncthreads();
+  }
+  for (int i = tid; i < banned_n; i += ADJ_THREADS) {
+    const int id = banned[i];
+    if (id >= 0 && id < vocab) x[id] = -INFINITY;
+  }
+  __syncthreads();
+  for (int i = tid; i < bias_n; i += ADJ_THREADS) {  // an id appears once
+    const int id = bias_ids[i];
+    if (id >= 0 && id < vocab) x[id] += bias_values[i];
+  }
+  __syncthreads();
+  if (rep != 1.f || freq != 0.f || pres != 0.f) {
+    for (int i = tid; i < hist_len; i += ADJ_THREADS) {
+      const int token = hist[i];
+      if (token < 0 || token >= vocab) continue;
+      bool first = true;
+      for (int j = 0; j < i; ++j) {
+        if (hist[j] == token) {
+          first = false;
+          break;
+        }
+      }
+      if (!first) continue;  // the thread of the first copy speaks for the token
+      int in_output = i >= prompt_len ? 1 : 0;
+      for (int j = i + 1; j < hist_len; ++j) {
+        if (hist[j] == token && j >= prompt_len) ++in_output;
+      }
+      float v = x[token];
+      v = v > 0.f ? v / rep : v * rep;
+      v -= freq * (float)in_output;
+      if (in_output > 0) v -= pres;
+      x[token] = v;
+    }
+  }
+}
+
 }  // namespace ayk
 
 AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
@@ -462,4 +553,19 @@ AYK_API int ayk_sample(const float* logits, int ld, int rows, int vocab, const f
   return ayk::launch_kernel(ayk::sample_kernel, dim3(rows), dim3(ayk::SMP_THREADS), bytes,
                             (cudaStream_t)stream, 1, logits, ld, vocab, temperature, top_k,
                             top_p, min_p, seeds, positions, out);
+}
+
+// Adjust `num_rows` rows of fp32 logits in place as `desc` says (see logits_adjust_kernel).
+// `mask_scratch` holds num_rows * ceil(vocab / 32) words (needed only by rows with an allowed
+// list; may be null when no row has one).
+AYK_API int ayk_logits_adjust(float* logits, int ld, int vocab, const int* desc, int num_rows,
+                              unsigned* mask_scratch, void* stream) {
+  using namespace ayk;
+  if (num_rows == 0) return AYK_OK;
+  if (num_rows < 0 || vocab < 1 || ld < vocab || logits == nullptr || desc == nullptr) {
+    return AYK_BAD_ARGUMENT;
+  }
+  return launch_kernel(logits_adjust_kernel, dim3(num_rows), dim3(ADJ_THREADS), 0,
+                       (cudaStream_t)stream, 1, logits, ld, vocab, desc, mask_scratch,
+                       (vocab + 31) / 32);
 }

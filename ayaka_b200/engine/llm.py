@@ -147,6 +147,14 @@ class LLM:
             if type(token) is not int or not 0 <= token < vocab:
                 raise InvalidRequestError(
                     f"prompt token {token!r} is not an integer in [0, {vocab})")
+        if sampling is not None:
+            named = [token for token, _ in sampling.logit_bias or ()]
+            named += list(sampling.allowed_token_ids or ())
+            for token in named:
+                if token >= vocab:
+                    raise InvalidRequestError(
+                        f"token id {token} in logit_bias or allowed_token_ids is outside the "
+                        f"vocabulary of {vocab}")
         self._counter += 1
         request_id = f"req-{self._counter}"
         request = self.scheduler.add_request(request_id, ids, sampling)
@@ -166,12 +174,15 @@ class LLM:
         if plan is None:
             return
         try:
-            if self.graphs is not None and self.graphs.can_run(plan):
-                picked = self.graphs.run(plan, self._sample_rows(plan))
+            rows = self._sample_rows(plan)
+            # (a captured step chooses its tokens inside the graph: rows that want their
+            # logits adjusted first take the ordinary step)
+            if self.graphs is not None and self.graphs.can_run(plan) and \
+                    not any(row.adjusts for row in rows):
+                picked = self.graphs.run(plan, rows)
             else:
                 logits = self.core.runner.run(plan.entries)
-                picked = self.sampler.sample(logits, self._sample_rows(plan)) \
-                    if plan.sampled else []
+                picked = self.sampler.sample(logits, rows) if plan.sampled else []
         except BackendError as error:
             # a refused step ends its requests; the engine goes on (reference:
             # python/ayaka/execution/runner.py:227-231)
@@ -182,10 +193,15 @@ class LLM:
 
     def _sample_rows(self, plan: object) -> list[SampleRow]:
         rows = []
+        eos = self.scheduler.eos_token_id
         for request_id in plan.sampled:  # type: ignore[attr-defined]
             request = self.scheduler.running[request_id]
-            rows.append(SampleRow(request.params, request.seed,
-                                  len(request.prompt) + len(request.output)))
+            params = request.params
+            history = request.prompt + tuple(request.output) if params.penalises else ()
+            rows.append(SampleRow(params, request.seed,
+                                  len(request.prompt) + len(request.output), history,
+                                  len(request.prompt),
+                                  params.banned_at(len(request.output), eos)))
         return rows
 
     def _dispatch(self, events: list[RequestEvent]) -> None:

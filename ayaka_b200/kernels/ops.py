@@ -28,6 +28,7 @@ __all__ = [
     "layer_norm",
     "linear",
     "linear_normed",
+    "logits_adjust",
     "sample",
     "set_pdl",
 ]
@@ -485,4 +486,36 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor 
         _ptr(logits), c_int(logits.stride(0)), c_int(n), c_int(logits.shape[1]),
         _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(seeds), _ptr(positions),
         _ptr(out), _stream())
+    check(status, op)
+
+
+#: words of a row's header in the descriptor of :func:`logits_adjust`
+ADJUST_WORDS = 16
+
+
+def logits_adjust(logits: torch.Tensor, desc: torch.Tensor, num_rows: int,
+                  mask_scratch: torch.Tensor | None = None) -> None:
+    """Adjust rows of fp32 ``logits`` in place before a token is chosen: allowed and banned
+    ids, additive biases, repetition / frequency / presence penalties, in that order.
+
+    ``desc`` (int32, on the device) holds ``num_rows`` headers of ``ADJUST_WORDS`` words
+    followed by the lists they point to (offsets are word indices into ``desc``): row of
+    ``logits``; history offset, history length, prompt length (the history is the request's
+    prompt followed by its output); bias offset and count (ids, then as many float32 values);
+    allowed offset and count (-1: no restriction); banned offset and count; repetition,
+    frequency and presence as float32 bits. ``mask_scratch`` (int32, ``num_rows *
+    ceil(vocab / 32)`` words) is needed when a row has an allowed list.
+    """
+    op = "logits_adjust"
+    _need(op, "logits", logits, torch.float32, 2)
+    _need(op, "desc", desc, torch.int32, 1)
+    if num_rows < 0 or desc.shape[0] < num_rows * ADJUST_WORDS:
+        raise BackendError(f"{op}: the descriptor does not hold {num_rows} rows")
+    if mask_scratch is not None:
+        _need(op, "mask_scratch", mask_scratch, torch.int32, 1)
+        if mask_scratch.shape[0] < num_rows * ((logits.shape[1] + 31) // 32):
+            raise BackendError(f"{op}: mask_scratch is too small")
+    status = library("sampling").ayk_logits_adjust(
+        _ptr(logits), c_int(logits.stride(0)), c_int(logits.shape[1]), _ptr(desc),
+        c_int(num_rows), _ptr(mask_scratch), _stream())
     check(status, op)

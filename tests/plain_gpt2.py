@@ -221,6 +221,37 @@ def sample_token(row: torch.Tensor, temperature: float, u: float, top_k: int = 0
     return int(order[min(first, last)])
 
 
+def adjust_logits(row: torch.Tensor, prompt: list[int], output: list[int], *,
+                  repetition: float = 1.0, frequency: float = 0.0, presence: float = 0.0,
+                  bias: dict[int, float] | None = None, allowed: set[int] | None = None,
+                  banned: set[int] | None = None) -> torch.Tensor:
+    """What a request may have done to its logits before the draw, in the reference's order
+    (python/ayaka/ops/sampling.py:10-20): the mask of allowed and banned ids
+    (python/ayaka/sampling/logits.py:176-214), the additive bias (python/ayaka/ops/backends/
+    torch/sampling.py:203-213), then the penalties (python/ayaka/ops/sampling.py:176-200):
+    x / r or x * r where the token occurs in prompt or output, minus f per occurrence in the
+    output, minus s where it occurs in the output."""
+    x = row.clone()
+    vocab = x.shape[0]
+    if allowed is not None:
+        keep = torch.zeros(vocab, dtype=torch.bool)
+        keep[sorted(allowed)] = True
+        x[~keep] = -math.inf
+    for token in banned or ():
+        x[token] = -math.inf
+    for token, value in (bias or {}).items():
+        x[token] = x[token] + value
+    seen = torch.zeros(vocab, dtype=torch.bool)
+    seen[list(prompt) + list(output)] = True
+    count = torch.zeros(vocab, dtype=x.dtype)
+    for token in output:
+        count[token] += 1
+    x = torch.where(seen, torch.where(x > 0, x / repetition, x * repetition), x)
+    x = x - frequency * count
+    x = x - presence * (count > 0).to(x.dtype)
+    return x
+
+
 def greedy_generate(state: dict, config: dict, prompt: list[int], steps: int) -> list[int]:
     """Greedy continuation by rerunning the whole sequence each step, no cache
     (tests/_support/tiny_model.py:225-238 does the same in the reference)."""

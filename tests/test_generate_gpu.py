@@ -251,3 +251,108 @@ def test_sample_kernel_frequencies_follow_the_distribution():
     expected = [plain.sample_token(probabilities.log(), 1.0, plain.draw_uniform(12345, p))
                 for p in range(200)]
     assert out[:200].tolist() == expected
+
+
+# ---- masks, biases and penalties before the draw ---------------------------------------------
+def test_logits_adjust_kernel_against_the_plain_function():
+    """Allowed and banned ids, biases and the three penalties in the fixed order, on rows
+    chosen out of a larger buffer; rows that are not named stay bit for bit."""
+    import numpy as np
+
+    from ayaka_b200.kernels import ops
+
+    vocab, rows = 1000, 6
+    g = torch.Generator().manual_seed(7)
+    logits = (torch.randn(rows, vocab, generator=g) * 3).cuda()
+    before = logits.clone()
+    cases = {
+        4: dict(prompt=[3, 3, 999, 17], output=[17, 5, 5, 5], repetition=1.3, frequency=0.4,
+                presence=0.7),
+        1: dict(prompt=[1], output=[], allowed={0, 2, 500, 999}, bias={2: 4.5, 500: -100.0},
+                banned={999}),
+        2: dict(prompt=list(range(0, 700)), output=list(range(600, 900)) + [650] * 5,
+                repetition=0.8, frequency=-0.25, presence=-1.0, bias={650: 1.0}, banned={3}),
+    }
+    header = np.zeros((len(cases), ops.ADJUST_WORDS), dtype=np.int32)
+    lists, cursor = [], len(cases) * ops.ADJUST_WORDS
+
+    def place(values):
+        nonlocal cursor
+        offset = cursor
+        lists.append(np.asarray(values, dtype=np.int32))
+        cursor += len(values)
+        return offset
+
+    for slot, (row, case) in enumerate(cases.items()):
+        history = case["prompt"] + case["output"]
+        bias = sorted(case.get("bias", {}).items())
+        header[slot, 0] = row
+        header[slot, 1], header[slot, 2], header[slot, 3] = place(history), len(history), \
+            len(case["prompt"])
+        header[slot, 4], header[slot, 5] = place([t for t, _ in bias]), len(bias)
+        place(np.asarray([v for _, v in bias], dtype=np.float32).view(np.int32))
+        allowed = case.get("allowed")
+        header[slot, 6], header[slot, 7] = (0, -1) if allowed is None else \
+            (place(sorted(allowed)), len(allowed))
+        header[slot, 8], header[slot, 9] = place(sorted(case.get("banned", ()))), \
+            len(case.get("banned", ()))
+        header.view(np.float32)[slot, 10:13] = (case.get("repetition", 1.0),
+                                                case.get("frequency", 0.0),
+                                                case.get("presence", 0.0))
+    desc = torch.from_numpy(np.concatenate([header.reshape(-1)] + lists)).cuda()
+    mask = torch.zeros(len(cases) * ((vocab + 31) // 32), dtype=torch.int32, device="cuda")
+    ops.logits_adjust(logits, desc, len(cases), mask)
+    for row in range(rows):
+        if row not in cases:
+            assert torch.equal(logits[row], before[row])
+            continue
+        case = cases[row]
+        want = plain.adjust_logits(
+            before[row].cpu(), case["prompt"], case["output"],
+            repetition=case.get("repetition", 1.0), frequency=case.get("frequency", 0.0),
+            presence=case.get("presence", 0.0), bias=case.get("bias"),
+            allowed=case.get("allowed"), banned=case.get("banned"))
+        torch.testing.assert_close(logits[row].cpu(), want, rtol=1e-6, atol=1e-6)
+
+
+def test_generation_with_penalties_bias_allowed_ids_and_min_tokens(tmp_path):
+    """Greedy generation whose every token is the plain implementation's argmax after the
+    same adjustments: the penalties change with every token, the end-of-sequence token cannot
+    appear before min_tokens, and a request without adjustments in the same batch is not
+    touched (it still runs from the captured graph when alone)."""
+    from ayaka_b200 import SamplingParams
+
+    config = dict(TINY_A, eos_token_id=7)
+    folder, state = es.make_model(tmp_path / "loud", config, 0, INIT_LOUD, "float32")
+    wide = plain.cast_state(state, torch.float64)
+    prompts = [random_tokens(256, n, 900 + n) for n in (6, 19, 11)]
+    allowed = frozenset(range(0, 256, 3)) | {7}
+    params = [
+        SamplingParams(temperature=0.0, max_tokens=14, repetition_penalty=1.7,
+                       frequency_penalty=0.9, presence_penalty=0.6, ignore_eos=True),
+        SamplingParams(temperature=0.0, max_tokens=12, allowed_token_ids=allowed,
+                       logit_bias={7: 100.0, 9: 6.0}, min_tokens=5),
+        SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True),
+    ]
+    with _llm(folder, "float32", cuda_graph=True) as llm:
+        outputs = llm.generate([tuple(p) for p in prompts], params)
+        llm.core.manager.check_integrity()
+    for prompt, output, one in zip(prompts, outputs, params):
+        got = list(output.outputs[0].token_ids)
+        produced: list[int] = []
+        for token in got:
+            row = plain.logits(wide, config, torch.tensor(prompt + produced))[-1]
+            banned = set(one.banned_at(len(produced), 7))
+            row = plain.adjust_logits(
+                row, prompt, produced, repetition=one.repetition_penalty,
+                frequency=one.frequency_penalty, presence=one.presence_penalty,
+                bias=dict(one.logit_bias or ()), banned=banned,
+                allowed=None if one.allowed_token_ids is None else set(one.allowed_token_ids))
+            assert float(row[token]) >= float(row.max()) - 1e-4 * float(row[row > -1e30].abs().max())
+            produced.append(token)
+    # the biased end-of-sequence token wins as soon as min_tokens allows it, and ends the request
+    second = list(outputs[1].outputs[0].token_ids)
+    assert second[5] == 7 and len(second) == 6 and 7 not in second[:5]
+    assert all(token in allowed for token in second)
+    assert outputs[1].outputs[0].finish_reason.value == "stop"
+    assert len(outputs[0].outputs[0].token_ids) == 14

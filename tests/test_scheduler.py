@@ -267,3 +267,31 @@ def test_random_workloads_keep_every_promise(seed):
             assert len(got) >= 1
     assert manager.live_requests() == []
     assert manager.num_free_pages() == manager.pools[0].num_usable
+
+
+def test_sampling_params_for_logit_adjustments():
+    """Penalties, logit bias and allowed ids are validated once, and the parameters say when
+    the logits of the next token need adjusting (python/ayaka/core/params.py:56-90, 205-215;
+    python/ayaka/sampling/logits.py:105-128)."""
+    from ayaka_b200.errors import InvalidRequestError
+
+    plain = SamplingParams()
+    assert not plain.penalises and not plain.adjusts_logits(0, 7)
+    full = SamplingParams(repetition_penalty=1.2, frequency_penalty=-2.0, presence_penalty=2.0,
+                          logit_bias={9: 1.5, 3: -100.0}, allowed_token_ids={4, 9})
+    assert full.logit_bias == ((3, -100.0), (9, 1.5)) and full.allowed_token_ids == {4, 9}
+    assert full.penalises and full.adjusts_logits(99, None)
+    assert SamplingParams(logit_bias=[(5, 0.5)]).logit_bias == ((5, 0.5),)
+    assert SamplingParams(logit_bias={}).logit_bias is None
+    # the stop ids (and the end-of-sequence id unless ignored) are held back until min_tokens
+    held = SamplingParams(min_tokens=3, stop_token_ids={11})
+    assert held.banned_at(2, 7) == {7, 11} and held.banned_at(3, 7) == frozenset()
+    assert held.adjusts_logits(0, None) and not held.adjusts_logits(3, 7)
+    assert SamplingParams(min_tokens=3, ignore_eos=True).banned_at(0, 7) == frozenset()
+    for bad in (dict(repetition_penalty=0.0), dict(frequency_penalty=2.5),
+                dict(presence_penalty=-2.5), dict(logit_bias={3: 101.0}),
+                dict(logit_bias=[(3, 1.0), (3, 2.0)]), dict(logit_bias={-1: 1.0}),
+                dict(logit_bias="x"), dict(allowed_token_ids=set()),
+                dict(allowed_token_ids={-2}), dict(repetition_penalty=float("nan"))):
+        with pytest.raises(InvalidRequestError):
+            SamplingParams(**bad)
