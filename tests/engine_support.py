@@ -16,10 +16,11 @@ PAGE = 16
 
 
 def log_error(name: str, value: float) -> None:
-    """Append a measured error to ``gpurun_out/errors.log`` when that folder exists."""
-    folder = Path(__file__).resolve().parent.parent / "gpurun_out"
-    if folder.is_dir():
-        with open(folder / "errors.log", "a", encoding="utf-8") as handle:
+    """Append a measured error to the file the environment variable ``AYK_ERROR_LOG`` names
+    (nothing is written when it is not set)."""
+    target = os.environ.get("AYK_ERROR_LOG")
+    if target:
+        with open(target, "a", encoding="utf-8") as handle:
             handle.write(f"{name}\t{value:.3e}\n")
 
 
