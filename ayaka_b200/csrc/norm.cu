@@ -47,10 +47,10 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float
 }
 
 // The same with the row held in registers: one pass over global memory (all loads in flight
-// at once), mean and variance from the registers. For rows of at most 256 * 4 * VEC floats
+// at once), mean and variance from the registers. For rows of at most THREADS * 4 * VEC floats
 // whose addresses allow 16-byte loads.
-template <typename TOut, int VEC>
-__global__ void __launch_bounds__(256)
+template <typename TOut, int VEC, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 layer_norm_held_kernel(const float* __restrict__ x, int ld_x, const int* __restrict__ rows,
                        const float* __restrict__ gamma, const float* __restrict__ beta,
                        float eps, TOut* __restrict__ out, int ld_out, int width,
@@ -64,7 +64,7 @@ layer_norm_held_kernel(const float* __restrict__ x, int ld_x, const int* __restr
   float4 g[VEC], b[VEC];
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
-    const int c = (i * 256 + threadIdx.x) * 4;
+    const int c = (i * THREADS + threadIdx.x) * 4;
     g[i] = b[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c < width) {
       g[i] = __ldg(reinterpret_cast<const float4*>(gamma + c));
@@ -77,7 +77,7 @@ layer_norm_held_kernel(const float* __restrict__ x, int ld_x, const int* __restr
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
-    const int c = (i * 256 + threadIdx.x) * 4;
+    const int c = (i * THREADS + threadIdx.x) * 4;
     held[i] = c < width ? *reinterpret_cast<const float4*>(src + c)
                         : make_float4(0.f, 0.f, 0.f, 0.f);
     s += (held[i].x + held[i].y) + (held[i].z + held[i].w);
@@ -86,7 +86,7 @@ layer_norm_held_kernel(const float* __restrict__ x, int ld_x, const int* __restr
   float q = 0.f;
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
-    if ((i * 256 + threadIdx.x) * 4 < width) {
+    if ((i * THREADS + threadIdx.x) * 4 < width) {
       const float a = held[i].x - mean, bb = held[i].y - mean;
       const float c = held[i].z - mean, d = held[i].w - mean;
       q += (a * a + bb * bb) + (c * c + d * d);
@@ -96,7 +96,7 @@ layer_norm_held_kernel(const float* __restrict__ x, int ld_x, const int* __restr
   TOut* dst = out + (size_t)r * ld_out;
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
-    const int c = (i * 256 + threadIdx.x) * 4;
+    const int c = (i * THREADS + threadIdx.x) * 4;
     if (c < width) {
       const float v0 = (held[i].x - mean) * inv * g[i].x + b[i].x;
       const float v1 = (held[i].y - mean) * inv * g[i].y + b[i].y;
@@ -123,13 +123,17 @@ int layer_norm(const float* x, int ld_x, const int* rows, const float* gamma, co
   // whole groups of four outputs can be stored at once when the rows start on such groups
   const int wide_out = (ld_out % 4 == 0 && ((uintptr_t)out % (4 * sizeof(TOut))) == 0) ? 1 : 0;
   if (vector_ok && width <= 8192 && width >= 256) {
-#define AYK_LN_HELD(VEC)                                                                       \
-  return launch_kernel(layer_norm_held_kernel<TOut, VEC>, dim3(n), dim3(256), 0, stream, 1, x,  \
-                       ld_x, rows, gamma, beta, eps, (TOut*)out, ld_out, width, wide_out)
-    if (width <= 1024) AYK_LN_HELD(1);
-    if (width <= 2048) AYK_LN_HELD(2);
-    if (width <= 4096) AYK_LN_HELD(4);
-    AYK_LN_HELD(8);
+#define AYK_LN_HELD(VEC, THREADS)                                                              \
+  return launch_kernel(layer_norm_held_kernel<TOut, VEC, THREADS>, dim3(n), dim3(THREADS), 0,  \
+                       stream, 1, x, ld_x, rows, gamma, beta, eps, (TOut*)out, ld_out, width,  \
+                       wide_out)
+    // with many rows, CTAs of 128 threads (more of them resident per SM) hide the one memory
+    // round trip of a row better; with few rows the wider CTA has the shorter chain
+    if (n >= 512 && width <= 2048) AYK_LN_HELD(4, 128);
+    if (width <= 1024) AYK_LN_HELD(1, 256);
+    if (width <= 2048) AYK_LN_HELD(2, 256);
+    if (width <= 4096) AYK_LN_HELD(4, 256);
+    AYK_LN_HELD(8, 256);
 #undef AYK_LN_HELD
   }
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
