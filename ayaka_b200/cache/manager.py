@@ -75,6 +75,7 @@ class _Held:
     row: int
     committed: int = 0
     reserved: int = 0  # tokens beyond `committed` that pages exist for
+    pages_hi: int = 0  # every live table entry below this index holds a page
 
 
 class CacheManager:
@@ -141,6 +142,10 @@ class CacheManager:
     def row(self, request_id: str) -> int:
         return self._held[request_id].row
 
+    def held(self, request_id: str) -> _Held:
+        """Row and token counts of a live request (read only)."""
+        return self._held[request_id]
+
     def committed(self, request_id: str) -> int:
         held = self._held.get(request_id)
         return 0 if held is None else held.committed
@@ -172,6 +177,10 @@ class CacheManager:
         if total > self.max_tokens_per_request:
             return False
         page_hi = -(-total // self.page_size)
+        if not new_request and page_hi <= held.pages_hi:  # the usual decode step: the last page still has room
+            if num_tokens > held.reserved:
+                held.reserved = num_tokens
+            return True
         plan: list[list[int]] = []
         for group, pool in enumerate(self.pools):
             table = self.tables[group][held.row]
@@ -191,6 +200,7 @@ class CacheManager:
                 assert page is not None
                 table[index] = page
         held.reserved = max(held.reserved, num_tokens)
+        held.pages_hi = max(held.pages_hi, page_hi)
         return True
 
     def commit(self, request_id: str, num_tokens: int) -> None:
@@ -254,6 +264,10 @@ class CacheManager:
                 row = table[held.row]
                 first = self._first_live_page(group, held.committed)
                 last = -(-(held.committed + held.reserved) // self.page_size)
+                if held.pages_hi > last:
+                    raise EngineError(
+                        f"request {request_id!r} counts {held.pages_hi} table entries as "
+                        f"filled but its tokens end in page {last}")
                 for index in range(self.max_pages_per_request):
                     page = int(row[index])
                     if page and not first <= index < max(last, first):

@@ -41,6 +41,9 @@ class EngineConfig:
         max_tokens_per_step: token budget of one step.
         max_waiting: longest queue of requests not yet admitted.
         cuda_graph: replay decode-only steps from CUDA graphs.
+        decode_ahead: with ``cuda_graph``, launch the next decode step while the tokens of
+            the current one are still on their way to the host (the device feeds them
+            on); the launch is dropped if the next plan turns out otherwise.
     """
 
     model: str
@@ -54,6 +57,7 @@ class EngineConfig:
     max_tokens_per_step: int = 2048
     max_waiting: int = 1024
     cuda_graph: bool = False
+    decode_ahead: bool = True
 
     def __post_init__(self) -> None:
         if self.dtype not in DTYPE_NAMES:

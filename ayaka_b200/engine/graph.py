@@ -53,10 +53,14 @@ class _Bucket:
         self.o_top_k = take(size)
         self.o_seeds, self.o_sample_positions = take(2 * size), take(2 * size)
         self.words = cursor
-        self.staging = torch.zeros(cursor, dtype=torch.int32).pin_memory()
+        # two launches may be in flight (the step and the one launched ahead of its result):
+        # each has its own pinned metadata, pinned result and event
+        self.staging = [torch.zeros(cursor, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.out_host = [torch.zeros(size, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.events = [torch.cuda.Event() for _ in range(2)]
+        self.turn = 0
         self.meta = torch.zeros(cursor, dtype=torch.int32, device=core.device)
         self.out = torch.zeros(size, dtype=torch.int32, device=core.device)
-        self.out_host = torch.zeros(size, dtype=torch.int32).pin_memory()
         meta = self.meta
 
         def view(offset: int, length: int) -> torch.Tensor:
@@ -96,6 +100,41 @@ class _Bucket:
                    self.out, rows=size)
 
 
+class _Launch:
+    """A step that was launched: where its result arrives and what it ran."""
+
+    __slots__ = ("bucket", "ids", "positions", "rows", "out_host", "event", "count", "pick",
+                 "exact")
+
+    def __init__(self, bucket: _Bucket, ids: tuple[str, ...], positions: list[int],
+                 rows: list[SampleRow], out_host: torch.Tensor, event: torch.cuda.Event) -> None:
+        self.bucket, self.ids, self.positions, self.rows = bucket, ids, positions, rows
+        self.out_host, self.event = out_host, event
+        self.count = len(ids)
+        self.pick = list(range(self.count))  # the launch's row of each entry of its plan
+        self.exact = True  # every row of the launch belongs to an entry, in plan order
+
+    def covers(self, ids: tuple[str, ...], positions: list[int],
+               rows: list[SampleRow]) -> list[int] | None:
+        """The launch's row for each of ``ids`` if it ran every one of them at the given
+        position and with the given sampling; else ``None``. Rows of requests that ended
+        meanwhile are left out: no row's result depends on another row."""
+        if len(rows) != len(ids):
+            return None
+        where = {request_id: index for index, request_id in enumerate(self.ids)}
+        pick = []
+        for request_id, position, row in zip(ids, positions, rows):
+            index = where.get(request_id)
+            if index is None or self.positions[index] != position:
+                return None
+            mine = self.rows[index]
+            if mine.params is not row.params or mine.seed != row.seed or \
+                    mine.position != row.position or row.adjusts:
+                return None
+            pick.append(index)
+        return pick
+
+
 class DecodeGraphs:
     """Captures and replays decode steps; falls back to nothing — a step it cannot run is
     run by the ordinary step function."""
@@ -112,7 +151,10 @@ class DecodeGraphs:
             buckets = tuple(sizes)
         self.sizes = tuple(sorted(set(min(size, limit) for size in buckets)))
         self._buckets: dict[int, _Bucket] = {}
+        self._ahead: _Launch | None = None
         self.replays = 0
+        self.adopted = 0  # launches made ahead that the next plan took over
+        self.dropped = 0  # launches made ahead that the next plan did not fit
 
     def can_run(self, plan: object) -> bool:
         entries = plan.entries  # type: ignore[attr-defined]
@@ -132,19 +174,82 @@ class DecodeGraphs:
 
     def run(self, plan: object, rows: list[SampleRow]) -> list[int]:
         """Run a decode-only plan through its bucket's graph; returns one id per entry."""
+        return self.finish(self.launch(plan, rows))
+
+    def launch(self, plan: object, rows: list[SampleRow]) -> _Launch:
+        """Start a decode-only plan, or take over the launch made ahead for it."""
+        manager = self.core.manager
         entries = plan.entries  # type: ignore[attr-defined]
-        count = len(entries)
+        ids = tuple(entry.request_id for entry in entries)
+        held = [manager.held(request_id) for request_id in ids]
+        positions = [h.committed for h in held]
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None:
+            pick = ahead.covers(ids, positions, rows)
+            if pick is not None:
+                self.adopted += 1
+                ahead.pick = pick
+                ahead.exact = pick == list(range(ahead.count))
+                return ahead
+            # The plan is not the one foreseen. What the launch stored in the cache is what
+            # this step stores again (or lies in pages that were given back); only its
+            # buffers have to be free before they are filled anew.
+            ahead.event.synchronize()
+            self.dropped += 1
+        tokens = [entry.tokens[0] for entry in entries]
+        return self._launch(ids, [h.row for h in held], positions, rows, tokens, None)
+
+    def launch_ahead(self, after: _Launch, rows: list[SampleRow]) -> None:
+        """Start the step that follows ``after`` before ``after``'s tokens have reached the
+        host: same requests in the same rows, one position on, each row fed the id the
+        earlier launch chose, copied on the device. The caller has made room for the next
+        position of every request. :meth:`launch` hands the result to the next plan if that
+        plan turns out as foreseen, and drops it otherwise."""
+        if not after.exact or self._ahead is not None:
+            raise RuntimeError("a launch ahead follows a launch whose rows are all live")
+        manager = self.core.manager
+        table_rows = [manager.held(request_id).row for request_id in after.ids]
+        self._ahead = self._launch(after.ids, table_rows,
+                                   [position + 1 for position in after.positions], rows,
+                                   None, after)
+
+    def drop_ahead(self) -> None:
+        """Forget a launch made ahead (waits for it: its buffers are filled anew later)."""
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None:
+            ahead.event.synchronize()
+            self.dropped += 1
+
+    def finish(self, launch: _Launch) -> list[int]:
+        """Wait for a launch and return the chosen id of each of its plan's entries."""
+        launch.event.synchronize()
+        chosen = launch.out_host.tolist()
+        return [chosen[index] for index in launch.pick]
+
+    def _launch(self, ids: tuple[str, ...], table_rows: list[int], positions: list[int],
+                rows: list[SampleRow], tokens: list[int] | None,
+                after: _Launch | None) -> _Launch:
+        count = len(ids)
         bucket = self.bucket_for(count)
-        self._fill(bucket, entries, rows)
-        bucket.meta.copy_(bucket.staging, non_blocking=True)
+        if after is not None and after.bucket is not bucket:
+            raise RuntimeError("a launch ahead stays in the bucket of the launch before it")
+        slot = bucket.turn
+        bucket.turn ^= 1
+        staging = bucket.staging[slot]
+        self._fill(bucket, staging, table_rows, positions, rows, tokens)
+        bucket.meta.copy_(staging, non_blocking=True)
+        if after is not None:
+            bucket.meta[bucket.o_tokens:bucket.o_tokens + count].copy_(
+                bucket.out[:count], non_blocking=True)
         greedy = all(row.params.greedy for row in rows)
         if greedy not in bucket.graphs:
-            self._capture(bucket, greedy)
+            self._capture(bucket, greedy)  # (runs the step it captures: the same stores)
         bucket.graphs[greedy].replay()
-        bucket.out_host.copy_(bucket.out, non_blocking=True)
-        torch.cuda.current_stream(self.core.device).synchronize()
+        bucket.out_host[slot].copy_(bucket.out, non_blocking=True)
+        event = bucket.events[slot]
+        event.record(torch.cuda.current_stream(self.core.device))
         self.replays += 1
-        return bucket.out_host[:count].tolist()
+        return _Launch(bucket, ids, positions, rows, bucket.out_host[slot], event)
 
     def _capture(self, bucket: _Bucket, greedy: bool) -> None:
         core = self.core
@@ -164,12 +269,13 @@ class DecodeGraphs:
             bucket.kernels = ops.launch_count() - before
             bucket.graphs[greedy] = graph
 
-    def _fill(self, bucket: _Bucket, entries: object, rows: list[SampleRow]) -> None:
+    def _fill(self, bucket: _Bucket, staging: torch.Tensor, table_rows: list[int],
+              positions_of: list[int], rows: list[SampleRow], tokens: list[int] | None) -> None:
         manager = self.core.manager
         size, width, page = bucket.size, bucket.width, manager.page_size
-        host = bucket.staging.numpy()
+        host = staging.numpy()
         floats = host.view(np.float32)
-        count = len(entries)  # type: ignore[arg-type]
+        count = len(table_rows)
         host[bucket.o_request:bucket.o_request + size] = -1
         host[bucket.o_tokens:bucket.o_tokens + size] = 0
         host[bucket.o_positions:bucket.o_positions + size] = 0
@@ -177,24 +283,21 @@ class DecodeGraphs:
         host[bucket.o_want:bucket.o_want + size] = np.arange(size)
         host[bucket.o_row_start:bucket.o_row_start + size + 1] = np.arange(size + 1)
         floats[bucket.o_temperature:bucket.o_temperature + size] = 0.0
-        table_rows = []
-        for b, entry in enumerate(entries):  # type: ignore[arg-type]
-            position = manager.committed(entry.request_id)
-            row = manager.row(entry.request_id)
-            table_rows.append(row)
-            host[bucket.o_tokens + b] = entry.tokens[0]
-            host[bucket.o_positions + b] = position
-            host[bucket.o_request + b] = b
-            host[bucket.o_kv_len + b] = position + 1
-            host[bucket.o_state + b] = row
+        slots = np.asarray(table_rows, dtype=np.int32)
+        positions = np.asarray(positions_of, dtype=np.int32)
+        if tokens is not None:
+            host[bucket.o_tokens:bucket.o_tokens + count] = tokens
+        host[bucket.o_positions:bucket.o_positions + count] = positions
+        host[bucket.o_request:bucket.o_request + count] = np.arange(count)
+        host[bucket.o_kv_len:bucket.o_kv_len + count] = positions + 1
+        host[bucket.o_state:bucket.o_state + count] = slots
+        live = np.arange(count)
         for group, (o_slots, o_table) in enumerate(bucket.o_groups):
-            table = manager.tables[group]
             host[o_slots:o_slots + size] = -1
             block = host[o_table:o_table + size * width].reshape(size, width)
-            for b in range(count):
-                block[b] = table[table_rows[b]]
-                position = int(host[bucket.o_positions + b])
-                host[o_slots + b] = int(block[b, position // page]) * page + position % page
+            block[:count] = manager.tables[group][slots]
+            host[o_slots:o_slots + count] = (block[live, positions // page] * page
+                                             + positions % page)
         longs_seed = host[bucket.o_seeds:bucket.o_seeds + 2 * size].view(np.int64)
         longs_pos = host[bucket.o_sample_positions:
                          bucket.o_sample_positions + 2 * size].view(np.int64)

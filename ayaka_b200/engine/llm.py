@@ -177,10 +177,17 @@ class LLM:
             rows = self._sample_rows(plan)
             # (a captured step chooses its tokens inside the graph: rows that want their
             # logits adjusted first take the ordinary step)
-            if self.graphs is not None and self.graphs.can_run(plan) and \
+            graphs = self.graphs
+            if graphs is not None and graphs.can_run(plan) and \
                     not any(row.adjusts for row in rows):
-                picked = self.graphs.run(plan, rows)
+                launch = graphs.launch(plan, rows)
+                following = self._rows_ahead(plan) if launch.exact else None
+                if following is not None:
+                    graphs.launch_ahead(launch, following)
+                picked = graphs.finish(launch)
             else:
+                if graphs is not None:
+                    graphs.drop_ahead()
                 logits = self.core.runner.run(plan.entries)
                 picked = self.sampler.sample(logits, rows) if plan.sampled else []
         except BackendError as error:
@@ -190,6 +197,36 @@ class LLM:
             self.core.manager.check_integrity()
             return
         self._dispatch(scheduler.update(plan, dict(zip(plan.sampled, picked))))
+
+    def _rows_ahead(self, plan: object) -> list[SampleRow] | None:
+        """The sampling rows of the step after ``plan`` if that step can be foreseen: the
+        same requests, all decoding, none at the end of its length, nothing waiting and
+        room in the cache for one more position each. A stop token cannot be foreseen:
+        the launch made ahead then has a row too many, which is left out."""
+        scheduler, manager = self.scheduler, self.core.manager
+        if not self.config.decode_ahead or scheduler.waiting or \
+                len(plan.entries) != len(scheduler.running):  # type: ignore[attr-defined]
+            return None
+        eos, limit = scheduler.eos_token_id, scheduler.max_positions
+        capacity = manager.max_context_tokens
+        rows = []
+        for request_id in plan.sampled:  # type: ignore[attr-defined]
+            request = scheduler.running[request_id]
+            params = request.params
+            produced = len(request.output) + 1  # once this step's token has arrived
+            if limit - len(request.prompt) - produced <= 0 or request.computed + 2 > capacity:
+                return None
+            if params.max_tokens is not None and params.max_tokens - produced <= 0:
+                return None
+            row = SampleRow(params, request.seed, len(request.prompt) + produced, (),
+                            len(request.prompt), params.banned_at(produced, eos))
+            if row.adjusts:
+                return None
+            rows.append(row)
+        for request_id in plan.sampled:  # type: ignore[attr-defined]
+            if not manager.allocate(request_id, 2):
+                return None
+        return rows
 
     def _sample_rows(self, plan: object) -> list[SampleRow]:
         rows = []
@@ -227,6 +264,8 @@ class LLM:
 
     def close(self) -> None:
         """Shut the engine down; later calls raise ``EngineError``."""
+        if self.graphs is not None and not self._closed:
+            self.graphs.drop_ahead()
         self._closed = True
 
     def __enter__(self) -> LLM:

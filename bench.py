@@ -165,7 +165,9 @@ def decode_run(llm, cfg: dict, batch: int, warmup: int, steps: int, seed: int) -
     for _ in range(warmup):
         llm._advance()
     torch.cuda.synchronize()
-    first_context = PROMPT + 1 + warmup
+    # with the next step launched ahead, the device is one step further than the host
+    ahead = 1 if llm.graphs and llm.config.decode_ahead else 0
+    first_context = PROMPT + 1 + warmup + ahead
     launches_before = ops.launch_count()
     replays_before = llm.graphs.replays if llm.graphs else 0
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

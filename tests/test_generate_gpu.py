@@ -356,3 +356,94 @@ def test_generation_with_penalties_bias_allowed_ids_and_min_tokens(tmp_path):
     assert all(token in allowed for token in second)
     assert outputs[1].outputs[0].finish_reason.value == "stop"
     assert len(outputs[0].outputs[0].token_ids) == 14
+
+
+def _tokens(outputs):
+    return [list(output.outputs[0].token_ids) for output in outputs]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_from_graphs_and_launched_ahead(tmp_path, dtype):
+    """Decode steps replayed from captured graphs, with and without the next step launched
+    before the current tokens reach the host, give the tokens of the step-by-step engine:
+    greedy and seeded rows, requests of different lengths, one that ends on a stop token that
+    nothing foresaw (the launch ahead then has a row too many), and pages so few that a
+    launch ahead sometimes finds no room."""
+    from ayaka_b200 import SamplingParams
+
+    folder, state = es.make_model(tmp_path / "loud", TINY_B, 3, INIT_LOUD, dtype)
+    prompts = [tuple(random_tokens(503, n, 700 + n)) for n in (4, 33, 18, 7)]
+    base = [SamplingParams(temperature=0.0, max_tokens=40),
+            SamplingParams(temperature=0.9, top_k=50, max_tokens=29, seed=5),
+            SamplingParams(temperature=0.0, max_tokens=35),
+            SamplingParams(temperature=1.1, max_tokens=12, seed=6)]
+    with _llm(folder, dtype) as llm:
+        plainly = _tokens(llm.generate(prompts, base))
+    # a stop token for the third request that its plain run produces as its 10th token and
+    # not earlier
+    third = plainly[2]
+    stop = next(token for index, token in enumerate(third) if index >= 9
+                and token not in third[:index])
+    cut = third.index(stop) + 1
+    params = list(base)
+    params[2] = SamplingParams(temperature=0.0, max_tokens=35, stop_token_ids=(stop,))
+    expected = [plainly[0], plainly[1], third[:cut], plainly[3]]
+    slack = 1e-4 if dtype == "float32" else 5e-2
+    for pool in (dict(), dict(block_size=4, num_blocks=22)):
+        with _llm(folder, dtype, **pool) as llm:
+            stepwise = _tokens(llm.generate(prompts, params))
+            short = llm.scheduler.stats.shed + llm.scheduler.stats.stalled_rows
+        if pool:
+            assert short > 0  # the pool is too small for the four of them
+        elif dtype == "float32":
+            assert stepwise == expected
+        for ahead in (False, True):
+            with _llm(folder, dtype, cuda_graph=True, decode_ahead=ahead, **pool) as llm:
+                outputs = llm.generate(prompts, params)
+                llm.core.manager.check_integrity()
+                assert llm.core.manager.live_requests() == []
+                graphs = llm.graphs
+                assert graphs.replays > 0
+                if ahead:
+                    assert graphs.adopted > 10
+                else:
+                    assert graphs.adopted == graphs.dropped == 0
+            if dtype == "float32":
+                assert _tokens(outputs) == stepwise, (pool, ahead)
+            if not pool:
+                assert outputs[2].outputs[0].finish_reason.value == "stop"
+                assert [len(tokens) for tokens in _tokens(outputs)] == [40, 29, cut, 12]
+            for prompt, output, one in zip(prompts, outputs, params):
+                if one.top_k <= 0 and one.top_p >= 1.0:  # (the check knows no truncation)
+                    check_generation(state, TINY_B, prompt, list(output.outputs[0].token_ids),
+                                     one, output.seed, slack)
+
+
+def test_a_launch_ahead_that_the_next_plan_does_not_fit_is_dropped(tmp_path):
+    """A request that arrives between two decode steps changes the next plan: the step
+    launched ahead is dropped, the plan runs as scheduled, and every token is the one the
+    step-by-step engine gives."""
+    from ayaka_b200 import SamplingParams
+
+    folder, _ = es.make_model(tmp_path / "loud", TINY_A, 4, INIT_LOUD, "float32")
+    first, second = tuple(random_tokens(256, 9, 1)), tuple(random_tokens(256, 21, 2))
+    params = SamplingParams(temperature=0.0, max_tokens=24)
+
+    def drive(**options):
+        with _llm(folder, "float32", **options) as llm:
+            a = llm._add(first, params)
+            for _ in range(6):
+                llm._advance()
+            b = llm._add(second, params)
+            while llm.scheduler.has_unfinished:
+                llm._advance()
+            got = {request_id: [token for event in llm._pending[request_id]
+                                for token in event.tokens] for request_id in (a, b)}
+            llm.core.manager.check_integrity()
+            return got[a], got[b], llm.graphs
+
+    plain_a, plain_b, _ = drive()
+    ahead_a, ahead_b, graphs = drive(cuda_graph=True)
+    assert (ahead_a, ahead_b) == (plain_a, plain_b)
+    assert len(ahead_a) == len(ahead_b) == 24
+    assert graphs.dropped >= 1 and graphs.adopted > 10
