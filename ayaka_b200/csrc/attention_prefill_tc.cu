@@ -4,24 +4,34 @@
 //
 // A CTA owns 256 consecutive query rows of one request and one head, as two groups of 128,
 // and walks that request's keys 128 at a time from position 0 (or the window's first block)
-// up to the tile's last row. Fifteen warps, by role:
+// up to the tile's last row. The (group, block) pairs are worked on in one order, group 0
+// before group 1 for every block; pair i has its scores in slot i mod 3 of a ring in tensor
+// memory, its P in the same slot of a ring in shared memory, and the slot's three mbarriers
+// (scores ready, P handed over, product finished). Sixteen warps, by role:
 //   warps 0-3, 4-7  softmax of group 0 and of group 1: a thread owns one query row. For every
-//              block it reads its row of S = Q K^T from tensor memory (twice: once for the row
-//              maximum, once to exponentiate), keeps the running reference maximum and sum in
-//              fp32 registers, writes P = exp2(S * scale * log2e - reference) as bf16 into
-//              shared memory in the layout the tensor core reads (128-byte swizzle), and
-//              rescales its group's output accumulator in tensor memory when the reference
-//              moved;
-//   warp 8     one thread issues the MMAs: S = Q K^T (4 x 128x128x16 per group) and O += P V
-//              (8 x 128x64x16 per group; V is read as stored, [key][64], as an MN-major
-//              operand), in the order PV0(j), S0(j+1), PV1(j), S1(j+1): while one group's
-//              softmax runs, the tensor core works for the other;
-//   warps 9-11, 12-14  gather Q and the K blocks, and the V blocks, from the pages with
+//              block it reads its row of S = Q K^T from tensor memory, keeps the running
+//              reference maximum and sum in fp32 registers, writes P = exp2(S * scale * log2e
+//              - reference) as bf16 into shared memory in the layout the tensor core reads
+//              (128-byte swizzle), and rescales its group's output accumulator in tensor
+//              memory when the reference moved;
+//   warp 8     one thread issues S = Q K^T (4 x 128x128x16 per pair). The scores of pair i + 3
+//              go out as soon as pair i has been handed over (its slot is free): they are the
+//              *other* group's next block, while the group that just finished finds the
+//              scores of its own next block (pair i + 2) waiting, so the round trip through
+//              the issuing threads is off the softmax's path;
+//   warp 9     one thread issues O += P V (8 x 128x64x16 per pair; V is read as stored,
+//              [key][64], as an MN-major operand) when a pair is handed over. Two issuing
+//              threads because one is too slow: with these small MMAs a single thread spent
+//              1.2 microseconds per pair on waits, descriptors, issue and commits;
+//   warps 10-12, 13-15  gather Q and the K blocks, and the V blocks, from the pages with
 //              16-byte cp.async copies into a ring of three shared-memory stages (both groups
 //              share them).
 // mbarriers connect the roles; every wait is bounded (tc_common.cuh) and a wait that runs out
-// sets the status word. One CTA per SM: 192 KB of shared memory, 384 of the 512 tensor-memory
-// columns (S0, S1: 128 each; O0, O1: 64 each).
+// sets the status word. No barrier can complete two phases unseen by a waiter: a slot's next
+// tenant is admitted only after the hand-over of the present one has been seen, and a pair is
+// handed over only after the product that last read its P slot has finished. One CTA per SM:
+// 224 KB of shared memory and all 512 tensor-memory columns (three score tiles of 128; O0,
+// O1: 64 each).
 //
 // The reference maximum moves only when the block's maximum exceeds it by more than 8 (in
 // log2 units), so most blocks do not touch the accumulator; probabilities stay below 2^8 and
@@ -42,16 +52,18 @@ constexpr int FA_HD = 64;                   // head size: one 128-byte swizzle r
 constexpr int FA_TILE = FA_GM * FA_HD * 2;  // bytes of a [128][64] bf16 tile
 constexpr int FA_STAGES = 3;                // K and V blocks in flight
 constexpr int FA_PRODUCERS = 3;              // warps that gather K, and as many for V
-constexpr int FA_THREADS = (9 + 2 * FA_PRODUCERS) * 32;
+constexpr int FA_FIRST_PRODUCER = 10;        // warps 0-7 softmax, 8 and 9 issue the MMAs
+constexpr int FA_THREADS = (FA_FIRST_PRODUCER + 2 * FA_PRODUCERS) * 32;
+constexpr int FA_RING = 3;                  // score tiles (tensor memory) and P tiles (shared)
 constexpr float FA_LAZY = 8.f;              // how far a block's maximum may exceed the reference
 
 struct FaSmem {
   static constexpr int Q = 0;                // two groups
   static constexpr int K = Q + 2 * FA_TILE;          // FA_STAGES stages
   static constexpr int V = K + FA_STAGES * FA_TILE;  // FA_STAGES stages
-  static constexpr int P = V + FA_STAGES * FA_TILE;  // per group [128 rows][128 keys] = two tiles
-  static constexpr int BAR = P + 4 * FA_TILE;
-  static constexpr int NUM_BARS = 1 + 4 * FA_STAGES + 8;
+  static constexpr int P = V + FA_STAGES * FA_TILE;  // FA_RING x [128 rows][128 keys] (two tiles)
+  static constexpr int BAR = P + FA_RING * 2 * FA_TILE;
+  static constexpr int NUM_BARS = 1 + 4 * FA_STAGES + 3 * FA_RING;
   static constexpr int DYNAMIC = BAR + NUM_BARS * 8 + 16 + 1024;  // room to align the base
 };
 
@@ -152,15 +164,18 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   uint64_t* k_empty = k_full + FA_STAGES;        // [stage], MMA commits
   uint64_t* v_full = k_empty + FA_STAGES;        // [stage]
   uint64_t* v_empty = v_full + FA_STAGES;        // [stage]
-  uint64_t* s_full = v_empty + FA_STAGES;        // [group] MMA commit: S is in tensor memory
-  uint64_t* s_empty = s_full + 2;   // [group] 4 arrivals: every softmax warp has read S
-  uint64_t* p_full = s_empty + 2;   // [group] 4 arrivals: P is in shared memory, O is rescaled
-  uint64_t* pv_done = p_full + 2;   // [group] MMA commit: O += P V has finished
+  uint64_t* s_full = v_empty + FA_STAGES;  // [ring slot] MMA commit: S is in tensor memory
+  // [ring slot], like s_full: the next use of a slot's barriers belongs to the pair three
+  // further on, whose scores are issued only after this pair's hand-over has been seen, so no
+  // waiter ever has two phases of one barrier to tell apart
+  uint64_t* p_full = s_full + FA_RING;   // 4 arrivals: S is read, P is in shared memory
+  uint64_t* pv_done = p_full + FA_RING;  // MMA commit: O += P V (and all before it) has finished
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + FaSmem::NUM_BARS);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr uint32_t TMEM_COLS = 512;  // S0: 0..127, S1: 128..255, O0: 256..319, O1: 320..383
+  constexpr uint32_t TMEM_COLS = 512;  // S ring: 3 x 128 columns; O0: 384..447, O1: 448..511
+  constexpr uint32_t O_COL = FA_RING * FA_BN;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, FA_PRODUCERS);
@@ -170,9 +185,8 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
       mbar_init(&v_full[s], FA_PRODUCERS);
       mbar_init(&v_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < FA_RING; ++s) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4);
       mbar_init(&p_full[s], 4);
       mbar_init(&pv_done[s], 1);
     }
@@ -238,10 +252,26 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
     uint8_t* q_s = smem + FaSmem::Q;
     uint8_t* p_s = smem + FaSmem::P;
 
-    if (warp >= 9) {
-      // ---- producers: warps 9.. bring Q and the K blocks, the next FA_PRODUCERS the V blocks
-      const bool keys = warp < 9 + FA_PRODUCERS;
-      const int part = (warp - 9) % FA_PRODUCERS;
+    // The (group, block) pairs in the order they are worked on: block by block, group 0
+    // before group 1. Pair number i has its scores in ring slot i % FA_RING of tensor memory
+    // and its P in the same slot of shared memory.
+    auto active = [&](int g, int j) { return j >= blo[g] && j <= bhi[g]; };
+    auto advance = [&](int& g, int& j) {
+      do {
+        if (g == 0) {
+          g = 1;
+        } else {
+          g = 0;
+          ++j;
+        }
+      } while (j <= jhi && !active(g, j));
+    };
+
+    if (warp >= FA_FIRST_PRODUCER) {
+      // ---- producers: the first FA_PRODUCERS warps bring Q and the K blocks, the next the V
+      // blocks
+      const bool keys = warp < FA_FIRST_PRODUCER + FA_PRODUCERS;
+      const int part = (warp - FA_FIRST_PRODUCER) % FA_PRODUCERS;
       uint64_t* full = keys ? k_full : v_full;
       uint64_t* empty = keys ? k_empty : v_empty;
       uint8_t* stages = smem + (keys ? FaSmem::K : FaSmem::V);
@@ -288,64 +318,66 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
       }
       if (!ok && lane == 0) *failed = 1;
     } else if (warp == 8) {
-      // ---- MMA issuer ---------------------------------------------------------------------
+      // ---- issuer of S = Q K^T -------------------------------------------------------------
       if (lane == 0) {
         constexpr uint32_t idesc_s = umma_idesc_bf16(FA_GM, FA_BN);
-        constexpr uint32_t idesc_o = umma_idesc_bf16(FA_GM, FA_HD) | (1u << 16);  // B: MN-major
-        int ns[2] = {0, 0}, npv[2] = {0, 0};  // blocks issued so far, per group
+        int sg = 0, sj = jlo, si = 0;  // the next pair
+        if (!active(0, jlo)) advance(sg, sj);
         bool ok = mbar_wait(q_full, 0);
-        auto active = [&](int g, int j) { return j >= blo[g] && j <= bhi[g]; };
-        // S_g = Q_g K^T for block j (its K stage is known to be full)
-        auto issue_s = [&](int g, int j) {
-          if (ns[g] >= 1 && ok) ok = mbar_wait(&s_empty[g], (uint32_t)(ns[g] - 1) & 1u);
-          if (!ok) return;
+        while (ok && sj <= jhi) {
+          const int jj = sj - jlo, stage = jj % FA_STAGES, slot = si % FA_RING;
+          // the slot's tenant three pairs ago has been read
+          if (si >= FA_RING) {
+            ok = mbar_wait(&p_full[slot], (uint32_t)(si / FA_RING - 1) & 1u);
+          }
+          if (ok) {
+            ok = mbar_wait(&k_full[stage], (uint32_t)(jj / FA_STAGES) & 1u);
+          }
+          if (!ok) break;
           tc_fence_after();
-          const uint8_t* k_tile = smem + FaSmem::K + ((j - jlo) % FA_STAGES) * FA_TILE;
-          const uint8_t* q_tile = q_s + g * FA_TILE;
+          const uint8_t* k_tile = smem + FaSmem::K + stage * FA_TILE;
+          const uint8_t* q_tile = q_s + sg * FA_TILE;
 #pragma unroll
           for (int k = 0; k < FA_HD / 16; ++k) {
-            umma_f16(tmem_base + (uint32_t)(g * FA_BN), umma_desc_k128(q_tile, k * 32),
+            umma_f16(tmem_base + (uint32_t)(slot * FA_BN), umma_desc_k128(q_tile, k * 32),
                      umma_desc_k128(k_tile, k * 32), idesc_s, k != 0);
           }
-          umma_commit(&s_full[g]);
-          ++ns[g];
-        };
-        // O_g += P_g V for block j (its V stage is known to be full)
-        auto issue_pv = [&](int g, int j) {
-          if (ok) ok = mbar_wait(&p_full[g], (uint32_t)npv[g] & 1u);
-          if (!ok) return;
+          umma_commit(&s_full[slot]);
+          if (sg == 1 || !active(1, sj)) umma_commit(&k_empty[stage]);  // the block's last reader
+          ++si;
+          advance(sg, sj);
+        }
+        if (!ok) *failed = 1;
+      }
+      __syncwarp();
+    } else if (warp == 9) {
+      // ---- issuer of O += P V --------------------------------------------------------------
+      if (lane == 0) {
+        constexpr uint32_t idesc_o = umma_idesc_bf16(FA_GM, FA_HD) | (1u << 16);  // B: MN-major
+        int pg = 0, pj = jlo, pi = 0, npv[2] = {0, 0};
+        if (!active(0, jlo)) advance(pg, pj);
+        bool ok = true;
+        while (ok && pj <= jhi) {
+          const int jj = pj - jlo, stage = jj % FA_STAGES, slot = pi % FA_RING;
+          ok = mbar_wait(&v_full[stage], (uint32_t)(jj / FA_STAGES) & 1u);
+          if (ok) {
+            ok = mbar_wait(&p_full[slot], (uint32_t)(pi / FA_RING) & 1u);
+          }
+          if (!ok) break;
           tc_fence_after();
-          const uint8_t* v_tile = smem + FaSmem::V + ((j - jlo) % FA_STAGES) * FA_TILE;
-          const uint8_t* p_tile = p_s + g * 2 * FA_TILE;
+          const uint8_t* v_tile = smem + FaSmem::V + stage * FA_TILE;
+          const uint8_t* p_tile = p_s + slot * 2 * FA_TILE;
 #pragma unroll
           for (int k = 0; k < FA_BN / 16; ++k) {
-            umma_f16(tmem_base + (uint32_t)(2 * FA_BN + g * FA_HD),
+            umma_f16(tmem_base + O_COL + (uint32_t)(pg * FA_HD),
                      umma_desc_k128(p_tile + (k >> 2) * FA_TILE, (k & 3) * 32),
-                     umma_desc_mn128(v_tile + k * 16 * 128), idesc_o, (npv[g] | k) != 0);
+                     umma_desc_mn128(v_tile + k * 16 * 128), idesc_o, (npv[pg] | k) != 0);
           }
-          umma_commit(&pv_done[g]);
-          ++npv[g];
-        };
-        if (ok) ok = mbar_wait(&k_full[0], 0);
-        for (int g = 0; g < 2 && ok; ++g) {
-          if (active(g, jlo)) issue_s(g, jlo);
-        }
-        if (ok) umma_commit(&k_empty[0]);
-        for (int j = jlo; j <= jhi && ok; ++j) {
-          const int jj = j - jlo, stage = jj % FA_STAGES, after = (jj + 1) % FA_STAGES;
-          const bool next = j < jhi;
-          ok = mbar_wait(&v_full[stage], (uint32_t)(jj / FA_STAGES) & 1u);
-          if (!ok) break;
-          if (active(0, j)) issue_pv(0, j);
-          if (ok && next) ok = mbar_wait(&k_full[after], (uint32_t)((jj + 1) / FA_STAGES) & 1u);
-          if (!ok) break;
-          if (next && active(0, j + 1)) issue_s(0, j + 1);
-          if (active(1, j)) issue_pv(1, j);
-          if (!ok) break;
-          umma_commit(&v_empty[stage]);
-          if (next && active(1, j + 1)) issue_s(1, j + 1);
-          if (!ok) break;
-          if (next) umma_commit(&k_empty[after]);
+          umma_commit(&pv_done[slot]);
+          if (pg == 1 || !active(1, pj)) umma_commit(&v_empty[stage]);
+          ++npv[pg];
+          ++pi;
+          advance(pg, pj);
         }
         if (!ok) *failed = 1;
       }
@@ -355,30 +387,46 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
       const int g = warp >> 2;
       const int r = threadIdx.x & (FA_GM - 1);  // the row inside the group
       const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-      const uint32_t s_acc = tmem_base + (uint32_t)(g * FA_BN) + lane_base;
-      const uint32_t o_acc = tmem_base + (uint32_t)(2 * FA_BN + g * FA_HD) + lane_base;
+      const uint32_t o_acc = tmem_base + O_COL + (uint32_t)(g * FA_HD) + lane_base;
       const int g_pos0 = pos0 + g * FA_GM;
       const int pos = g_pos0 + r;
       const int after = window > 0 ? pos - window : -2147483647 - 1;  // keys > after are seen
       const float scale2 = scale * 1.4426950408889634f;  // scores in units of log2
       float ref = -INFINITY, sum = 0.f;
-      uint8_t* p_row = p_s + g * 2 * FA_TILE + r * 128;
       const int swz = r & 7;
       const int my_blocks = bhi[g] - blo[g] + 1;
+      const int other = g ^ 1;
+      const int other_blocks = bhi[other] >= blo[other] ? bhi[other] - blo[other] + 1 : 0;
       bool ok = true;
+      // The number of this group's block n in the order of work (see the MMA issuer): its own
+      // blocks so far plus the other group's blocks that come before it.
+      auto pair_of = [&](int n) {
+        int before = blo[g] + n - blo[other] + (other < g ? 1 : 0);
+        before = before < 0 ? 0 : (before > other_blocks ? other_blocks : before);
+        return n + before;
+      };
+      // Wait until the product O += P V of a pair of this group has finished (and with it
+      // every product issued before). The slot's barrier was last used three pairs earlier,
+      // by a product that finished before this pair's scores were committed.
+      auto wait_pv = [&](int pair) {
+        if (lane == 0) ok = mbar_wait(&pv_done[pair % FA_RING], (uint32_t)(pair / FA_RING) & 1u);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        tc_fence_after();
+      };
       for (int n = 0; n < my_blocks; ++n) {
         const int key0 = (blo[g] + n) * FA_BN;
-        if (lane == 0) ok = mbar_wait(&s_full[g], (uint32_t)n & 1u);
+        const int pair = pair_of(n), slot = pair % FA_RING;
+        const uint32_t s_acc = tmem_base + (uint32_t)(slot * FA_BN) + lane_base;
+        uint8_t* p_row = p_s + slot * 2 * FA_TILE + r * 128;
+        if (lane == 0) ok = mbar_wait(&s_full[slot], (uint32_t)(pair / FA_RING) & 1u);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
         tc_fence_after();
-        // P's shared memory and the accumulator are free once the product before has finished
-        // (it was issued a whole softmax ago: this wait is almost always over already)
-        if (n > 0) {
-          if (lane == 0) ok = mbar_wait(&pv_done[g], (uint32_t)(n - 1) & 1u);
-          ok = __shfl_sync(0xffffffffu, ok, 0);
+        // the slot's P was last read by the product of three pairs ago, handed over more than
+        // a block ago
+        if (pair >= FA_RING) {
+          wait_pv(pair - FA_RING);
           if (!ok) break;
-          tc_fence_after();
         }
         // A block wholly before the group's first row (and no window) has nothing to mask.
         // The masked variant selects without branching: per element it is two integer
@@ -474,6 +522,10 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
             ref = top;
           }
           if (n > 0) {
+            // the accumulator is whole once this group's product before has finished
+            // (issued a whole softmax ago: over long since)
+            wait_pv(pair_of(n - 1));  // (issued a whole softmax ago: over long since)
+            if (!ok) break;
 #pragma unroll 1
             for (int c = 0; c < FA_HD / 32; ++c) {
               uint32_t raw[32];
@@ -487,19 +539,17 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
           }
           sum *= alpha;
         }
+        if (!ok) break;
         sum += part;
-        // S has been read for the last time: the next block's scores may overwrite it
+        // S has been read for the last time and P is written (generic-proxy writes that the
+        // tensor core reads): one arrival says both
         tc_fence_before();
+        fence_proxy_async_shared();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&s_empty[g]);
-        fence_proxy_async_shared();  // P: generic-proxy writes, read by the tensor core
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full[g]);
+        if (lane == 0) mbar_arrive(&p_full[slot]);
       }
-      if (ok) {
-        if (lane == 0) ok = mbar_wait(&pv_done[g], (uint32_t)(my_blocks - 1) & 1u);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-      }
+      // (no pair three further on exists: the other group ends at most a block later)
+      if (ok) wait_pv(pair_of(my_blocks - 1));
       if (ok) {
         tc_fence_after();
         const float inv = 1.f / sum;

@@ -12,6 +12,9 @@
 #ifndef AYK_WAIT_NS
 #define AYK_WAIT_NS 2000000000ull  // 2 s; a legitimate wait is microseconds
 #endif
+#ifndef AYK_SUSPEND_NS
+#define AYK_SUSPEND_NS 4000  // longest park of one mbarrier.try_wait, in nanoseconds
+#endif
 
 namespace ayk {
 
@@ -44,7 +47,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // the thread for up to `suspend_ns` while the phase is pending and wakes it when the phase
 // completes, so a waiting warp does not take issue slots from the warps that work.
 __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity,
-                                         uint32_t suspend_ns = 4000) {
+                                         uint32_t suspend_ns = AYK_SUSPEND_NS) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
