@@ -23,9 +23,12 @@
 //              [key][64], as an MN-major operand) when a pair is handed over. Two issuing
 //              threads because one is too slow: with these small MMAs a single thread spent
 //              1.2 microseconds per pair on waits, descriptors, issue and commits;
-//   warps 10-12, 13-15  gather Q and the K blocks, and the V blocks, from the pages with
-//              16-byte cp.async copies into a ring of three shared-memory stages (both groups
-//              share them).
+//   warps 10-15  gather Q with 16-byte cp.async copies; then warp 10 brings the K blocks and
+//              warp 13 the V blocks into rings of three shared-memory stages (both groups
+//              share them) by TMA, one box per page (a head's slots of a page are contiguous
+//              rows of 128 bytes; page sizes 8, 16, 32, ... only). With other page sizes warps
+//              10-12 and 13-15 gather the blocks with cp.async instead. Measured at 8,192
+//              tokens: 435 against 513 microseconds for the kernel.
 // mbarriers connect the roles; every wait is bounded (tc_common.cuh) and a wait that runs out
 // sets the status word. No barrier can complete two phases unseen by a waiter: a slot's next
 // tenant is admitted only after the hand-over of the present one has been seen, and a pair is
@@ -39,6 +42,10 @@
 // row's blocks are aligned to absolute key positions, so its result does not depend on how
 // the prompt was cut or on the rows that share its tile.
 #include <cuda.h>
+
+#include <cstring>
+#include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -63,7 +70,7 @@ struct FaSmem {
   static constexpr int V = K + FA_STAGES * FA_TILE;  // FA_STAGES stages
   static constexpr int P = V + FA_STAGES * FA_TILE;  // FA_RING x [128 rows][128 keys] (two tiles)
   static constexpr int BAR = P + FA_RING * 2 * FA_TILE;
-  static constexpr int NUM_BARS = 1 + 4 * FA_STAGES + 3 * FA_RING;
+  static constexpr int NUM_BARS = 2 + 4 * FA_STAGES + 3 * FA_RING;
   static constexpr int DYNAMIC = BAR + NUM_BARS * 8 + 16 + 1024;  // room to align the base
 };
 
@@ -148,7 +155,9 @@ __device__ __forceinline__ void fa_gather_block(uint8_t* tile,
 }
 
 __global__ void __launch_bounds__(FA_THREADS, 1)
-attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, int box_rows,
+                            const __nv_bfloat16* __restrict__ q, int ld_q,
                             const __nv_bfloat16* __restrict__ k_pages,
                             const __nv_bfloat16* __restrict__ v_pages,
                             const int* __restrict__ block_table, int table_stride,
@@ -159,7 +168,7 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   extern __shared__ uint8_t fa_raw[];
   uint8_t* smem = fa_raw + ((1024 - (smem_u32(fa_raw) & 1023)) & 1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FaSmem::BAR);
-  uint64_t* q_full = bars;        // one arrival per K producer warp
+  uint64_t* q_full = bars;        // one arrival per producer warp
   uint64_t* k_full = bars + 1;                   // [stage], one arrival per producer warp
   uint64_t* k_empty = k_full + FA_STAGES;        // [stage], MMA commits
   uint64_t* v_full = k_empty + FA_STAGES;        // [stage]
@@ -170,6 +179,7 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   // waiter ever has two phases of one barrier to tell apart
   uint64_t* p_full = s_full + FA_RING;   // 4 arrivals: S is read, P is in shared memory
   uint64_t* pv_done = p_full + FA_RING;  // MMA commit: O += P V (and all before it) has finished
+  uint64_t* v_land = pv_done + FA_RING;  // TMA: a V block that needs rows zeroed lands here first
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + FaSmem::NUM_BARS);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -178,11 +188,14 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   constexpr uint32_t O_COL = FA_RING * FA_BN;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, FA_PRODUCERS);
+    // a block is published by its gathering warps, or (TMA) by one arrival with the bytes
+    const uint32_t publishers = box_rows > 0 ? 1 : FA_PRODUCERS;
+    mbar_init(q_full, 2 * FA_PRODUCERS);
+    mbar_init(v_land, 1);
     for (int s = 0; s < FA_STAGES; ++s) {
-      mbar_init(&k_full[s], FA_PRODUCERS);
+      mbar_init(&k_full[s], publishers);
       mbar_init(&k_empty[s], 1);
-      mbar_init(&v_full[s], FA_PRODUCERS);
+      mbar_init(&v_full[s], publishers);
       mbar_init(&v_empty[s], 1);
     }
     for (int s = 0; s < FA_RING; ++s) {
@@ -268,53 +281,120 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
     };
 
     if (warp >= FA_FIRST_PRODUCER) {
-      // ---- producers: the first FA_PRODUCERS warps bring Q and the K blocks, the next the V
-      // blocks
+      // ---- producers: all of them bring Q; then the first FA_PRODUCERS warps bring the K
+      // blocks and the others the V blocks
       const bool keys = warp < FA_FIRST_PRODUCER + FA_PRODUCERS;
       const int part = (warp - FA_FIRST_PRODUCER) % FA_PRODUCERS;
       uint64_t* full = keys ? k_full : v_full;
       uint64_t* empty = keys ? k_empty : v_empty;
       uint8_t* stages = smem + (keys ? FaSmem::K : FaSmem::V);
       const __nv_bfloat16* pages = keys ? k_pages : v_pages;
-      if (keys) {
+      {
         const int piece = lane & 7;
-        for (int t = part; t < FA_BM / 4; t += FA_PRODUCERS) {
+        for (int t = warp - FA_FIRST_PRODUCER; t < FA_BM / 4; t += 2 * FA_PRODUCERS) {
           const int r = t * 4 + (lane >> 3);
           const bool valid = r < nrows;
           const __nv_bfloat16* src =
               q + (size_t)(first_row + (valid ? r : 0)) * ld_q + head * FA_HD + piece * 8;
           fa_cp_async16(q_s + r * 128 + ((piece ^ (r & 7)) << 4), src, valid);
         }
-        // (no commit: Q lands with the first block of keys)
+        fa_cp_async_commit();
       }
       bool ok = true;
-      for (int jj = 0; jj < num_blocks && ok; ++jj) {
-        const int stage = jj % FA_STAGES;
-        if (jj >= FA_STAGES) {  // the stage's last tenant must have been read by its MMAs
-          if (lane == 0) ok = mbar_wait(&empty[stage], (uint32_t)(jj / FA_STAGES - 1) & 1u);
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          if (!ok) break;
-        }
-        fa_gather_block(stages + stage * FA_TILE, pages, table, (jlo + jj) * FA_BN, lo_min,
-                        last_key, num_kv_heads, kv_head, page_size, page_shift, lane, part);
-        fa_cp_async_commit();
-        // The block before has landed once only this one is still in flight: publish it.
-        // (With three stages the wait for this block's stage, above, concerns a block the
-        // consumer finished two blocks ago, so it never holds a publication back.)
-        fa_cp_async_wait<1>();
+      if (box_rows > 0) {
+        // ---- TMA: a page's [slots][64] of one head is contiguous, so a block of 128 keys is
+        // 128 / box_rows boxes of box_rows rows (box_rows = min(page size, 128)); lane t
+        // fetches box t. Boxes wholly outside [lo_min, last_key] are left out (their pages
+        // may be gone); rows outside it inside a fetched box hold whatever the page holds.
+        // For K that is harmless (their scores are masked). For V they must be zero (0 * NaN
+        // would poison the sum): such a block lands on a barrier of this warp first, which
+        // zeroes the rows and then publishes the block.
+        fa_cp_async_wait<0>();
         fence_proxy_async_shared();
         __syncwarp();
-        if (lane == 0 && jj > 0) {
-          mbar_arrive(&full[(jj - 1) % FA_STAGES]);
-          if (keys && jj == 1) mbar_arrive(q_full);
+        if (lane == 0) mbar_arrive(q_full);
+        if (part == 0) {
+          const CUtensorMap* map = keys ? &map_k : &map_v;
+          const int boxes = FA_BN / box_rows;
+          const uint32_t box_bytes = (uint32_t)box_rows * 128u;
+          int landed = 0, issued = 0;
+          for (int jj = 0; jj < num_blocks && ok; ++jj) {
+            const int stage = jj % FA_STAGES;
+            if (jj >= FA_STAGES) {  // the stage's last tenant must have been read by its MMAs
+              if (lane == 0) ok = mbar_wait(&empty[stage], (uint32_t)(jj / FA_STAGES - 1) & 1u);
+              ok = __shfl_sync(0xffffffffu, ok, 0);
+              if (!ok) break;
+            }
+            const int key0 = (jlo + jj) * FA_BN;
+            const int key = key0 + lane * box_rows;
+            const bool fetch = lane < boxes && key + box_rows - 1 >= lo_min && key <= last_key;
+            const uint32_t count = (uint32_t)__popc(__ballot_sync(0xffffffffu, fetch));
+            const bool fix = !keys && (key0 < lo_min || key0 + FA_BN - 1 > last_key);
+            uint64_t* lands = fix ? v_land : &full[stage];
+            uint8_t* tile = stages + stage * FA_TILE;
+            if (lane == 0) mbar_expect_tx(lands, count * box_bytes);
+            __syncwarp();
+            if (fetch) {
+              const int index = page_shift >= 0 ? key >> page_shift : key / page_size;
+              const int slot = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+              const int page = table[index];
+              tma_load_2d(tile + (size_t)lane * box_bytes, map, lands, 0,
+                          (page * num_kv_heads + kv_head) * page_size + slot);
+            }
+            if (fix) {
+              if (lane == 0) ok = mbar_wait(v_land, (uint32_t)landed & 1u);
+              ok = __shfl_sync(0xffffffffu, ok, 0);
+              if (!ok) break;
+              ++landed;
+              // rows of keys outside [lo_min, last_key]: eight 16-byte pieces each
+              for (int i = lane; i < FA_BN * 8; i += 32) {
+                const int r = i >> 3;
+                if (key0 + r < lo_min || key0 + r > last_key) {
+                  *reinterpret_cast<uint4*>(tile + r * 128 + ((i & 7) << 4)) =
+                      make_uint4(0u, 0u, 0u, 0u);
+                }
+              }
+              fence_proxy_async_shared();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&full[stage]);
+            }
+            issued = jj + 1;
+          }
+          // nothing of this warp's is in flight when it leaves: the last blocks have landed
+          if (lane == 0) {
+            for (int jj = issued > FA_STAGES ? issued - FA_STAGES : 0; jj < issued; ++jj) {
+              mbar_wait(&full[jj % FA_STAGES], (uint32_t)(jj / FA_STAGES) & 1u);
+            }
+          }
+          __syncwarp();
         }
-      }
-      fa_cp_async_wait<0>();
-      fence_proxy_async_shared();
-      __syncwarp();
-      if (lane == 0 && ok) {
-        mbar_arrive(&full[(num_blocks - 1) % FA_STAGES]);
-        if (keys && num_blocks == 1) mbar_arrive(q_full);
+      } else {
+        for (int jj = 0; jj < num_blocks && ok; ++jj) {
+          const int stage = jj % FA_STAGES;
+          if (jj >= FA_STAGES) {  // the stage's last tenant must have been read by its MMAs
+            if (lane == 0) ok = mbar_wait(&empty[stage], (uint32_t)(jj / FA_STAGES - 1) & 1u);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+          }
+          fa_gather_block(stages + stage * FA_TILE, pages, table, (jlo + jj) * FA_BN, lo_min,
+                          last_key, num_kv_heads, kv_head, page_size, page_shift, lane, part);
+          fa_cp_async_commit();
+          // The block before has landed once only this one is still in flight: publish it.
+          // (With three stages the wait for this block's stage, above, concerns a block the
+          // consumer finished two blocks ago, so it never holds a publication back.) Q was
+          // committed before the first block.
+          fa_cp_async_wait<1>();
+          fence_proxy_async_shared();
+          __syncwarp();
+          if (lane == 0) {
+            if (jj == 0) mbar_arrive(q_full);
+            if (jj > 0) mbar_arrive(&full[(jj - 1) % FA_STAGES]);
+          }
+        }
+        fa_cp_async_wait<0>();
+        fence_proxy_async_shared();
+        __syncwarp();
+        if (lane == 0 && ok) mbar_arrive(&full[(num_blocks - 1) % FA_STAGES]);
       }
       if (!ok && lane == 0) *failed = 1;
     } else if (warp == 8) {
@@ -597,6 +677,33 @@ attention_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   }
 }
 
+// Tensor maps of the caches' page tensors, kept by base address: a serving process has two
+// per layer and encodes each once.
+static int pages_map(const void* base, uint64_t rows, uint32_t box_rows, CUtensorMap* out) {
+  struct Entry {
+    const void* base;
+    uint64_t rows;
+    uint32_t box_rows;
+    CUtensorMap map;
+  };
+  static std::mutex mu;
+  static std::vector<Entry> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  for (const Entry& e : cache) {
+    if (e.base == base && e.rows == rows && e.box_rows == box_rows) {
+      *out = e.map;
+      return AYK_OK;
+    }
+  }
+  Entry e{base, rows, box_rows, {}};
+  const int r = make_map_bf16_k64(&e.map, base, rows, FA_HD, FA_HD, box_rows);
+  if (r != AYK_OK) return r;
+  if (cache.size() >= 1024) cache.clear();
+  cache.push_back(e);
+  *out = e.map;
+  return AYK_OK;
+}
+
 }  // namespace ayk
 
 AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
@@ -614,7 +721,8 @@ AYK_API int ayk_attention_prefill_tc(const void* q, int ld_q, const void* k_page
                                      int table_stride, const int* row_start, const int* kv_len,
                                      void* out, int ld_out, int num_requests, int total_tiles,
                                      int num_heads, int num_kv_heads, int head_dim, int page_size,
-                                     float scale, int window, int* status, void* stream) {
+                                     int num_pages, float scale, int window, int* status,
+                                     void* stream) {
   using namespace ayk;
   if (num_requests == 0 || total_tiles == 0) return AYK_OK;
   if (head_dim != FA_HD || status == nullptr || !(scale > 0.f)) return AYK_BAD_ARGUMENT;
@@ -640,9 +748,23 @@ AYK_API int ayk_attention_prefill_tc(const void* q, int ld_q, const void* k_page
     page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
   }
+  // Pages of a power-of-two size from 8 slots up are fetched by TMA: one head's slots of a
+  // page are contiguous rows of 128 bytes, so the pages tensor is a matrix of
+  // pages * heads * slots rows to the tensor map. Other page sizes are gathered by cp.async.
+  CUtensorMap map_k, map_v;
+  memset(&map_k, 0, sizeof(map_k));
+  memset(&map_v, 0, sizeof(map_v));
+  int box_rows = 0;
+  const unsigned long long cache_rows = (unsigned long long)num_pages * num_kv_heads * page_size;
+  if (page_shift >= 3 && num_pages > 0 && cache_rows < 2147483648ull) {
+    box_rows = page_size < FA_BN ? page_size : FA_BN;
+    int r = pages_map(k_pages, cache_rows, (uint32_t)box_rows, &map_k);
+    if (r == AYK_OK) r = pages_map(v_pages, cache_rows, (uint32_t)box_rows, &map_v);
+    if (r != AYK_OK) return r;
+  }
   return launch_kernel(attention_prefill_tc_kernel, dim3(num_heads, total_tiles),
-                       dim3(FA_THREADS), FaSmem::DYNAMIC, (cudaStream_t)stream, 1,
-                       (const __nv_bfloat16*)q, ld_q, (const __nv_bfloat16*)k_pages,
+                       dim3(FA_THREADS), FaSmem::DYNAMIC, (cudaStream_t)stream, 1, map_k, map_v,
+                       box_rows, (const __nv_bfloat16*)q, ld_q, (const __nv_bfloat16*)k_pages,
                        (const __nv_bfloat16*)v_pages, block_table, table_stride, row_start,
                        kv_len, (__nv_bfloat16*)out, ld_out, num_requests, num_kv_heads,
                        num_heads / num_kv_heads, page_size, scale, window, total_tiles,

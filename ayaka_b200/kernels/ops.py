@@ -333,8 +333,8 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
             _ptr(q), c_int(q.stride(0)), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
             c_int(block_table.stride(0)), _ptr(row_start), _ptr(kv_len), _ptr(out),
             c_int(out.stride(0)), c_int(count), c_int(tiles), c_int(num_heads), c_int(kv_heads),
-            c_int(head_dim), c_int(page_size), c_float(scale), c_int(window),
-            _ptr(_status_word(q.device)), _stream())
+            c_int(head_dim), c_int(page_size), c_int(k_pages.shape[0]), c_float(scale),
+            c_int(window), _ptr(_status_word(q.device)), _stream())
         check(status, op)
         return
     tiles = sum(-(-rows // 64) for rows in host_rows)
