@@ -37,7 +37,8 @@
 // O1: 64 each).
 //
 // The reference maximum moves only when the block's maximum exceeds it by more than 8 (in
-// log2 units), so most blocks do not touch the accumulator; probabilities stay below 2^8 and
+// log2 units; a row's first reference is 0 if its first maximum lies within 8 of that), so
+// most blocks do not touch the accumulator; probabilities stay below 2^8 and
 // the final division by the running sum makes the result the same function of the scores. A
 // row's blocks are aligned to absolute key positions, so its result does not depend on how
 // the prompt was cut or on the rows that share its tile.
@@ -594,7 +595,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
           }
           part = (part0 + part1) + (part2 + part3);
           const float top = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)) * scale2;
-          const bool moves = top > ref + FA_LAZY || (ref == -INFINITY && top > -INFINITY);
+          // A row without a reference ran this pass against 0 (see offset): that stands as
+          // its reference if its maximum is within FA_LAZY of it, and the first block then
+          // needs no second pass either.
+          const bool fresh = ref == -INFINITY;
+          const bool moves = fresh ? (top > FA_LAZY || (top < -FA_LAZY && top > -INFINITY))
+                                   : top > ref + FA_LAZY;
+          if (fresh && !moves && top > -INFINITY) ref = 0.f;
           if (attempt == 1 || !__any_sync(0xffffffffu, moves)) break;
           float alpha = 1.f;
           if (moves) {

@@ -488,6 +488,40 @@ def test_attention_prefill_tensor_cores(case, kernel):
     torch.testing.assert_close(out[:n].float(), plain_out.float(), rtol=2e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize("sign", [-1.0, 1.0, 0.0])
+def test_attention_prefill_first_reference(sign):
+    """The tcgen05 kernel takes 0 as a row's first reference when its first maximum is within
+    2^8 of that and moves it otherwise: scores that are all far below zero (every probability
+    would underflow against 0), all far above (they would overflow), and ordinary ones."""
+    ops = _ops()
+    n, heads, head_dim, page = 300, 2, 64, 16
+    g = torch.Generator().manual_seed(31)
+    unit = torch.nn.functional.normalize(torch.randn(head_dim, generator=g), dim=0)
+    q = 0.3 * torch.randn(n, heads, head_dim, generator=g) + 6.0 * abs(sign) * unit
+    k = 0.3 * torch.randn(n, heads, head_dim, generator=g) + 6.0 * sign * unit
+    v = torch.randn(n, heads, head_dim, generator=g)
+    q, k, v = (t.bfloat16().float() for t in (q, k, v))
+    scale = 1.0  # scores near 36 * sign: e^-36 and e^36 against a reference of 0
+    pages = -(-n // page)
+    k_pages = torch.full((pages + 1, heads, page, head_dim), float("nan"))
+    v_pages = torch.full_like(k_pages, float("nan"))
+    for t in range(n):
+        k_pages[1 + t // page, :, t % page] = k[t]
+        v_pages[1 + t // page, :, t % page] = v[t]
+    table = torch.arange(1, pages + 1, dtype=torch.int32).view(1, pages).to(DEV)
+    out = torch.zeros(n, heads * head_dim, dtype=torch.bfloat16, device=DEV)
+    ops.attention_prefill(
+        q.reshape(n, -1).bfloat16().to(DEV), k_pages.bfloat16().to(DEV),
+        v_pages.bfloat16().to(DEV), table,
+        torch.tensor([0, n], dtype=torch.int32, device=DEV),
+        torch.tensor([n], dtype=torch.int32, device=DEV), out, num_heads=heads, scale=scale,
+        host_rows=[n], kernel="tcgen05")
+    from ayaka_b200.kernels import gemm_tc
+    gemm_tc.check_status(out.device)
+    expected = plain.causal_attention(q.double(), k.double(), v.double(), scale)
+    torch.testing.assert_close(out.double().cpu(), expected.reshape(n, -1), rtol=2e-2, atol=2e-2)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("splits", [1, 2, 5, 8, 16, -2, -7])
 @pytest.mark.parametrize("case", [
