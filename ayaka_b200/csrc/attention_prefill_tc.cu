@@ -107,6 +107,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// max(a, b, c) in one instruction (three-input max, sm_100).
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
@@ -522,26 +528,25 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
           const float offset = ref == -INFINITY ? 0.f : ref;
           float part0 = 0.f, part1 = 0.f, part2 = 0.f, part3 = 0.f;
           float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
-          // 32 columns of the row at a time; the load of the next 32 is in flight while these
-          // are exponentiated (two register buffers, the loop unrolled by two)
+          constexpr int CW = 32;  // columns of the row worked on at a time
           auto process = [&](const uint32_t* raw, int c) {
-            float p[32];
+            float p[CW];
             if (all_seen) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 4) {
-                t0 = fmaxf(t0, __uint_as_float(raw[i]));
-                t1 = fmaxf(t1, __uint_as_float(raw[i + 1]));
-                t2 = fmaxf(t2, __uint_as_float(raw[i + 2]));
-                t3 = fmaxf(t3, __uint_as_float(raw[i + 3]));
+              for (int i = 0; i < CW; i += 8) {
+                t0 = fmax3(t0, __uint_as_float(raw[i]), __uint_as_float(raw[i + 1]));
+                t1 = fmax3(t1, __uint_as_float(raw[i + 2]), __uint_as_float(raw[i + 3]));
+                t2 = fmax3(t2, __uint_as_float(raw[i + 4]), __uint_as_float(raw[i + 5]));
+                t3 = fmax3(t3, __uint_as_float(raw[i + 6]), __uint_as_float(raw[i + 7]));
               }
 #pragma unroll
-              for (int i = 0; i < 32; ++i) {
+              for (int i = 0; i < CW; ++i) {
                 p[i] = fast_exp2(fmaf(__uint_as_float(raw[i]), scale2, -offset));
               }
             } else {
-              const int key = key0 + c * 32;
+              const int key = key0 + c * CW;
 #pragma unroll
-              for (int i = 0; i < 32; i += 4) {
+              for (int i = 0; i < CW; i += 4) {
                 const bool a0 = (key + i <= pos) & (key + i > after);
                 const bool a1 = (key + i + 1 <= pos) & (key + i + 1 > after);
                 const bool a2 = (key + i + 2 <= pos) & (key + i + 2 > after);
@@ -561,15 +566,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
               }
             }
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
+            for (int i = 0; i < CW; i += 4) {
               part0 += p[i];
               part1 += p[i + 1];
               part2 += p[i + 2];
               part3 += p[i + 3];
             }
-            uint8_t* dst = p_row + (c >> 1) * FA_TILE;
+            // 64 keys make a tile of 128-byte rows; eight keys a 16-byte piece of it
+            uint8_t* dst = p_row + ((c * CW) >> 6) * FA_TILE;
+            const int piece0 = ((c * CW) & 63) >> 3;
 #pragma unroll
-            for (int h = 0; h < 4; ++h) {
+            for (int h = 0; h < CW / 8; ++h) {
               uint4 packed;
               __nv_bfloat162 h0 = __floats2bfloat162_rn(p[h * 8], p[h * 8 + 1]);
               __nv_bfloat162 h1 = __floats2bfloat162_rn(p[h * 8 + 2], p[h * 8 + 3]);
@@ -579,19 +586,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
               packed.y = *reinterpret_cast<uint32_t*>(&h1);
               packed.z = *reinterpret_cast<uint32_t*>(&h2);
               packed.w = *reinterpret_cast<uint32_t*>(&h3);
-              *reinterpret_cast<uint4*>(dst + ((((c & 1) * 4 + h) ^ swz) << 4)) = packed;
+              *reinterpret_cast<uint4*>(dst + (((piece0 + h) ^ swz) << 4)) = packed;
             }
           };
-          uint32_t raw_a[32], raw_b[32];
-          tmem_ld_32x32(s_acc, raw_a);
+          // One load and one copy of the arithmetic: loading the next columns while these
+          // are worked on (two register buffers, the arithmetic twice in the loop) measured
+          // slower, 426 against 408 microseconds at 8,192 tokens; the warps wait for
+          // instructions more than for tensor memory, and the other group's warps fill the gap.
+          uint32_t raw[CW];
 #pragma unroll 1
-          for (int c = 0; c < FA_BN / 32; c += 2) {
+          for (int c = 0; c < FA_BN / CW; ++c) {
+            tmem_ld_32x32(s_acc + (uint32_t)(c * CW), raw);
             tmem_ld_wait();
-            tmem_ld_32x32(s_acc + (uint32_t)((c + 1) * 32), raw_b);
-            process(raw_a, c);
-            tmem_ld_wait();
-            if (c + 2 < FA_BN / 32) tmem_ld_32x32(s_acc + (uint32_t)((c + 2) * 32), raw_a);
-            process(raw_b, c + 1);
+            process(raw, c);
           }
           part = (part0 + part1) + (part2 + part3);
           const float top = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)) * scale2;
