@@ -452,6 +452,9 @@ def test_kv_store_then_attend(dtype):
     ((700, 3, 200, 129), (130, 3, 65, 129), 6, 2, 64, 16, 0),
     ((3000,), (1500,), 2, 1, 64, 12, 0),
     ((900, 260), (513, 255), 3, 3, 64, 8, 300),
+    ((600, 300), (600, 257), 2, 1, 64, 256, 0),   # pages larger than a block of keys
+    ((700,), (300,), 2, 2, 64, 32, 150),
+    ((515, 64), (515, 64), 1, 1, 64, 64, 0),
 ])
 def test_attention_prefill_tensor_cores(case, kernel):
     """The bfloat16 flash kernels for prompt portions (tcgen05 for head size 64, tiles of 128
