@@ -35,12 +35,25 @@ TINY_C = {
     "tie_word_embeddings": False,
 }
 
+# a fourth: head size 64 and a context long enough for prompt portions of 256 rows and more,
+# which the tcgen05 attention kernel serves in bfloat16
+TINY_D = {
+    "architectures": ARCH, "n_layer": 2, "n_embd": 128, "n_head": 2, "n_inner": 272,
+    "vocab_size": 300, "n_positions": 640, "layer_norm_epsilon": 2e-5,
+    "activation_function": "gelu_new", "scale_attn_by_inverse_layer_idx": False,
+    "tie_word_embeddings": True,
+}
+
 #: BASELINE-style initialisations (small deviations) and a "loud" one for sensitive tests.
 INIT_A = RandomInit(weight_std=0.02, scale_residual_projections=True, bias_std=0.0, norm_std=0.0)
 INIT_B = RandomInit(weight_std=0.02, scale_residual_projections=False, bias_std=0.02,
                     norm_std=0.02)
 INIT_LOUD = RandomInit(weight_std=0.2, scale_residual_projections=False, bias_std=0.1,
                        norm_std=0.1)
+# for TINY_D: twice as wide, so the same deviation is louder; at 0.2 the bfloat16 rounding of
+# the activations alone (the same with either attention kernel) reaches the tolerance
+INIT_LOUD_WIDE = RandomInit(weight_std=0.14, scale_residual_projections=False, bias_std=0.1,
+                            norm_std=0.1)
 
 CASES = {
     "golden_a": {"config": TINY_A, "seed": 0, "init": INIT_LOUD, "lengths": (5, 17, 32, 9),

@@ -33,7 +33,7 @@ def make_model(folder: Path, config: dict, seed: int, init, dtype: str) -> tuple
 
 
 def build_core(model_dir: Path, dtype: str, *, num_blocks: int, max_running: int = 4,
-               max_tokens_per_step: int = 512, block_size: int = PAGE, poison: bool = True):
+               max_tokens_per_step: int = 1024, block_size: int = PAGE, poison: bool = True):
     from ayaka_b200.config.engine import EngineConfig
     from ayaka_b200.engine.core import EngineCore
 

@@ -10,12 +10,14 @@ import pytest
 import torch
 
 import engine_support as es
-from cases import INIT_LOUD, TINY_A, TINY_B, TINY_C, random_tokens
+from cases import INIT_LOUD, INIT_LOUD_WIDE, TINY_A, TINY_B, TINY_C, TINY_D, random_tokens
 
 pytestmark = pytest.mark.gpu
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-LENGTHS = {"A": (5, 17, 32, 9, 100, 128), "B": (1, 64, 130, 200, 47), "C": (70, 33, 250, 2)}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+LENGTHS = {"A": (5, 17, 32, 9, 100, 128), "B": (1, 64, 130, 200, 47), "C": (70, 33, 250, 2),
+           "D": (600, 257, 40, 333)}
+INITS = {"A": INIT_LOUD, "B": INIT_LOUD, "C": INIT_LOUD, "D": INIT_LOUD_WIDE}
 DTYPES = ("float32", "bfloat16")
 
 
@@ -32,7 +34,7 @@ def models(tmp_path_factory):
     for name, config in CONFIGS.items():
         for dtype in DTYPES:
             folder = tmp_path_factory.mktemp(f"tiny_{name}_{dtype}")
-            made[name, dtype] = (*es.make_model(folder, config, seed=ord(name), init=INIT_LOUD,
+            made[name, dtype] = (*es.make_model(folder, config, seed=ord(name), init=INITS[name],
                                                 dtype=dtype), config)
     return made
 
@@ -102,6 +104,32 @@ def test_mixed_batches_with_pages_used_again(models, expected, name, dtype):
     total_pages = sum(-(-len(t) // es.PAGE) for t in doubled.values())
     assert total_pages > core.manager.pools[0].num_usable
     assert core.manager.num_free_pages() == core.manager.pools[0].num_usable
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_large_portions_side_by_side(models, expected, dtype):
+    """Head size 64 and portions of 256 rows and more (in bfloat16 the tcgen05 attention
+    kernel): two long prompts cut at 300 and 256 in the same steps beside a short one, then
+    their rests beside single tokens."""
+    folder, _, _ = models["D", dtype]
+    sequences = sequences_of("D")
+    a, b, c, d = (sequences[f"d{i}"] for i in range(4))
+
+    def entry(rid, tokens, at, size):
+        return {"id": rid, "tokens": tokens[at:at + size], "want": list(range(size))}
+
+    steps = [
+        {"entries": [entry("d0", a, 0, 300), entry("d1", b, 0, 256), entry("d2", c, 0, 39)],
+         "end": []},
+        {"entries": [entry("d0", a, 300, 299), entry("d1", b, 256, 1), entry("d2", c, 39, 1),
+                     entry("d3", d, 0, 333)], "end": ["d1", "d2", "d3"]},
+        {"entries": [entry("d0", a, 599, 1)], "end": ["d0"]},
+    ]
+    core = es.build_core(folder, dtype, num_blocks=_pages_for(sequences),
+                         max_tokens_per_step=1024)
+    got = es.replay(core, steps)
+    es.assert_logits_close(got, expected["D", dtype], dtype, "large-portions/D")
+    assert core.manager.live_requests() == []
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
