@@ -447,3 +447,27 @@ def test_a_launch_ahead_that_the_next_plan_does_not_fit_is_dropped(tmp_path):
     assert (ahead_a, ahead_b) == (plain_a, plain_b)
     assert len(ahead_a) == len(ahead_b) == 24
     assert graphs.dropped >= 1 and graphs.adopted > 10
+
+
+def test_cancelling_a_stream_while_a_step_is_launched_ahead(tmp_path):
+    """A stream closed after a few tokens leaves a decode step in flight that was launched
+    ahead for it: its pages go back at once (the stream orders what reuses them after that
+    step), the launch is dropped, and the next request gets the step-by-step engine's tokens."""
+    from ayaka_b200 import SamplingParams
+
+    folder, state = es.make_model(tmp_path / "a", TINY_A, 0, INIT_LOUD, "float32")
+    first, second = random_tokens(256, 13, 21), random_tokens(256, 30, 22)
+    params = SamplingParams(temperature=0.0, max_tokens=20)
+    with _llm(folder, "float32", cuda_graph=True, num_blocks=8) as llm:
+        generator = llm.stream(tuple(first), params)
+        seen = [token for _, piece in zip(range(5), generator)
+                for token in piece.outputs[0].token_ids]
+        assert llm.graphs.adopted >= 2
+        generator.close()
+        assert llm.core.manager.live_requests() == []
+        llm.core.manager.check_integrity()
+        output = llm.generate(tuple(second), params)
+        assert llm.graphs.dropped >= 1
+        llm.core.manager.check_integrity()
+    assert seen == plain.greedy_generate(state, TINY_A, first, 20)[:5]
+    assert list(output.outputs[0].token_ids) == plain.greedy_generate(state, TINY_A, second, 20)
