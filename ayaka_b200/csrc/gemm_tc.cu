@@ -135,12 +135,36 @@ __device__ __forceinline__ void stage_bias(float* bias_s, const float* __restric
   __syncwarp();
 }
 
-template <int BN>
+// The key and value columns of a fused query/key/value projection go into the cache instead
+// of the output: columns from q_width on are keys, then values (kv_width of each), heads of head_dim columns; row m is
+// stored at slot slots[m] (page * page_size + offset; negative: nowhere) of pages laid out
+// [page][kv_head][slot][head_dim]. head_dim and the widths are multiples of 32, so the 32
+// columns a warp converts at a time lie in one head.
+struct KvScatter {
+  const int* slots;
+  __nv_bfloat16* k_pages;
+  __nv_bfloat16* v_pages;
+  int q_width, kv_width, num_kv_heads, head_dim, page_size;
+};
+
+// Where row m goes in the cache: the element offset of its slot in head 0, or -1 for a row
+// that stores nothing. The slots are the step's metadata, not written by the kernel ahead:
+// the epilogue warps fetch this before they wait for the accumulator.
+__device__ __forceinline__ long long kv_row_offset(const KvScatter& kv, int m, int M) {
+  const int slot = m < M ? __ldg(kv.slots + m) : -1;
+  if (slot < 0) return -1;
+  const int page = slot / kv.page_size, within = slot - page * kv.page_size;
+  return ((long long)page * kv.num_kv_heads * kv.page_size + within) * kv.head_dim;
+}
+
+template <int BN, bool SCATTER = false>
 __device__ __forceinline__ void epilogue_warp(uint32_t acc, int lane, int m_warp, int n0, int M,
                                               int N, const float* __restrict__ bias,
                                               const float* bias_s, void* __restrict__ out,
                                               int ldo, int mode, int act, int vec_ok,
-                                              const CUtensorMap* map_out, uint8_t* staging) {
+                                              const CUtensorMap* map_out, uint8_t* staging,
+                                              const KvScatter& kv = KvScatter{},
+                                              long long kv_row = -1) {
   if (!vec_ok) {
     const int m = m_warp + lane;
 #pragma unroll 1
@@ -162,8 +186,22 @@ __device__ __forceinline__ void epilogue_warp(uint32_t acc, int lane, int m_warp
   for (int c = 0; c < BN / 32; ++c) {
     const int n = n0 + c * 32;
     if (n >= N) break;
+    uint8_t* kv_dst = nullptr;  // this chunk's 64 bytes of the row in the cache, if any
+    if (SCATTER && n >= kv.q_width && kv_row >= 0) {
+      const int col = n - kv.q_width;
+      const int value = col >= kv.kv_width ? 1 : 0;
+      const int hcol = col - value * kv.kv_width;
+      const int head = hcol / kv.head_dim;
+      __nv_bfloat16* pages = value ? kv.v_pages : kv.k_pages;
+      kv_dst = reinterpret_cast<uint8_t*>(
+          pages + (size_t)kv_row + (size_t)head * kv.page_size * kv.head_dim +
+          (hcol - head * kv.head_dim));
+    }
+    // key and value columns go to the cache only (q_width is a multiple of 64: a box of 64
+    // columns is all queries or all keys/values)
+    const bool to_cache = SCATTER && n >= kv.q_width;
     // a box is 64 bf16 columns (two passes of this loop) or 32 fp32 columns (one)
-    const bool opens_box = mode != OUT_BF16 || (c & 1) == 0;
+    const bool opens_box = !to_cache && (mode != OUT_BF16 || (c & 1) == 0);
     if (opens_box) {
       if (lane == 0) bulk_wait_read_all();  // the box before has left the staging rows
       __syncwarp();
@@ -202,7 +240,11 @@ __device__ __forceinline__ void epilogue_warp(uint32_t acc, int lane, int m_warp
         packed.y = *reinterpret_cast<uint32_t*>(&h1);
         packed.z = *reinterpret_cast<uint32_t*>(&h2);
         packed.w = *reinterpret_cast<uint32_t*>(&h3);
-        *reinterpret_cast<uint4*>(row + (((piece0 + q) ^ swz) << 4)) = packed;
+        if (to_cache) {
+          if (kv_dst != nullptr) *reinterpret_cast<uint4*>(kv_dst + (q << 4)) = packed;
+        } else {
+          *reinterpret_cast<uint4*>(row + (((piece0 + q) ^ swz) << 4)) = packed;
+        }
       }
     } else {
 #pragma unroll
@@ -211,8 +253,8 @@ __device__ __forceinline__ void epilogue_warp(uint32_t acc, int lane, int m_warp
             make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
       }
     }
-    const bool closes_box = mode != OUT_BF16 || (c & 1) == 1 || c + 1 == BN / 32 ||
-                            n + 32 >= N;
+    const bool closes_box = !to_cache && (mode != OUT_BF16 || (c & 1) == 1 ||
+                                          c + 1 == BN / 32 || n + 32 >= N);
     if (closes_box) {
       fence_proxy_async_shared();
       __syncwarp();
@@ -229,11 +271,12 @@ __device__ __forceinline__ void epilogue_warp(uint32_t acc, int lane, int m_warp
   }
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool SCATTER = false>
 __global__ void __launch_bounds__(128)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias, void* __restrict__ out, int ldo, int M, int N,
-               int K, int act, int mode, int vec_ok, int* __restrict__ status) {
+               const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias,
+               void* __restrict__ out, int ldo, int M, int N, int K, int act, int mode,
+               int vec_ok, int* __restrict__ status, KvScatter kv) {
   using L = TcSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
@@ -320,14 +363,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncwarp();
   float* bias_s = reinterpret_cast<float*>(smem + L::BIAS_OFFSET) + warp * BN;
   stage_bias<BN>(bias_s, bias, n0, N, lane);
+  const long long kv_row = SCATTER ? kv_row_offset(kv, m0 + warp * 32 + lane, M) : -1;
   pdl_wait();
   bool have = mbar_wait(accum, 0);
   if (!have) *failed = 1;
   tc_fence_after();
   if (have && *failed == 0) {
-    epilogue_warp<BN>(tmem_base + ((uint32_t)(warp * 32) << 16), lane, m0 + warp * 32, n0, M, N,
-                      bias, bias_s, out, ldo, mode, act, vec_ok, &map_out,
-                      smem + L::EPI_OFFSET + warp * EPI_WARP_BYTES);
+    epilogue_warp<BN, SCATTER>(tmem_base + ((uint32_t)(warp * 32) << 16), lane, m0 + warp * 32,
+                               n0, M, N, bias, bias_s, out, ldo, mode, act, vec_ok, &map_out,
+                               smem + L::EPI_OFFSET + warp * EPI_WARP_BYTES, kv, kv_row);
     if (lane == 0) bulk_wait_all();  // the stores are done before the CTA says it is
   }
 
@@ -367,14 +411,14 @@ struct PersistentSmem {
   static constexpr int DYNAMIC = TOTAL + 1024;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool SCATTER = false>
 __global__ void __launch_bounds__(192)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                           const __grid_constant__ CUtensorMap map_w,
                           const __grid_constant__ CUtensorMap map_out,
                           const float* __restrict__ bias, void* __restrict__ out, int ldo, int M,
                           int N, int K, int act, int mode, int vec_ok,
-                          int* __restrict__ status) {
+                          int* __restrict__ status, KvScatter kv) {
   using L = PersistentSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
@@ -500,6 +544,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
       tile_origin(t, m0, n0);
       float* bias_s = reinterpret_cast<float*>(smem + L::BIAS_OFFSET) + quarter * BN;
       stage_bias<BN>(bias_s, bias, n0, N, lane);
+      const long long kv_row = SCATTER ? kv_row_offset(kv, m0 + quarter * 32 + lane, M) : -1;
       bool have = true;
       if (lane == 0) have = mbar_wait(&acc_full[buf], (local >> 1) & 1);
       have = __shfl_sync(0xffffffffu, have, 0);
@@ -508,10 +553,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         break;
       }
       tc_fence_after();
-      epilogue_warp<BN>(tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quarter * 32) << 16), lane,
-                        m0 + quarter * 32, n0, M, N, bias, bias_s, out, ldo, mode, act, vec_ok,
-                        &map_out,
-                        smem + L::EPI_OFFSET + quarter * EPI_WARP_BYTES);
+      epilogue_warp<BN, SCATTER>(
+          tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(quarter * 32) << 16), lane,
+          m0 + quarter * 32, n0, M, N, bias, bias_s, out, ldo, mode, act, vec_ok, &map_out,
+          smem + L::EPI_OFFSET + quarter * EPI_WARP_BYTES, kv, kv_row);
       // this warp has read its lanes of the accumulator: hand it back
       tc_fence_before();
       __syncwarp();
@@ -1025,10 +1070,10 @@ static int output_map(void* out, int ldo, int M, int N, int mode, const CUtensor
   return cached_map(out, (uint64_t)M, (uint64_t)N, (uint64_t)ldo, 32, map_out, (int)elem);
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool SCATTER = false>
 int launch_gemm_tc(const void* a, int lda, const void* w, int ldw, const float* bias, void* out,
                    int ldo, int M, int N, int K, int act, int mode, int* status,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, const KvScatter& kv = KvScatter{}) {
   using L = TcSmem<BN, STAGES>;
   CUtensorMap map_a, map_w;
   int r = cached_map(a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BM, &map_a);
@@ -1037,7 +1082,7 @@ int launch_gemm_tc(const void* a, int lda, const void* w, int ldw, const float* 
   if (r != AYK_OK) return r;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, SCATTER>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYNAMIC);
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -1049,14 +1094,17 @@ int launch_gemm_tc(const void* a, int lda, const void* w, int ldw, const float* 
   const long long gy = (M + TC_BM - 1) / TC_BM;
   if (gy > 65535) return AYK_TOO_LARGE;
   dim3 grid((N + BN - 1) / BN, (unsigned)gy);
-  return launch_kernel(gemm_tc_kernel<BN, STAGES>, grid, dim3(128), L::DYNAMIC, stream, 1, map_a,
-                       map_w, map_out, bias, out, ldo, M, N, K, act, mode, vec_ok, status);
+  if (SCATTER && !vec_ok) return AYK_BAD_ALIGNMENT;  // (the caller checks before it asks)
+  return launch_kernel(gemm_tc_kernel<BN, STAGES, SCATTER>, grid, dim3(128), L::DYNAMIC, stream,
+                       1, map_a, map_w, map_out, bias, out, ldo, M, N, K, act, mode, vec_ok,
+                       status, kv);
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool SCATTER = false>
 int launch_gemm_tc_persistent(const void* a, int lda, const void* w, int ldw, const float* bias,
                               void* out, int ldo, int M, int N, int K, int act, int mode,
-                              int* status, cudaStream_t stream) {
+                              int* status, cudaStream_t stream,
+                              const KvScatter& kv = KvScatter{}) {
   using L = PersistentSmem<BN, STAGES>;
   CUtensorMap map_a, map_w;
   int r = cached_map(a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BM, &map_a);
@@ -1066,7 +1114,7 @@ int launch_gemm_tc_persistent(const void* a, int lda, const void* w, int ldw, co
   static bool configured = false;
   static int num_sms = 0;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES, SCATTER>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYNAMIC);
     if (e != cudaSuccess) return (int)e;
     int device = 0;
@@ -1083,9 +1131,10 @@ int launch_gemm_tc_persistent(const void* a, int lda, const void* w, int ldw, co
   const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
   if (tiles > 0x7fffffffLL) return AYK_TOO_LARGE;
   const int grid = tiles < num_sms ? (int)tiles : num_sms;
-  return launch_kernel(gemm_tc_persistent_kernel<BN, STAGES>, dim3(grid), dim3(192), L::DYNAMIC,
-                       stream, 1, map_a, map_w, map_out, bias, out, ldo, M, N, K, act, mode,
-                       vec_ok, status);
+  if (SCATTER && !vec_ok) return AYK_BAD_ALIGNMENT;  // (the caller checks before it asks)
+  return launch_kernel(gemm_tc_persistent_kernel<BN, STAGES, SCATTER>, dim3(grid), dim3(192),
+                       L::DYNAMIC, stream, 1, map_a, map_w, map_out, bias, out, ldo, M, N, K, act,
+                       mode, vec_ok, status, kv);
 }
 
 template <int BN, int STAGES>
@@ -1163,6 +1212,39 @@ inline int pick_splits(int tile_n, int N, int M) {
   return splits;
 }
 
+// The tile code (see ayk_gemm_bf16_tc) for a product with more than 64 rows.
+inline int choose_tile(int M, int N) {
+  // measured at GPT-2 XL's shapes: with more 128 x 256 tiles than SMs the persistent kernel
+  // wins (its epilogues hide under the next tile's main loop); with fewer, one tile per CTA
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device) !=
+            cudaSuccess) {
+      num_sms = 148;
+    }
+  }
+  // tile width 256, 192 or 128: the one with the least (rounds over the SMs) x (time of a
+  // round). Measured at K = 1600: a round of 256-wide tiles takes only 7 % longer than one
+  // of 192-wide tiles (9.8 against 9.2 microseconds), i.e. about (width + 768) units, so
+  // the number of rounds decides and the width breaks ties. One tile per CTA while
+  // everything fits one round, else the persistent kernel.
+  const long long tiles_m = (M + TC_BM - 1) / TC_BM;
+  long long best_cost = -1;
+  int best_bn = 256;
+  for (int bn : {256, 192, 128}) {
+    const long long tiles = tiles_m * ((N + bn - 1) / bn);
+    const long long cost = ((tiles + num_sms - 1) / num_sms) * (bn + 768);
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best_bn = bn;
+    }
+  }
+  const long long tiles = tiles_m * ((N + best_bn - 1) / best_bn);
+  return tiles > num_sms ? 1000 + best_bn : best_bn;
+}
+
 }  // namespace ayk
 
 AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
@@ -1205,37 +1287,7 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
     return launch_gemm_tc_small<64, 6>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
                                        splits, status, s);
   }
-  if (tile_n == 0) {
-    // measured at GPT-2 XL's shapes: with more 128 x 256 tiles than SMs the persistent kernel
-    // wins (its epilogues hide under the next tile's main loop); with fewer, one tile per CTA
-    static int num_sms = 0;
-    if (num_sms == 0) {
-      int device = 0;
-      if (cudaGetDevice(&device) != cudaSuccess ||
-          cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device) !=
-              cudaSuccess) {
-        num_sms = 148;
-      }
-    }
-    // tile width 256, 192 or 128: the one with the least (rounds over the SMs) x (time of a
-    // round). Measured at K = 1600: a round of 256-wide tiles takes only 7 % longer than one
-    // of 192-wide tiles (9.8 against 9.2 microseconds), i.e. about (width + 768) units, so
-    // the number of rounds decides and the width breaks ties. One tile per CTA while
-    // everything fits one round, else the persistent kernel.
-    const long long tiles_m = (M + TC_BM - 1) / TC_BM;
-    long long best_cost = -1;
-    int best_bn = 256;
-    for (int bn : {256, 192, 128}) {
-      const long long tiles = tiles_m * ((N + bn - 1) / bn);
-      const long long cost = ((tiles + num_sms - 1) / num_sms) * (bn + 768);
-      if (best_cost < 0 || cost < best_cost) {
-        best_cost = cost;
-        best_bn = bn;
-      }
-    }
-    const long long tiles = tiles_m * ((N + best_bn - 1) / best_bn);
-    tile_n = tiles > num_sms ? 1000 + best_bn : best_bn;
-  }
+  if (tile_n == 0) tile_n = choose_tile(M, N);
   switch (tile_n) {
     case 192:
       return launch_gemm_tc<192, 5>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
@@ -1264,5 +1316,57 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
       return launch_gemm_tc<256, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
     default:
       return AYK_BAD_ARGUMENT;
+  }
+}
+
+// The fused query/key/value projection of a step of more than 64 rows: bf16 a w^T + bias as
+// above, of which the query columns go to `out` and the key and value columns (from q_width
+// on: kv_width of keys, then of values) of every row m go to the cache at slot slots[m] (see
+// KvScatter; a negative slot stores nothing) and *not* to `out`: the attention kernels for
+// prompt portions read them from the cache. Returns AYK_OK when it ran; 1 when this product
+// cannot carry the store (few rows, a head size that is no multiple of 32, a query width that
+// is no multiple of 64, an output TMA cannot write): nothing ran then and the caller does the
+// product and the store on their own.
+AYK_API int ayk_gemm_bf16_tc_kv(const void* a, int lda, const void* w, int ldw,
+                                const float* bias, void* out, int ldo, int M, int N, int K,
+                                const int* slots, void* k_pages, void* v_pages, int q_width,
+                                int kv_width, int num_kv_heads, int head_dim, int page_size,
+                                int* status, void* stream) {
+  using namespace ayk;
+  if (M < 0 || N < 1 || K < 1 || lda < K || ldw < K || ldo < N || status == nullptr ||
+      slots == nullptr || k_pages == nullptr || v_pages == nullptr || num_kv_heads < 1 ||
+      page_size < 1 || head_dim < 1 || kv_width != num_kv_heads * head_dim ||
+      N != q_width + 2 * kv_width) {
+    return AYK_BAD_ARGUMENT;
+  }
+  if (M <= 64 || head_dim % 32 || q_width % 64 || ((uintptr_t)a % 16) || ((uintptr_t)w % 16) ||
+      (lda % 8) || (ldw % 8) || ((uintptr_t)out % 16) || (ldo % 8) ||
+      ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16)) {
+    return 1;
+  }
+  const KvScatter kv{slots, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, q_width, kv_width,
+                     num_kv_heads, head_dim, page_size};
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (choose_tile(M, N)) {
+    case 128:
+      return launch_gemm_tc<128, 4, true>(a, lda, w, ldw, bias, out, ldo, M, N, K, ACT_NONE,
+                                          OUT_BF16, status, s, kv);
+    case 192:
+      return launch_gemm_tc<192, 5, true>(a, lda, w, ldw, bias, out, ldo, M, N, K, ACT_NONE,
+                                          OUT_BF16, status, s, kv);
+    case 256:
+      return launch_gemm_tc<256, 4, true>(a, lda, w, ldw, bias, out, ldo, M, N, K, ACT_NONE,
+                                          OUT_BF16, status, s, kv);
+    case 1128:
+      return launch_gemm_tc_persistent<128, 6, true>(a, lda, w, ldw, bias, out, ldo, M, N, K,
+                                                     ACT_NONE, OUT_BF16, status, s, kv);
+    case 1192:
+      return launch_gemm_tc_persistent<192, 5, true>(a, lda, w, ldw, bias, out, ldo, M, N, K,
+                                                     ACT_NONE, OUT_BF16, status, s, kv);
+    case 1256:
+      return launch_gemm_tc_persistent<256, 4, true>(a, lda, w, ldw, bias, out, ldo, M, N, K,
+                                                     ACT_NONE, OUT_BF16, status, s, kv);
+    default:
+      return 1;
   }
 }

@@ -9,7 +9,7 @@ import torch
 from ayaka_b200.errors import BackendError
 from ayaka_b200.kernels.lib import check, library
 
-__all__ = ["check_status", "linear_bf16", "status_word"]
+__all__ = ["check_status", "linear_bf16", "linear_bf16_kv", "status_word"]
 
 _status: dict[int, torch.Tensor] = {}
 
@@ -61,3 +61,31 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
                 c_void_p(status_word(a.device).data_ptr()),
                 c_void_p(torch.cuda.current_stream().cuda_stream))
     check(status, "linear (tcgen05)")
+
+
+def linear_bf16_kv(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
+                   out: torch.Tensor, rows: int, slot_mapping: torch.Tensor,
+                   k_pages: torch.Tensor, v_pages: torch.Tensor, q_width: int) -> bool:
+    """The fused query/key/value projection with the key and value columns also stored into
+    the cache pages (``[page, kv_head, slot, head_dim]``) at ``slot_mapping``. Returns False,
+    having run nothing, when the library cannot carry the store with this product."""
+    if not usable(a, weight):
+        return False
+    n, k = weight.shape
+    _, kv_heads, page_size, head_dim = k_pages.shape
+    from ayaka_b200.kernels import ops
+
+    fn = library("gemm_tc").ayk_gemm_bf16_tc_kv
+    status = fn(c_void_p(a.data_ptr()), c_int(a.stride(0)), c_void_p(weight.data_ptr()),
+                c_int(weight.stride(0)), c_void_p(0 if bias is None else bias.data_ptr()),
+                c_void_p(out.data_ptr()), c_int(out.stride(0)), c_int(rows), c_int(n), c_int(k),
+                c_void_p(slot_mapping.data_ptr()), c_void_p(k_pages.data_ptr()),
+                c_void_p(v_pages.data_ptr()), c_int(q_width), c_int(kv_heads * head_dim),
+                c_int(kv_heads), c_int(head_dim), c_int(page_size),
+                c_void_p(status_word(a.device).data_ptr()),
+                c_void_p(torch.cuda.current_stream().cuda_stream))
+    if status == 1:
+        return False
+    ops._launches += 1
+    check(status, "linear with key/value store (tcgen05)")
+    return True

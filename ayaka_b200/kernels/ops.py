@@ -203,6 +203,41 @@ def linear(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out
     check(status, op)
 
 
+def linear_kv(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
+              out: torch.Tensor, slot_mapping: torch.Tensor, k_pages: torch.Tensor,
+              v_pages: torch.Tensor, *, q_width: int, rows: int | None = None) -> bool:
+    """``a @ weight.T + bias`` for a fused query/key/value projection (bfloat16): the query
+    columns go to ``out[:, :q_width]``; the key and value columns (keys, then values) go into
+    the cache pages at ``slot_mapping``, written by the product's own epilogue, and **not**
+    to ``out`` (whose columns from ``q_width`` on keep what they held). Returns False, having
+    done nothing, when that cannot be had (float32, few rows, sizes the kernel does not
+    take): the caller then runs :func:`linear` and :func:`kv_store`."""
+    op = "linear_kv"
+    if a.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or BF16_GEMM != "tcgen05":
+        return False
+    _need(op, "a", a, torch.bfloat16, 2)
+    _need(op, "weight", weight, torch.bfloat16, 2)
+    _need(op, "out", out, torch.bfloat16, 2)
+    _need(op, "slot_mapping", slot_mapping, torch.int32, 1)
+    _need(op, "k_pages", k_pages, torch.bfloat16, 4)
+    _need(op, "v_pages", v_pages, torch.bfloat16, 4)
+    if bias is not None:
+        _need(op, "bias", bias, torch.float32, 1)
+    m = a.shape[0] if rows is None else rows
+    n, k = weight.shape
+    _, kv_heads, _, head_dim = k_pages.shape
+    if a.shape[1] != k or m > a.shape[0] or m > out.shape[0] or out.shape[1] != n or \
+            m > slot_mapping.shape[0] or n != q_width + 2 * kv_heads * head_dim or \
+            v_pages.shape != k_pages.shape or (bias is not None and bias.shape[0] != n):
+        raise BackendError(f"{op}: shapes do not fit")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous():
+        raise BackendError(f"{op}: contiguous pages only")
+    from ayaka_b200.kernels import gemm_tc
+
+    return gemm_tc.linear_bf16_kv(a, weight, bias, out, m, slot_mapping, k_pages, v_pages,
+                                  q_width)
+
+
 def linear_normed(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor | None, eps: float,
                   weight: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor, *,
                   scratch: torch.Tensor, count: int, activation: str = "none",

@@ -9,7 +9,7 @@ from ayaka_b200.parts.base import BuildContext, Part, register_part
 from ayaka_b200.parts.context import StepContext
 from ayaka_b200.parts.spec import PartSpec
 
-__all__ = ["LearnedPositions", "LinearHead", "NoPositions", "TokenEmbedding"]
+__all__ = ["LearnedPositions", "LinearHead", "NoPositions", "PositionEncoding", "TokenEmbedding"]
 
 
 class PositionEncoding(Part):

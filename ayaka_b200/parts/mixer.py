@@ -7,6 +7,7 @@ import torch
 from ayaka_b200.kernels import ops
 from ayaka_b200.parts.base import BuildContext, CacheNeed, Part, StateNeed, register_part
 from ayaka_b200.parts.context import LayerCache, StepContext
+from ayaka_b200.parts.embedding import PositionEncoding
 from ayaka_b200.parts.spec import PartSpec
 
 __all__ = ["Attention", "Mixer"]
@@ -61,6 +62,9 @@ class Attention(Mixer):
         self.scale = float(spec.scale)  # type: ignore[arg-type]
         self.window = int(spec.get("window", 0))  # type: ignore[arg-type]
         self.position = position
+        # keys go to the cache as projected unless the position encoding rewrites them first
+        self._keys_as_projected = position is None or \
+            type(position).on_query_key is PositionEncoding.on_query_key
         if self.num_heads % self.num_kv_heads:
             raise ValueError(f"num_kv_heads ({self.num_kv_heads}) must divide num_heads "
                              f"({self.num_heads})")
@@ -83,21 +87,35 @@ class Attention(Mixer):
                 cache: LayerCache) -> None:
         qkv = step.workspace.buffer("attention.qkv", self.q_width + 2 * self.kv_width,
                                     self.ctx.dtype)
-        ops.linear(hidden, self.qkv_weight, self.qkv_bias, qkv, rows=step.num_rows)
-        self._attend(qkv, residual, step, cache)
+        stored = self._project(hidden, qkv, step, cache)
+        self._attend(qkv, residual, step, cache, stored)
 
     def forward_normed(self, norm: Part, residual: torch.Tensor, step: StepContext,
                        cache: LayerCache) -> None:
         qkv = step.workspace.buffer("attention.qkv", self.q_width + 2 * self.kv_width,
                                     self.ctx.dtype)
         scratch = step.workspace.buffer("block.normed", self.width, self.ctx.dtype)
-        ops.linear_normed(residual, norm.weight, norm.bias, norm.eps,  # type: ignore
-                          self.qkv_weight, self.qkv_bias, qkv, scratch=scratch,
-                          count=step.num_rows)
-        self._attend(qkv, residual, step, cache)
+        ops.layer_norm(residual, norm.weight, norm.bias, norm.eps,  # type: ignore
+                       scratch, count=step.num_rows)
+        stored = self._project(scratch, qkv, step, cache)
+        self._attend(qkv, residual, step, cache, stored)
+
+    def _project(self, hidden: torch.Tensor, qkv: torch.Tensor, step: StepContext,
+                 cache: LayerCache) -> bool:
+        """The fused projection; True if its epilogue also stored the keys and values of the
+        step's rows into the cache (prompt portions in bfloat16, no position encoding that
+        would change the keys first)."""
+        if cache.writes and not step.decode_only and self._keys_as_projected:
+            group = step.groups[cache.group]  # type: ignore[index]
+            if ops.linear_kv(hidden, self.qkv_weight, self.qkv_bias, qkv, group.slot_mapping,
+                             cache.k_pages, cache.v_pages, q_width=self.q_width,
+                             rows=step.num_rows):
+                return True
+        ops.linear(hidden, self.qkv_weight, self.qkv_bias, qkv, rows=step.num_rows)
+        return False
 
     def _attend(self, qkv: torch.Tensor, residual: torch.Tensor, step: StepContext,
-                cache: LayerCache) -> None:
+                cache: LayerCache, stored: bool = False) -> None:
         n = step.num_rows
         group = step.groups[cache.group]  # type: ignore[index]
         q = qkv[:, :self.q_width]
@@ -105,7 +123,7 @@ class Attention(Mixer):
         v = qkv[:, self.q_width + self.kv_width:]
         if self.position is not None:
             self.position.on_query_key(q, k, step)  # type: ignore[attr-defined]
-        if cache.writes and not step.decode_only:
+        if cache.writes and not step.decode_only and not stored:
             ops.kv_store(k, v, group.slot_mapping, cache.k_pages, cache.v_pages, rows=n)
         attended = step.workspace.buffer("attention.out", self.q_width, self.ctx.dtype)
         if step.decode_only:

@@ -412,6 +412,55 @@ def test_kv_store_scatters_rows(dtype, heads, head_dim, page):
                        torch.nan_to_num(want_v.float(), nan=-7.0))
 
 
+@pytest.mark.parametrize("rows,width,heads,kv_heads,head_dim,page", [
+    (2048, 1600, 25, 25, 64, 16),   # the persistent kernel, 192-wide tiles that straddle q | k
+    (300, 136, 4, 2, 32, 8),        # one tile per CTA, grouped heads, a ragged last row tile
+    (200, 72, 2, 1, 96, 8),         # queries 192 wide, one key/value head of 96
+    (130, 200, 4, 2, 96, 4),        # a head size that is no power of two
+    (65, 64, 2, 2, 32, 16),
+])
+def test_linear_that_also_stores_keys_and_values(rows, width, heads, kv_heads, head_dim, page):
+    """The fused projection whose epilogue writes the key and value columns into the pages
+    (and the query columns to its output) gives bit for bit what the product followed by the
+    store gives, and stores nothing for rows without a slot. A product that cannot carry the store says so and does nothing."""
+    ops = _ops()
+    q_width, kv_width = heads * head_dim, kv_heads * head_dim
+    n = q_width + 2 * kv_width
+    a = _randn(rows + 3, width, seed=41, dtype=torch.bfloat16)
+    w = (_randn(n, width, seed=42) * 0.1).bfloat16()
+    bias = _randn(n, seed=43)
+    pages = -(-rows // page) + 5
+    order = torch.randperm(pages * page, generator=torch.Generator().manual_seed(6))[:rows + 3]
+    order[::11] = -1
+    slots = order.to(torch.int32).to(DEV)
+
+    def empty_pages():
+        return torch.full((pages, kv_heads, page, head_dim), float("nan"), dtype=torch.bfloat16,
+                          device=DEV)
+
+    out_a = torch.zeros(rows + 3, n, dtype=torch.bfloat16, device=DEV)
+    k_a, v_a = empty_pages(), empty_pages()
+    assert ops.linear_kv(a, w, bias, out_a, slots, k_a, v_a, q_width=q_width, rows=rows)
+    from ayaka_b200.kernels import gemm_tc
+    gemm_tc.check_status(a.device)
+    out_b = torch.zeros_like(out_a)
+    k_b, v_b = empty_pages(), empty_pages()
+    ops.linear(a, w, bias, out_b, rows=rows)
+    ops.kv_store(out_b[:, q_width:q_width + kv_width], out_b[:, q_width + kv_width:], slots,
+                 k_b, v_b, rows=rows)
+    assert torch.equal(out_a[:, :q_width], out_b[:, :q_width])
+    assert not out_a[:, q_width:].any()  # keys and values went to the cache only
+    for got, want in ((k_a, k_b), (v_a, v_b)):
+        assert torch.equal(torch.nan_to_num(got.float(), nan=-7.0),
+                           torch.nan_to_num(want.float(), nan=-7.0))
+    assert int((~torch.isnan(k_a.float())).sum()) == int((order[:rows] >= 0).sum()) * kv_width
+    # few rows: the weight-streaming kernel has no such epilogue
+    assert not ops.linear_kv(a, w, bias, out_a, slots, k_a, v_a, q_width=q_width, rows=64)
+    # float32: not this kernel's business
+    assert not ops.linear_kv(a.float(), w.float(), bias, out_a.float(), slots, k_a.float(),
+                             v_a.float(), q_width=q_width, rows=rows)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_kv_store_then_attend(dtype):
     """The store writes exactly the slots it is given; a padding row stores nothing and a
