@@ -1018,6 +1018,12 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w,
   if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+}  // namespace ayk
+
+#include "gemm_stream.cuh"
+
+namespace ayk {
+
 // Tensor maps are cached by what they describe: weights are static and activations live in
 // persistent buffers, so a serving process encodes each map once.
 struct MapKey {
@@ -1249,12 +1255,25 @@ inline int choose_tile(int M, int N) {
 
 AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
 
+namespace ayk {
+// Products of up to this many rows go to gemm_stream_kernel when nothing else is asked for.
+inline int& stream_rows() {
+  static int rows = ST_MAX_ROWS;
+  return rows;
+}
+}  // namespace ayk
+// For measurements: 0 sends every product of at most 64 rows to the cluster split-K kernel.
+AYK_API void ayk_set_stream_rows(int rows) {
+  ayk::stream_rows() = rows < 0 ? 0 : (rows > ayk::ST_MAX_ROWS ? ayk::ST_MAX_ROWS : rows);
+}
+
 // mode: 0 = bf16 out with activation, 1 = fp32 out with activation, 2 = fp32 out += (residual).
 // tile_n: 0 = choose; 32, 64, 128, 192, 256 = one tile of that width per CTA; 1128, 1192,
 // 1256 = the persistent kernel with tiles 128, 192 or 256 wide; 2192, 2256 = the persistent
 // kernel for CTA pairs (256-row tiles, 192 or 256 wide; measured level with 1192 / 1256 at
 // GPT-2 XL's shapes, so the choice never picks it); negative = the few-rows kernel (see
-// pick_splits). `status` is one device int that a CTA sets to AYK_WAIT_TIMEOUT if a wait ran
+// pick_splits; -200 = the kernel for at most 16 rows that holds its weights on chip before the
+// rows arrive, gemm_stream.cuh). `status` is one device int that a CTA sets to AYK_WAIT_TIMEOUT if a wait ran
 // out; the host reads it when it checks a step.
 AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, const float* bias,
                              void* out, int ldo, int M, int N, int K, int act, int mode,
@@ -1272,6 +1291,12 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
     return AYK_BAD_ALIGNMENT;
   }
   cudaStream_t s = (cudaStream_t)stream;
+  if (tile_n == 0 && M <= stream_rows() && stream_splits(M, K) > 0) tile_n = -200;
+  if (tile_n == -200) {
+    const int splits = stream_splits(M, K);
+    if (splits == 0) return AYK_BAD_ARGUMENT;
+    return launch_gemm_stream(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, splits, s);
+  }
   if (tile_n == 0 && M <= 64) tile_n = -1;  // few rows: the weight-streaming kernel
   if (tile_n < 0) {
     if (M > 64) return AYK_BAD_ARGUMENT;

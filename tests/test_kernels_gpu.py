@@ -240,6 +240,59 @@ def test_linear_normed(m, n, k):
         assert torch.isnan(out[m:]).all()
 
 
+@pytest.mark.parametrize("m", [1, 5, 8, 9, 16])
+def test_linear_at_most_16_rows(m):
+    """The kernel that holds its weights on chip before the rows arrive (tile code -200): one
+    CTA per 16 columns, K over a cluster from 57 steps of 32 on (splits 1, 2, 4, 8), tails in
+    every dimension, every epilogue; rows beyond the product stay as they are."""
+    from ayaka_b200.kernels import gemm_tc
+    for n, k in ((1600, 1600), (300, 6400), (50257, 160), (136, 72), (77, 3200), (333, 14336),
+                 (17, 8)):
+        a = _randn(m, k, seed=50, dtype=torch.bfloat16)
+        w = _randn(n, k, seed=51, dtype=torch.bfloat16, scale=1 / math.sqrt(k))
+        bias = _randn(n, seed=52)
+        exact = a.double() @ w.double().t() + bias.double()
+        out = torch.full((m + 1, n), float("nan"), device=DEV)
+        gemm_tc.linear_bf16(a, w, bias, out, m, 0, False, tile_n=-200)
+        torch.testing.assert_close(out[:m].double(), exact, rtol=1e-4, atol=1e-4)
+        assert torch.isnan(out[m:]).all()
+        again = torch.zeros(m, n, device=DEV)
+        gemm_tc.linear_bf16(a, w, bias, again, m, 0, False, tile_n=-200)
+        assert torch.equal(again, out[:m])
+        base = _randn(m, n, seed=53)
+        acc = base.clone()
+        gemm_tc.linear_bf16(a, w, None, acc, m, 0, True, tile_n=-200)
+        torch.testing.assert_close(acc.double(), exact - bias.double() + base.double(),
+                                   rtol=1e-4, atol=1e-4)
+        half = torch.full((m + 1, n), 7.0, dtype=torch.bfloat16, device=DEV)
+        gemm_tc.linear_bf16(a, w, bias, half, m, 1, False, tile_n=-200)
+        torch.testing.assert_close(half[:m].double(), plain.gelu(exact, "gelu_new"),
+                                   rtol=1e-2, atol=1e-2)
+        assert bool((half[m:] == 7.0).all())
+        # a row's sums do not depend on the other rows of the step or on its place among them
+        if m > 1:
+            alone = torch.zeros(1, n, device=DEV)
+            gemm_tc.linear_bf16(a[m - 1:].contiguous(), w, bias, alone, 1, 0, False, tile_n=-200)
+            assert torch.equal(alone[0], out[m - 1])
+    gemm_tc.check_status(a.device)
+
+
+def test_linear_at_most_16_rows_refuses_what_it_cannot_take():
+    from ayaka_b200.errors import BackendError
+    from ayaka_b200.kernels import gemm_tc
+    w = _randn(64, 20480, seed=54, dtype=torch.bfloat16)
+    for m, k in ((17, 64), (4, 20480)):  # too many rows; K beyond eight CTAs' shared memory
+        a = _randn(m, k, seed=55, dtype=torch.bfloat16)
+        out = torch.zeros(m, 64, device=DEV)
+        with pytest.raises(BackendError):
+            gemm_tc.linear_bf16(a, w[:, :k], None, out, m, 0, False, tile_n=-200)
+    # left to itself the library takes another kernel for them
+    a = _randn(4, 20480, seed=56, dtype=torch.bfloat16)
+    out = torch.zeros(4, 64, device=DEV)
+    gemm_tc.linear_bf16(a, w, None, out, 4, 0, False)
+    torch.testing.assert_close(out.double(), a.double() @ w.double().t(), rtol=1e-3, atol=1e-3)
+
+
 def test_linear_tcgen05_few_rows_is_reproducible():
     from ayaka_b200.kernels import gemm_tc
     a = _randn(8, 6400, seed=34, dtype=torch.bfloat16)
@@ -274,15 +327,17 @@ def test_linear_batch_invariance():
             part = torch.zeros(rows, 200, device=DEV)
             ops.linear(a[:rows].contiguous(), w, None, part, kernel=kernel)
             assert torch.equal(part, whole[:rows])
-        # up to 64 rows the bfloat16 tensor-core product splits K over a cluster: the same
-        # sums in another order, equal within fp32 rounding and equal among themselves
-        small = torch.zeros(64, 200, device=DEV)
-        ops.linear(a[:64].contiguous(), w, None, small, kernel=kernel)
-        torch.testing.assert_close(small, whole[:64], rtol=1e-5, atol=1e-5)
-        for rows in (1, 7, 33):
-            part = torch.zeros(rows, 200, device=DEV)
-            ops.linear(a[:rows].contiguous(), w, None, part, kernel=kernel)
-            assert torch.equal(part, small[:rows])
+        # up to 64 rows the bfloat16 tensor-core product splits K over a cluster, up to 16
+        # rows over the warps of a CTA: the same sums in another order, equal within fp32
+        # rounding and equal among the row counts of their class
+        for most, fewer in ((64, (17, 33)), (16, (1, 7, 9))):
+            small = torch.zeros(most, 200, device=DEV)
+            ops.linear(a[:most].contiguous(), w, None, small, kernel=kernel)
+            torch.testing.assert_close(small, whole[:most], rtol=1e-5, atol=1e-5)
+            for rows in fewer:
+                part = torch.zeros(rows, 200, device=DEV)
+                ops.linear(a[:rows].contiguous(), w, None, part, kernel=kernel)
+                assert torch.equal(part, small[:rows])
 
 
 # ---------------------------------------------------------------------------------------------
