@@ -34,7 +34,9 @@ constexpr int DEC_THREADS = DEC_WARPS * 32;
 // decode layer (GPT-2 XL shapes, 768 keys): one batch ahead beats two and three at 8 and 64
 // rows (47 / 124 against 51 / 140 microseconds a layer) — a shallow queue is 32 KB of shared
 // memory per CTA, seven CTAs per SM, and the many resident warps hide more latency than a
-// deep queue of few warps does.
+// deep queue of few warps does. Filling both stages of the strip before the wait (and
+// requesting a batch's successor only once the batch is in registers) was slower too: 39.4
+// against 37.5 microseconds a layer at 8 rows, 129 against 113 at 64.
 #ifndef AYK_DEC_DEPTH
 #define AYK_DEC_DEPTH 1
 #endif
@@ -159,8 +161,18 @@ template <int N> __device__ __forceinline__ void cp_async_wait_group() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+__device__ __forceinline__ void dec_cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void dec_cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void dec_st_cluster(uint32_t address, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(address), "f"(v) : "memory");
+}
+
 template <typename T, int TPK, int BATCH>
-__global__ void __launch_bounds__(DEC_THREADS)
+__global__ void __launch_bounds__(DEC_THREADS, 6)
 attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k_pages,
                         const T* __restrict__ v_pages, const int* __restrict__ block_table,
                         int table_stride, const int* __restrict__ request_of_row,
@@ -199,6 +211,8 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
     }
     return;
   }
+  // "this CTA runs": awaited before any CTA of the cluster writes into another's shared memory
+  if (clustered) dec_cluster_arrive();
   const int kv_head = head / group;
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   // the request's keys lo..pos are cut into splits * warps contiguous shares, a multiple of
@@ -242,6 +256,10 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
   extern __shared__ __align__(16) unsigned char dec_smem[];
   uint4* strip = reinterpret_cast<uint4*>(dec_smem) +
                  (size_t)warp * (DEC_DEPTH + 1) * BATCH * 2 * PIECES * 32;
+  // where rank 0 of a cluster receives the CTAs' shares: [split][2 + head_dim] floats
+  float* recv = reinterpret_cast<float*>(reinterpret_cast<uint4*>(dec_smem) +
+                                         (size_t)DEC_WARPS * (DEC_DEPTH + 1) * BATCH * 2 *
+                                             PIECES * 32);
   auto piece = [&](int stage, int u, int kind, int part) {
     return strip + ((((size_t)stage * BATCH + u) * 2 + kind) * PIECES + part) * 32 + lane;
   };
@@ -369,7 +387,11 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
   }
   __syncthreads();
   DEC_MARK(4);
-  // fold the warps' shares, in warp order: c_share = (max, sum, weighted values[head_dim])
+  if (clustered) dec_cluster_wait();  // every CTA of the cluster has started
+  // fold the warps' shares, in warp order, into (max, sum, weighted values[head_dim]): into
+  // c_share, or with a cluster straight into this CTA's row of rank 0's `recv`
+  const uint32_t remote = clustered
+      ? peer_address(recv + (size_t)split * (head_dim + 2), 0u) : 0u;
   if (tid < TPK) {
     float m = -INFINITY, l = 0.f, total[8];
 #pragma unroll
@@ -377,55 +399,61 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
     for (int w = 0; w < DEC_WARPS; ++w) {
       merge_state(m, l, total, s_m[w][tid], s_l[w][tid], s_wacc[w][tid]);
     }
-    if (tid == 0) { c_share[0] = m; c_share[1] = l; }
-    if (tid * 8 < head_dim) {
+    if (clustered) {
+      if (tid == 0) {
+        dec_st_cluster(remote, m);
+        dec_st_cluster(remote + 4, l);
+      }
+      if (tid * 8 < head_dim) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) c_share[2 + tid * 8 + i] = total[i];
+        for (int i = 0; i < 8; ++i) dec_st_cluster(remote + (2 + tid * 8 + i) * 4, total[i]);
+      }
+    } else {
+      if (tid == 0) { c_share[0] = m; c_share[1] = l; }
+      if (tid * 8 < head_dim) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) c_share[2 + tid * 8 + i] = total[i];
+      }
     }
+  }
+  if (clustered) {
+    // the splits of one (request, head) are the CTAs of one cluster: every CTA has written
+    // its share into rank 0's shared memory, and after one cluster barrier rank 0 merges them
+    // from there, in rank order; no scratch, no tickets, no remote load
+    dec_cluster_arrive();
+    dec_cluster_wait();
+    if (split != 0) return;
+    float m[8], l[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      m[s] = s < splits ? recv[s * (head_dim + 2)] : -INFINITY;
+      l[s] = s < splits ? recv[s * (head_dim + 2) + 1] : 0.f;
+    }
+    float top = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) top = fmaxf(top, m[s]);
+    float w[8], denom = 0.f;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {  // rank order: the sum does not change from run to run
+      w[s] = m[s] == -INFINITY ? 0.f : expf(m[s] - top);
+      denom += l[s] * w[s];
+    }
+    const float inv = 1.f / denom;
+    for (int d = tid; d < head_dim; d += DEC_THREADS) {
+      float sum = 0.f;
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        if (s < splits) sum += recv[s * (head_dim + 2) + 2 + d] * w[s];
+      }
+      stf(dst + d, sum * inv);
+    }
+    return;
   }
   __syncthreads();
   if (splits == 1) {
     const float inv = 1.f / c_share[1];
     for (int d = tid; d < head_dim; d += DEC_THREADS) stf(dst + d, c_share[2 + d] * inv);
     DEC_MARK(5);
-    return;
-  }
-  if (clustered) {
-    // the splits of one (request, head) are the CTAs of one cluster: rank 0 merges the shares
-    // through distributed shared memory, in rank order; no scratch, no tickets
-    cluster_sync_all();
-    if (split == 0) {
-      // every remote value is requested before the first is used: the merge costs two trips
-      // through distributed shared memory (maxima and sums, then the values), not one per load
-      float m[8], l[8];
-#pragma unroll
-      for (int s = 0; s < 8; ++s) {
-        m[s] = s < splits ? ld_cluster_f32(peer_address(&c_share[0], (uint32_t)s)) : -INFINITY;
-        l[s] = s < splits ? ld_cluster_f32(peer_address(&c_share[1], (uint32_t)s)) : 0.f;
-      }
-      float top = -INFINITY;
-#pragma unroll
-      for (int s = 0; s < 8; ++s) top = fmaxf(top, m[s]);
-      float w[8], denom = 0.f;
-#pragma unroll
-      for (int s = 0; s < 8; ++s) {  // rank order: the sum does not change from run to run
-        w[s] = m[s] == -INFINITY ? 0.f : expf(m[s] - top);
-        denom += l[s] * w[s];
-      }
-      const float inv = 1.f / denom;
-      for (int d = tid; d < head_dim; d += DEC_THREADS) {
-        float v[8];
-#pragma unroll
-        for (int s = 0; s < 8; ++s) {
-          v[s] = s < splits ? ld_cluster_f32(peer_address(&c_share[2 + d], (uint32_t)s)) : 0.f;
-        }
-        float sum = 0.f;
-#pragma unroll
-        for (int s = 0; s < 8; ++s) sum += v[s] * w[s];
-        stf(dst + d, sum * inv);
-      }
-    }
-    cluster_sync_all();  // nobody leaves while rank 0 may still read its share
     return;
   }
   // through scratch: every CTA stores its share; the last one to finish merges them
@@ -477,11 +505,14 @@ int launch_decode(const void* q, int ld_q, const void* k_pages, const void* v_pa
     while ((1 << page_shift) < page_size) ++page_shift;
   }
   // every lane's strip: (depth + 1) stages x batch keys x (K, V) x 16 or 32 bytes
-  const size_t smem = (size_t)DEC_THREADS * (DEC_DEPTH + 1) * BATCH * 2 * 8 * sizeof(T);
+  const size_t strips = (size_t)DEC_THREADS * (DEC_DEPTH + 1) * BATCH * 2 * 8 * sizeof(T);
+  // ... and with a cluster the room where rank 0 receives the shares
+  const size_t smem = strips + (clustered ? (size_t)splits * (head_dim + 2) * sizeof(float) : 0);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<T, TPK, BATCH>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(strips + 8 * (256 + 2) * sizeof(float)));
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
