@@ -77,11 +77,14 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t address, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(address), "f"(v) : "memory");
 }
 
-// grid (ceil(N / 16), splits), cluster (1, splits): CTA (x, y) owns columns 16x .. 16x + 15
-// and the steps y * steps_per_split .. of K. Dynamic shared memory: steps_per_split KB of
-// weight slots, ST_RED_BYTES for the sum over warps, and with a split splits * 1 KB where
-// rank 0 receives the partial sums.
-__global__ void __launch_bounds__(ST_THREADS, 4)
+// grid (ceil(N / (16 CT)), splits), cluster (1, splits): CTA (x, y) owns CT tiles of 16
+// columns from column 16 CT x on and the steps y * steps_per_split .. of K. With CT = 2 (wide
+// products, no split) a lane's row fragments serve two column tiles: half the loads of rows
+// per byte of weights. Dynamic shared memory: CT * steps_per_split KB of weight slots, CT *
+// ST_RED_BYTES for the sum over warps, and with a split splits * 1 KB where rank 0 receives
+// the partial sums.
+template <int CT>
+__global__ void __launch_bounds__(ST_THREADS, 4 / CT)
 gemm_stream_kernel(const __nv_bfloat16* __restrict__ a, int lda,
                    const __nv_bfloat16* __restrict__ w, int ldw, const float* __restrict__ bias,
                    void* __restrict__ out, int ldo, int M, int N, int K, int act, int mode,
@@ -91,21 +94,22 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ a, int lda,
   const int g = lane >> 2, q = lane & 3;
   const int splits = gridDim.y;
   const int rank = blockIdx.y;
-  const int n0 = blockIdx.x * ST_COLS;
+  const int n0 = blockIdx.x * (ST_COLS * CT);
   const int total_steps = (K + ST_STEP_K - 1) / ST_STEP_K;
   const int step_lo = rank * steps_per_split;
   const int step_hi = min(step_lo + steps_per_split, total_steps);
   const int my_steps = max(step_hi - step_lo, 0);
 
   uint4* slots = reinterpret_cast<uint4*>(st_smem);
-  float* red = reinterpret_cast<float*>(st_smem + (size_t)steps_per_split * 1024);
-  float* recv = red + ST_RED_BYTES / 4;
+  float* red = reinterpret_cast<float*>(st_smem + (size_t)steps_per_split * 1024 * CT);
+  float* recv = red + CT * ST_RED_BYTES / 4;
 
   if (splits > 1) cluster_arrive();  // "this CTA runs": awaited before anyone writes to it
 
   // ---- everything that is a weight: requested now, whatever the kernel ahead is doing
-  {
-    const int row0 = n0 + g, row1 = n0 + 8 + g;
+#pragma unroll
+  for (int ct = 0; ct < CT; ++ct) {
+    const int row0 = n0 + ct * ST_COLS + g, row1 = row0 + 8;
     const __nv_bfloat16* src0 = w + (size_t)(row0 < N ? row0 : 0) * ldw;
     const __nv_bfloat16* src1 = w + (size_t)(row1 < N ? row1 : 0) * ldw;
 #pragma unroll
@@ -114,7 +118,7 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ a, int lda,
       if (local < my_steps) {
         const int k = (step_lo + local) * ST_STEP_K + 8 * q;
         const bool in_k = k < K;  // K is a multiple of 8: a piece is inside or outside
-        uint4* slot = slots + (size_t)local * 64 + lane;
+        uint4* slot = slots + ((size_t)local * CT + ct) * 64 + lane;
         cp_async_16_zfill(slot, in_k ? src0 + k : w, (in_k && row0 < N) ? 16u : 0u);
         cp_async_16_zfill(slot + 32, in_k ? src1 + k : w, (in_k && row1 < N) ? 16u : 0u);
       }
@@ -123,9 +127,9 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ a, int lda,
   pdl_launch_dependents();
   // the thread that writes output (row m, column n) of each tile of eight rows
   const int t = threadIdx.x;
-  const int c = t & 15, m_in_tile = (t >> 4) & 7;
-  const int n = n0 + c;
-  const bool writer = t < 128 && rank == 0 && n < N;
+  const int c = t & 15, m_in_tile = (t >> 4) & 7, tile_of_t = t >> 7;
+  const int n = n0 + tile_of_t * ST_COLS + c;
+  const bool writer = t < 128 * CT && rank == 0 && n < N;
   const float b = (writer && bias != nullptr) ? __ldg(bias + n) : 0.f;
 
   pdl_wait();
@@ -156,25 +160,38 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ a, int lda,
                  ? ld_rows_16(a_row + k) : make_uint4(0u, 0u, 0u, 0u);
     }
     if (mt == 0) cp_async_commit_wait_all();
-    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc0[CT][4], acc1[CT][4];
+#pragma unroll
+    for (int ct = 0; ct < CT; ++ct) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc0[ct][i] = acc1[ct][i] = 0.f;
+    }
 #pragma unroll
     for (int j = 0; j < ST_STEPS_PER_WARP; ++j) {
       const int local = warp + ST_WARPS * j;
       if (local < my_steps) {
-        const uint4 p0 = slots[(size_t)local * 64 + lane];
-        const uint4 p1 = slots[(size_t)local * 64 + 32 + lane];
-        mma_bf16_16816(acc0, p0.x, p1.x, p0.y, p1.y, x[j].x, x[j].y);
-        mma_bf16_16816(acc1, p0.z, p1.z, p0.w, p1.w, x[j].z, x[j].w);
+#pragma unroll
+        for (int ct = 0; ct < CT; ++ct) {
+          const uint4 p0 = slots[((size_t)local * CT + ct) * 64 + lane];
+          const uint4 p1 = slots[((size_t)local * CT + ct) * 64 + 32 + lane];
+          mma_bf16_16816(acc0[ct], p0.x, p1.x, p0.y, p1.y, x[j].x, x[j].y);
+          mma_bf16_16816(acc1[ct], p0.z, p1.z, p0.w, p1.w, x[j].z, x[j].w);
+        }
       }
     }
-    // lane (g, q) holds columns g and g + 8 of rows 2q and 2q + 1
+    // lane (g, q) holds columns g and g + 8 of rows 2q and 2q + 1 of each column tile
     if (mt > 0) __syncthreads();  // the last tile's sums have been read
-    reinterpret_cast<float4*>(red)[warp * 32 + lane] =
-        make_float4(acc0[0] + acc1[0], acc0[1] + acc1[1], acc0[2] + acc1[2], acc0[3] + acc1[3]);
+#pragma unroll
+    for (int ct = 0; ct < CT; ++ct) {
+      reinterpret_cast<float4*>(red)[(ct * ST_WARPS + warp) * 32 + lane] =
+          make_float4(acc0[ct][0] + acc1[ct][0], acc0[ct][1] + acc1[ct][1],
+                      acc0[ct][2] + acc1[ct][2], acc0[ct][3] + acc1[ct][3]);
+    }
     __syncthreads();
-    if (t < 128) {
+    if (t < 128 * CT) {
       const int from_lane = 4 * (c & 7) + (m_in_tile >> 1);
-      const int index = from_lane * 4 + (c >> 3) * 2 + (m_in_tile & 1);
+      const int index = tile_of_t * (ST_WARPS * 128) + from_lane * 4 + (c >> 3) * 2 +
+                        (m_in_tile & 1);
       float sum = red[index];
 #pragma unroll
       for (int v = 1; v < ST_WARPS; ++v) sum += red[v * 128 + index];
@@ -182,7 +199,7 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ a, int lda,
     }
   }
 
-  if (splits > 1) {
+  if (CT == 1 && splits > 1) {
     cluster_wait();  // every CTA of the cluster has started
     if (t < 128) {
       const uint32_t mine = peer_address(recv + rank * 256 + t, 0u);
@@ -230,26 +247,47 @@ inline int stream_splits(int M, int K) {
   return 0;
 }
 
+// From this many columns on a product without a K split runs with two column tiles per CTA
+// (half the CTAs, twice the weights each; GPT-2 XL: the query/key/value projection, the
+// feed-forward's first product and the head).
+#ifndef AYK_STREAM_WIDE_FROM
+#define AYK_STREAM_WIDE_FROM 4096
+#endif
+
+// wide: 0 = one column tile per CTA, 1 = two (refused with a K split), -1 = choose
 inline int launch_gemm_stream(const void* a, int lda, const void* w, int ldw, const float* bias,
                               void* out, int ldo, int M, int N, int K, int act, int mode,
-                              int splits, cudaStream_t stream) {
+                              int splits, int wide, cudaStream_t stream) {
   const int steps = (K + ST_STEP_K - 1) / ST_STEP_K;
   const int steps_per_split = (steps + splits - 1) / splits;
-  const size_t smem = (size_t)steps_per_split * 1024 + ST_RED_BYTES +
-                      (splits > 1 ? (size_t)splits * 1024 : 0);
+  if (wide < 0) wide = (splits == 1 && N >= AYK_STREAM_WIDE_FROM) ? 1 : 0;
+  if (wide && splits != 1) return AYK_BAD_ARGUMENT;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel,
+    cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<1>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          ST_MAX_STEPS * 1024 + ST_RED_BYTES + 8 * 1024);
+    if (e == cudaSuccess) {
+      e = cudaFuncSetAttribute(gemm_stream_kernel<2>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               2 * (ST_MAX_STEPS * 1024 + ST_RED_BYTES));
+    }
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return launch_kernel(gemm_stream_kernel, dim3((N + ST_COLS - 1) / ST_COLS, splits, 1),
-                       dim3(ST_THREADS), smem, stream, splits,
-                       reinterpret_cast<const __nv_bfloat16*>(a), lda,
-                       reinterpret_cast<const __nv_bfloat16*>(w), ldw, bias, out, ldo, M, N, K,
-                       act, mode, steps_per_split);
+  const __nv_bfloat16* a16 = reinterpret_cast<const __nv_bfloat16*>(a);
+  const __nv_bfloat16* w16 = reinterpret_cast<const __nv_bfloat16*>(w);
+  if (wide) {
+    const size_t smem = 2 * ((size_t)steps_per_split * 1024 + ST_RED_BYTES);
+    return launch_kernel(gemm_stream_kernel<2>, dim3((N + 2 * ST_COLS - 1) / (2 * ST_COLS), 1, 1),
+                         dim3(ST_THREADS), smem, stream, 1, a16, lda, w16, ldw, bias, out, ldo,
+                         M, N, K, act, mode, steps_per_split);
+  }
+  const size_t smem = (size_t)steps_per_split * 1024 + ST_RED_BYTES +
+                      (splits > 1 ? (size_t)splits * 1024 : 0);
+  return launch_kernel(gemm_stream_kernel<1>, dim3((N + ST_COLS - 1) / ST_COLS, splits, 1),
+                       dim3(ST_THREADS), smem, stream, splits, a16, lda, w16, ldw, bias, out,
+                       ldo, M, N, K, act, mode, steps_per_split);
 }
 
 }  // namespace ayk

@@ -1273,7 +1273,7 @@ AYK_API void ayk_set_stream_rows(int rows) {
 // kernel for CTA pairs (256-row tiles, 192 or 256 wide; measured level with 1192 / 1256 at
 // GPT-2 XL's shapes, so the choice never picks it); negative = the few-rows kernel (see
 // pick_splits; -200 = the kernel for at most 16 rows that holds its weights on chip before the
-// rows arrive, gemm_stream.cuh). `status` is one device int that a CTA sets to AYK_WAIT_TIMEOUT if a wait ran
+// rows arrive, gemm_stream.cuh; -201 / -202 = the same with one / two column tiles per CTA). `status` is one device int that a CTA sets to AYK_WAIT_TIMEOUT if a wait ran
 // out; the host reads it when it checks a step.
 AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, const float* bias,
                              void* out, int ldo, int M, int N, int K, int act, int mode,
@@ -1292,10 +1292,11 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
   }
   cudaStream_t s = (cudaStream_t)stream;
   if (tile_n == 0 && M <= stream_rows() && stream_splits(M, K) > 0) tile_n = -200;
-  if (tile_n == -200) {
+  if (tile_n <= -200 && tile_n >= -202) {
     const int splits = stream_splits(M, K);
     if (splits == 0) return AYK_BAD_ARGUMENT;
-    return launch_gemm_stream(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, splits, s);
+    return launch_gemm_stream(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, splits,
+                              tile_n == -200 ? -1 : (tile_n == -202 ? 1 : 0), s);
   }
   if (tile_n == 0 && M <= 64) tile_n = -1;  // few rows: the weight-streaming kernel
   if (tile_n < 0) {

@@ -240,39 +240,46 @@ def test_linear_normed(m, n, k):
         assert torch.isnan(out[m:]).all()
 
 
+@pytest.mark.parametrize("code", [-201, -202])
 @pytest.mark.parametrize("m", [1, 5, 8, 9, 16])
-def test_linear_at_most_16_rows(m):
-    """The kernel that holds its weights on chip before the rows arrive (tile code -200): one
-    CTA per 16 columns, K over a cluster from 57 steps of 32 on (splits 1, 2, 4, 8), tails in
-    every dimension, every epilogue; rows beyond the product stay as they are."""
+def test_linear_at_most_16_rows(m, code):
+    """The kernel that holds its weights on chip before the rows arrive: one CTA per 16
+    (tile code -201) or 32 columns (-202, without a K split), K over a cluster from 57 steps
+    of 32 on (splits 1, 2, 4, 8), tails in every dimension, every epilogue; rows beyond the
+    product stay as they are; both codes give the same bits."""
     from ayaka_b200.kernels import gemm_tc
     for n, k in ((1600, 1600), (300, 6400), (50257, 160), (136, 72), (77, 3200), (333, 14336),
                  (17, 8)):
+        if code == -202 and k > 1792:
+            continue
         a = _randn(m, k, seed=50, dtype=torch.bfloat16)
         w = _randn(n, k, seed=51, dtype=torch.bfloat16, scale=1 / math.sqrt(k))
         bias = _randn(n, seed=52)
         exact = a.double() @ w.double().t() + bias.double()
         out = torch.full((m + 1, n), float("nan"), device=DEV)
-        gemm_tc.linear_bf16(a, w, bias, out, m, 0, False, tile_n=-200)
+        gemm_tc.linear_bf16(a, w, bias, out, m, 0, False, tile_n=code)
         torch.testing.assert_close(out[:m].double(), exact, rtol=1e-4, atol=1e-4)
         assert torch.isnan(out[m:]).all()
+        other = torch.zeros(m, n, device=DEV)
+        gemm_tc.linear_bf16(a, w, bias, other, m, 0, False, tile_n=-201)
+        assert torch.equal(other, out[:m])
         again = torch.zeros(m, n, device=DEV)
-        gemm_tc.linear_bf16(a, w, bias, again, m, 0, False, tile_n=-200)
+        gemm_tc.linear_bf16(a, w, bias, again, m, 0, False, tile_n=code)
         assert torch.equal(again, out[:m])
         base = _randn(m, n, seed=53)
         acc = base.clone()
-        gemm_tc.linear_bf16(a, w, None, acc, m, 0, True, tile_n=-200)
+        gemm_tc.linear_bf16(a, w, None, acc, m, 0, True, tile_n=code)
         torch.testing.assert_close(acc.double(), exact - bias.double() + base.double(),
                                    rtol=1e-4, atol=1e-4)
         half = torch.full((m + 1, n), 7.0, dtype=torch.bfloat16, device=DEV)
-        gemm_tc.linear_bf16(a, w, bias, half, m, 1, False, tile_n=-200)
+        gemm_tc.linear_bf16(a, w, bias, half, m, 1, False, tile_n=code)
         torch.testing.assert_close(half[:m].double(), plain.gelu(exact, "gelu_new"),
                                    rtol=1e-2, atol=1e-2)
         assert bool((half[m:] == 7.0).all())
         # a row's sums do not depend on the other rows of the step or on its place among them
         if m > 1:
             alone = torch.zeros(1, n, device=DEV)
-            gemm_tc.linear_bf16(a[m - 1:].contiguous(), w, bias, alone, 1, 0, False, tile_n=-200)
+            gemm_tc.linear_bf16(a[m - 1:].contiguous(), w, bias, alone, 1, 0, False, tile_n=code)
             assert torch.equal(alone[0], out[m - 1])
     gemm_tc.check_status(a.device)
 
@@ -286,6 +293,10 @@ def test_linear_at_most_16_rows_refuses_what_it_cannot_take():
         out = torch.zeros(m, 64, device=DEV)
         with pytest.raises(BackendError):
             gemm_tc.linear_bf16(a, w[:, :k], None, out, m, 0, False, tile_n=-200)
+    a = _randn(4, 3200, seed=55, dtype=torch.bfloat16)  # two column tiles and a K split
+    with pytest.raises(BackendError):
+        gemm_tc.linear_bf16(a, w[:, :3200], None, torch.zeros(4, 64, device=DEV), 4, 0, False,
+                            tile_n=-202)
     # left to itself the library takes another kernel for them
     a = _randn(4, 20480, seed=56, dtype=torch.bfloat16)
     out = torch.zeros(4, 64, device=DEV)
