@@ -247,12 +247,30 @@ inline int stream_splits(int M, int K) {
   return 0;
 }
 
-// From this many columns on a product without a K split runs with two column tiles per CTA
-// (half the CTAs, twice the weights each; GPT-2 XL: the query/key/value projection, the
-// feed-forward's first product and the head).
+// From this many columns on, and while one column tile per CTA would still fit the SMs in
+// one round (four CTAs each), a product without a K split runs with two column tiles per CTA:
+// half the CTAs, twice the weights each (GPT-2 XL: the query/key/value projection and the
+// feed-forward's first product; measured 34.2 against 34.9 microseconds a layer at 8 rows).
+// Over several rounds the narrow CTAs win (the head, 50,257 columns: 29.7 against 30.8
+// microseconds at 8 rows).
 #ifndef AYK_STREAM_WIDE_FROM
 #define AYK_STREAM_WIDE_FROM 4096
 #endif
+
+inline int stream_sms() {
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device) !=
+            cudaSuccess) {
+      num_sms = 148;
+    }
+  }
+  return num_sms;
+}
+// Whether one column tile per CTA fits the SMs in one round.
+inline bool stream_one_round(int N) { return (N + ST_COLS - 1) / ST_COLS <= 4 * stream_sms(); }
 
 // wide: 0 = one column tile per CTA, 1 = two (refused with a K split), -1 = choose
 inline int launch_gemm_stream(const void* a, int lda, const void* w, int ldw, const float* bias,
@@ -260,7 +278,9 @@ inline int launch_gemm_stream(const void* a, int lda, const void* w, int ldw, co
                               int splits, int wide, cudaStream_t stream) {
   const int steps = (K + ST_STEP_K - 1) / ST_STEP_K;
   const int steps_per_split = (steps + splits - 1) / splits;
-  if (wide < 0) wide = (splits == 1 && N >= AYK_STREAM_WIDE_FROM) ? 1 : 0;
+  if (wide < 0) {
+    wide = (splits == 1 && N >= AYK_STREAM_WIDE_FROM && stream_one_round(N)) ? 1 : 0;
+  }
   if (wide && splits != 1) return AYK_BAD_ARGUMENT;
   static bool configured = false;
   if (!configured) {

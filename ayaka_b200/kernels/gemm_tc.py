@@ -7,7 +7,7 @@ from ctypes import c_int, c_void_p
 import torch
 
 from ayaka_b200.errors import BackendError
-from ayaka_b200.kernels.lib import check, library
+from ayaka_b200.kernels.lib import check, entry, raw_stream
 
 __all__ = ["check_status", "linear_bf16", "linear_bf16_kv", "status_word"]
 
@@ -53,13 +53,13 @@ def linear_bf16(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
     from ayaka_b200.kernels import ops
 
     ops._launches += 1
-    fn = library("gemm_tc").ayk_gemm_bf16_tc
+    fn = entry("gemm_tc", "ayk_gemm_bf16_tc")
     status = fn(c_void_p(a.data_ptr()), c_int(a.stride(0)), c_void_p(weight.data_ptr()),
                 c_int(weight.stride(0)), c_void_p(0 if bias is None else bias.data_ptr()),
                 c_void_p(out.data_ptr()), c_int(out.stride(0)), c_int(rows), c_int(n), c_int(k),
                 c_int(activation), c_int(mode), c_int(TILE_N if tile_n is None else tile_n),
                 c_void_p(status_word(a.device).data_ptr()),
-                c_void_p(torch.cuda.current_stream().cuda_stream))
+                c_void_p(raw_stream()))
     check(status, "linear (tcgen05)")
 
 
@@ -75,7 +75,7 @@ def linear_bf16_kv(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | N
     _, kv_heads, page_size, head_dim = k_pages.shape
     from ayaka_b200.kernels import ops
 
-    fn = library("gemm_tc").ayk_gemm_bf16_tc_kv
+    fn = entry("gemm_tc", "ayk_gemm_bf16_tc_kv")
     status = fn(c_void_p(a.data_ptr()), c_int(a.stride(0)), c_void_p(weight.data_ptr()),
                 c_int(weight.stride(0)), c_void_p(0 if bias is None else bias.data_ptr()),
                 c_void_p(out.data_ptr()), c_int(out.stride(0)), c_int(rows), c_int(n), c_int(k),
@@ -83,7 +83,7 @@ def linear_bf16_kv(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | N
                 c_void_p(v_pages.data_ptr()), c_int(q_width), c_int(kv_heads * head_dim),
                 c_int(kv_heads), c_int(head_dim), c_int(page_size),
                 c_void_p(status_word(a.device).data_ptr()),
-                c_void_p(torch.cuda.current_stream().cuda_stream))
+                c_void_p(raw_stream()))
     if status == 1:
         return False
     ops._launches += 1

@@ -13,7 +13,7 @@ from ctypes import c_float, c_int, c_void_p
 import torch
 
 from ayaka_b200.errors import BackendError
-from ayaka_b200.kernels.lib import check, library
+from ayaka_b200.kernels.lib import check, library, raw_stream
 
 __all__ = [
     "ACTIVATIONS",
@@ -67,7 +67,7 @@ def _status_word(device: torch.device) -> torch.Tensor:
 def _stream() -> c_void_p:
     global _launches
     _launches += 1
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    return c_void_p(raw_stream())
 
 
 def _ptr(tensor: torch.Tensor | None) -> c_void_p:
