@@ -14,6 +14,9 @@ time of 1 token) / (T - 1), the reference's method (``benchmarks/e2e/decode.py:1
 ``prefill`` is one 2,048-token step (two prompts of 1,024). ``roofline`` divides the bytes a
 decode step must read (every weight once plus the live requests' keys and values) by its
 time and by the measured copy bandwidth. ``points`` holds decode at batch 1 and 64.
+
+``--workload small|large`` runs one of the two serving workloads of BASELINE.json's other
+configurations instead (see :func:`workload_run`) and prints a line of its own.
 """
 
 from __future__ import annotations
@@ -244,6 +247,63 @@ def e2e_run(llm, cfg: dict, batch: int, tokens: int) -> dict:
             "ms_per_step": per_step * 1000}
 
 
+def workload_run(which: str) -> int:
+    """The two serving workloads BASELINE.json names beside the headline (``configs[3]`` and
+    ``configs[4]``), through ``LLM.generate`` with host token ids in and out; one JSON line.
+
+    ``small``: GPT-2 small sizes, 64 requests with prompt lengths uniform in [16, 1024) (cut
+    so that 128 more tokens fit), 128 greedy tokens each. ``large``: GPT-2 large sizes, 32
+    requests decoding 256 tokens at temperature 1.0 while eight 1,000-token prompts arrive in
+    portions of 256 tokens beside them (a step's budget is 288 tokens), page size 16."""
+    import torch
+
+    from ayaka_b200 import SamplingParams
+
+    def sized(n_layer: int, width: int, heads: int, inner: int) -> dict:
+        return {**XL, "n_layer": n_layer, "n_embd": width, "n_head": heads, "n_inner": inner}
+
+    generator = torch.Generator().manual_seed(7)
+
+    def prompts(lengths: list[int]) -> list[tuple[int, ...]]:
+        return [tuple(torch.randint(0, XL["vocab_size"], (n,), generator=generator).tolist())
+                for n in lengths]
+
+    if which == "small":
+        cfg = sized(12, 768, 12, 3072)
+        lengths = [min(int(n), cfg["n_positions"] - 128)
+                   for n in torch.randint(16, 1024, (64,), generator=generator).tolist()]
+        llm = build(cfg, 64, 2048)
+        batch = prompts(lengths)
+        params: object = SamplingParams(temperature=0.0, max_tokens=128, ignore_eos=True)
+        name = "GPT-2 small, 64 requests, prompts of 16 to 896 tokens, 128 greedy tokens each"
+    else:
+        cfg = sized(36, 1280, 20, 5120)
+        lengths = [64] * 32 + [1000] * 8
+        llm = build(cfg, 40, 288)
+        batch = prompts(lengths)
+        params = [SamplingParams(temperature=1.0, max_tokens=256 if i < 32 else 8,
+                                 ignore_eos=True, seed=i) for i in range(40)]
+        name = ("GPT-2 large, 32 requests decoding at temperature 1.0 beside 256-token "
+                "portions of eight 1,000-token prompts")
+    llm.generate(batch[:4], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    best, generated = math.inf, 0
+    for _ in range(3):
+        begin = time.perf_counter()
+        outputs = llm.generate(batch, params)
+        best = min(best, time.perf_counter() - begin)
+        generated = sum(len(o.outputs[0].token_ids) for o in outputs)
+    print(json.dumps({
+        "metric": f"generated tok/s through LLM.generate ({name})", "impl": "ours",
+        "value": round(generated / best, 1), "unit": "tok/s", "n_gpus": 1, "dtype": "bf16",
+        "data": "synthetic", "ms": round(best * 1000, 1), "generated_tokens": generated,
+        "prompt_tokens": sum(lengths),
+        "config": {"n_layer": cfg["n_layer"], "n_embd": cfg["n_embd"], "n_head": cfg["n_head"],
+                   "n_inner": cfg["n_inner"], "vocab_size": cfg["vocab_size"],
+                   "n_positions": cfg["n_positions"], "page_size": 16,
+                   "weights": "random bf16 seed 0", "cuda_graph": True}}))
+    return 0
+
+
 def reference_arm() -> int:
     print(json.dumps({
         "impl": "reference",
@@ -263,6 +323,10 @@ def main() -> int:
                         help="layers to build (GPT-2 XL has 48); sizes of a layer never change")
     parser.add_argument("--skip-points", action="store_true",
                         help="leave out the batch 1 / batch 64 points and the e2e run")
+    parser.add_argument("--workload", choices=("small", "large"),
+                        help="instead of the headline run: one of the two serving workloads "
+                             "(GPT-2 small with 64 ragged requests; GPT-2 large with prompt "
+                             "portions beside 32 decoding requests)")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -274,6 +338,8 @@ def main() -> int:
     if not torch.cuda.is_available():
         print("bench.py: no CUDA device")
         return 1
+    if args.workload:
+        return workload_run(args.workload)
     warmup = max(args.warmup, 3)
     steps = max(1, min(args.steps, XL["n_positions"] - PROMPT - 2 - warmup))
     cfg = {**XL, "n_layer": args.layers}
