@@ -742,3 +742,77 @@ def test_argmax_smallest_id_on_ties():
     tiny = torch.tensor([[3.0, 5.0, 5.0]], device=DEV)  # fewer columns than parts
     ops.argmax(tiny, split, rows=1, scratch=scratch)
     assert int(split[0]) == 1
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("rows", [1, 8, 16])
+def test_decode_chain_same_bits_with_and_without_dependent_launch(rows):
+    """Kernels of a decode step start before the kernel ahead has finished (programmatic
+    dependent launch) and read its output only after their wait, partly through L1. Over a
+    chain of 48 decode layers of GPT-2 XL's sizes (large enough that several kernels wait on
+    chip at once) nothing stale is ever read: the residual stream at the end has the same
+    bits with dependent launch on and off, launched one by one and replayed from a graph."""
+    ops = _ops()
+    width, inner, heads, head_dim, page, context, layers = 1600, 6400, 25, 64, 16, 256, 4
+
+    def weights(n, k, seed):
+        return [_randn(n, k, seed=seed + i, dtype=torch.bfloat16, scale=0.02)
+                for i in range(layers)]
+
+    w_qkv, w_out = weights(3 * width, width, 100), weights(width, width, 110)
+    w_up, w_down = weights(inner, width, 120), weights(width, inner, 130)
+    b_qkv, b_out, b_up = _randn(3 * width, seed=140), _randn(width, seed=141), \
+        _randn(inner, seed=142)
+    gamma, beta = _randn(width, seed=143) * 0.1 + 1.0, _randn(width, seed=144) * 0.1
+    start = _randn(rows, width, seed=145)
+    residual = torch.zeros(rows, width, device=DEV)
+    normed = torch.zeros(rows, width, dtype=torch.bfloat16, device=DEV)
+    qkv = torch.zeros(rows, 3 * width, dtype=torch.bfloat16, device=DEV)
+    attended = torch.zeros(rows, width, dtype=torch.bfloat16, device=DEV)
+    hidden = torch.zeros(rows, inner, dtype=torch.bfloat16, device=DEV)
+    pages = rows * context // page + 1
+    k_pages = [_randn(pages, heads, page, head_dim, seed=150 + i, dtype=torch.bfloat16)
+               for i in range(layers)]
+    v_pages = [_randn(pages, heads, page, head_dim, seed=160 + i, dtype=torch.bfloat16)
+               for i in range(layers)]
+    table = torch.arange(1, 1 + rows * context // page, dtype=torch.int32,
+                         device=DEV).view(rows, context // page)
+    request = torch.arange(rows, dtype=torch.int32, device=DEV)
+    position = torch.full((rows,), context - 1, dtype=torch.int32, device=DEV)
+    splits = ops.decode_splits(rows, heads, context)
+
+    def chain():
+        for index in range(48):
+            i = index % layers
+            ops.layer_norm(residual, gamma, beta, 1e-5, normed, count=rows)
+            ops.linear(normed, w_qkv[i], b_qkv, qkv, rows=rows)
+            ops.attention_decode(qkv[:, :width], k_pages[i], v_pages[i], table, request,
+                                 position, attended, num_heads=heads, scale=0.125, rows=rows,
+                                 splits=splits, k_new=qkv[:, width:2 * width],
+                                 v_new=qkv[:, 2 * width:], store=True)
+            ops.linear(attended, w_out[i], b_out, residual, residual=True, rows=rows)
+            ops.layer_norm(residual, gamma, beta, 1e-5, normed, count=rows)
+            ops.linear(normed, w_up[i], b_up, hidden, activation="gelu_tanh", rows=rows)
+            ops.linear(hidden, w_down[i], None, residual, residual=True, rows=rows)
+
+    results = []
+    try:
+        for dependent_launch in (False, True):
+            ops.set_pdl(dependent_launch)
+            residual.copy_(start)
+            chain()
+            results.append(residual.clone())
+            graph = torch.cuda.CUDAGraph()
+            residual.copy_(start)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph):
+                chain()
+            for _ in range(2):
+                residual.copy_(start)
+                graph.replay()
+                results.append(residual.clone())
+    finally:
+        ops.set_pdl(True)
+    torch.cuda.synchronize()
+    assert bool(torch.isfinite(results[0]).all())
+    assert all(torch.equal(results[0], other) for other in results[1:])
