@@ -248,6 +248,7 @@ class Scheduler:
         else:
             if tokens is None or set(tokens) != set(plan.sampled):
                 raise EngineError("update() needs one token for every sampled request")
+            context_limit = self.manager.max_context_tokens  # the same for every request
             for entry in plan.entries:
                 request = self.running[entry.request_id]
                 self.manager.commit(entry.request_id, len(entry.tokens))
@@ -255,7 +256,7 @@ class Scheduler:
                 if entry.request_id in tokens:
                     token = tokens[entry.request_id]
                     reason, stop = request.accept(token, self.eos_token_id, self.max_positions)
-                    if reason is None and request.computed + 1 > self.manager.max_context_tokens:
+                    if reason is None and request.computed + 1 > context_limit:
                         reason = FinishReason.LENGTH
                     if reason is not None:
                         self._finish(request, reason, new_tokens=(token,), stop=stop)
