@@ -6,23 +6,25 @@
 // the dependency wait, and keeps what follows the wait as short as it can be:
 //
 //   before the wait   every thread copies the weights it will multiply, all of them, into
-//                     shared-memory slots of its own with cp.async (up to 56 KB per CTA, four
-//                     CTAs per SM: the whole matrix of a GPT-2 XL product is in flight or
-//                     on chip when the rows arrive); bias
+//                     shared-memory slots of its own with cp.async (up to 56 KB per column
+//                     tile, about 220 KB per SM: the whole matrix of a GPT-2 XL product is in
+//                     flight or on chip when the rows arrive); bias
 //   after the wait    the rows' fragments straight from L1/L2 into registers (no staging, no
 //                     barrier), the old values of a residual sum, cp.async.wait_group,
 //                     mma.sync from the thread's own slots, a sum over the eight warps through
 //                     shared memory in warp order, (K split over a cluster: the partial sums
 //                     pushed into rank 0's shared memory, one cluster barrier,) epilogue, store.
 //
-// A CTA owns 16 output columns and a range of K; its eight warps take the 32-wide steps of
+// A CTA owns 16 output columns (32 as two tiles for wide products, see CT) and a range of K;
+// its eight warps take the 32-wide steps of
 // that range in turn (warp w: steps w, w + 8, ...). The tensor-core shape is m16n8k16 with the
 // weights as the 16-row operand and eight rows of A as the 8-column one. A lane's 16-byte
 // pieces are eight consecutive k of one weight row, used as the operands of two MMAs; the k
 // order inside a step is permuted the same way for both operands, which a sum over k does not
-// see. This is the legacy tensor path on purpose: at 8 rows the arithmetic is 0.1 % of the
-// time, and what counts is that a fragment needs no shared-memory layout, no descriptor and
-// no barrier. Products of more rows go to the tcgen05 kernels.
+// see. Nine to sixteen rows run as two row tiles, one after the other, over the same weights.
+// This is the legacy tensor path on purpose: at 8 rows the arithmetic is 0.1 % of the time,
+// and what counts is that a fragment needs no shared-memory layout, no descriptor and no
+// barrier. Products of more rows go to the tcgen05 kernels.
 //
 // The order of the sums is fixed (steps of a warp in order, warps in order, cluster ranks in
 // order) and does not depend on M or on which row of the step a token is.
@@ -34,7 +36,7 @@ namespace ayk {
 
 constexpr int ST_THREADS = 256;
 constexpr int ST_WARPS = ST_THREADS / 32;
-constexpr int ST_COLS = 16;        // output columns per CTA
+constexpr int ST_COLS = 16;        // output columns per column tile
 constexpr int ST_STEP_K = 32;      // k per step
 constexpr int ST_STEPS_PER_WARP = 7;
 constexpr int ST_MAX_STEPS = ST_WARPS * ST_STEPS_PER_WARP;  // per CTA: 56 KB of weights
