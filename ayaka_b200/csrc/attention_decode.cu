@@ -33,7 +33,7 @@ constexpr int DEC_THREADS = DEC_WARPS * 32;
 // Batches whose copies are in flight ahead of the arithmetic. Measured on a B200 inside a
 // decode layer (GPT-2 XL shapes, 768 keys): one batch ahead beats two and three at 8 and 64
 // rows (47 / 124 against 51 / 140 microseconds a layer) — a shallow queue is 32 KB of shared
-// memory per CTA, seven CTAs per SM, and the many resident warps hide more latency than a
+// memory per CTA, six CTAs per SM, and the many resident warps hide more latency than a
 // deep queue of few warps does. Filling both stages of the strip before the wait (and
 // requesting a batch's successor only once the batch is in registers) was slower too: 39.4
 // against 37.5 microseconds a layer at 8 rows, 129 against 113 at 64.
