@@ -384,8 +384,8 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
 
 def decode_splits(num_rows: int, num_heads: int, max_kv_len: int) -> int:
     """How many CTAs share one (request, head) of a decode step. Measured on a B200: the grid
-    should fill the GPU about once (six CTAs of this kernel are resident per SM, 888 in all;
-    the 1036 below is what measured best, a grid slightly larger than one round), a
+    should fill the GPU about once (the splits are cut for 1036 CTAs, tuned at GPT-2 XL's
+    shapes; six CTAs of this kernel are resident per SM, so that is a little over one round), a
     cluster merges up to 8 shares on chip, and a warp wants at least 32 keys."""
     fill = 1036 // max(1, num_rows * num_heads)
     enough_keys = max(1, max_kv_len // 128)
