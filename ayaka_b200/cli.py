@@ -11,7 +11,11 @@ error. Exit codes follow ``python/ayaka/entrypoints/console.py:34-41``: 0 ok, 1 
 3 model cannot be loaded, 4 model not found, 5 not enough memory, 6 engine failure, 130
 interrupted. Typed errors print one line, never a traceback.
 
-``python -m ayaka_b200 random CONFIG.json OUT`` writes a model folder with random weights.
+``python -m ayaka_b200 random CONFIG.json OUT`` writes a model folder with random weights;
+``python -m ayaka_b200 replay --model DIR --dtype D --out DIR --max-tokens N`` is the trace
+replay program (``bin/trace_run``); ``python -m ayaka_b200 info`` prints what this
+installation has, after the reference's ``ayaka info`` (``entrypoints/cli.py:212-219``):
+version, devices, architectures and parts it knows, compiler and compiled libraries.
 """
 
 from __future__ import annotations
@@ -71,6 +75,13 @@ def _parser() -> argparse.ArgumentParser:
     run.add_argument("-q", "--quiet", action="store_true", help="do not print the start-up line")
     run.add_argument("-v", "--verbose", action="count", default=0, help="log progress")
 
+    commands.add_parser(
+        "replay", add_help=False,
+        help="feed given token ids through a model step by step and write the logits "
+             "(the program bin/trace_run; `replay --help` lists its options)")
+    info = commands.add_parser(
+        "info", help="print the version, devices, architectures, parts and CUDA libraries")
+    info.add_argument("--output", choices=("text", "json"), default="text", help="text or json")
     rand = commands.add_parser("random", help="write a model folder with random weights")
     rand.add_argument("config", help="a config.json (the architecture's own keys)")
     rand.add_argument("out", help="folder to write config.json and model.safetensors into")
@@ -152,16 +163,81 @@ def _random(args: argparse.Namespace) -> int:
     return EXIT_OK
 
 
+def _info(args: argparse.Namespace) -> int:
+    import torch
+
+    import ayaka_b200
+    from ayaka_b200.kernels import build
+    from ayaka_b200.models.registry import supported_architectures
+    from ayaka_b200.parts.base import registered_kinds
+
+    import ayaka_b200.parts  # noqa: F401 - registers the built-in parts
+
+    devices = []
+    if torch.cuda.is_available():
+        for index in range(torch.cuda.device_count()):
+            properties = torch.cuda.get_device_properties(index)
+            devices.append({"index": index, "name": properties.name,
+                            "compute_capability": f"{properties.major}.{properties.minor}",
+                            "memory_gib": round(properties.total_memory / 2 ** 30, 1),
+                            "multiprocessors": properties.multi_processor_count})
+    folder = build.CSRC / "_build"
+    built = sorted(path.name for path in folder.glob("libayk_*.so")) if folder.is_dir() else []
+    report = {
+        "version": ayaka_b200.__version__,
+        "torch": torch.__version__,
+        "devices": devices,
+        "architectures": supported_architectures(),
+        "parts": {family: registered_kinds(family)
+                  for family in ("mixer", "feed_forward", "norm", "position", "block",
+                                 "embedding", "head")},
+        "nvcc": build._nvcc(),
+        "cuda_sources": build.library_names(),
+        "compiled_libraries": built,
+        "build_folder": str(folder),
+    }
+    if args.output == "json":
+        print(json.dumps(report, indent=1))
+        return EXIT_OK
+    print(f"ayaka_b200 {report['version']} (torch {report['torch']})")
+    if devices:
+        for device in devices:
+            print(f"device cuda:{device['index']}: {device['name']}, sm_"
+                  f"{device['compute_capability'].replace('.', '')}, {device['memory_gib']} GiB, "
+                  f"{device['multiprocessors']} SMs")
+    else:
+        print("devices: no CUDA device (this engine has no CPU path)")
+    print("architectures: " + ", ".join(report["architectures"]))
+    for family, kinds in report["parts"].items():
+        print(f"parts/{family}: " + (", ".join(kinds) or "-"))
+    print(f"nvcc: {report['nvcc'] or 'not found'}")
+    print(f"CUDA sources: {', '.join(report['cuda_sources'])}")
+    print(f"compiled libraries ({folder}): {len(built)}")
+    return EXIT_OK
+
+
 def main(argv: list[str] | None = None) -> int:
+    arguments = list(sys.argv[1:] if argv is None else argv)
+    if arguments[:1] == ["replay"]:  # its options are the replay program's own
+        from ayaka_b200.engine.replay import main as replay_main
+
+        try:
+            return replay_main(arguments[1:])
+        except SystemExit as stop:
+            return int(stop.code or 0)
+        except KeyboardInterrupt:
+            return EXIT_INTERRUPTED
     parser = _parser()
     try:
-        args = parser.parse_args(argv)
+        args = parser.parse_args(arguments)
     except SystemExit as stop:
         return int(stop.code or 0)
     if args.command is None:
         parser.print_help(sys.stderr)
         return EXIT_USAGE
     try:
+        if args.command == "info":
+            return _info(args)
         return _run(args) if args.command == "run" else _random(args)
     except KeyboardInterrupt:
         return EXIT_INTERRUPTED
