@@ -98,13 +98,6 @@ __device__ __forceinline__ void merge_state(float& m, float& l, float* acc, floa
   m = nm;
 }
 
-#ifdef AYK_DEC_TRACE
-__device__ long long dec_trace[64];
-#define DEC_MARK(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) dec_trace[i] = clock64(); } while (0)
-#else
-#define DEC_MARK(i)
-#endif
-
 // 8 consecutive elements as they lie in memory (16 bytes of bfloat16, 32 bytes of float32).
 template <typename T> struct Raw8;
 template <> struct Raw8<__nv_bfloat16> {
@@ -195,7 +188,6 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
   __shared__ float c_share[2 + 256];         // this CTA's (max, sum, weighted values)
   __shared__ int s_last;
 
-  DEC_MARK(0);
   pdl_launch_dependents();
   // Before the wait for the kernel ahead, only what no kernel of this step writes is touched:
   // the step's metadata (copied in before the step's first kernel) and the keys and values
@@ -241,7 +233,9 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
   int my_entry = 0;
   auto refill_table = [&](int from_page) {
     first_page = from_page;
-    const int last_page = k_hi > k_lo ? page_of(k_hi - 1) : from_page;
+    // (a warp whose share holds no key loads nothing: its first page may lie beyond the
+    // request's row of the table)
+    const int last_page = k_hi > k_lo ? page_of(k_hi - 1) : from_page - 1;
     my_entry = from_page + lane <= last_page ? table[from_page + lane] : 0;
   };
   refill_table(first_page);
@@ -300,7 +294,6 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
     }
     cp_async_commit_group();
   };
-  DEC_MARK(1);
   const int num_batches = k_hi > k_lo ? (k_hi - k_lo + STEP - 1) / STEP : 0;
   // The first batches start before the wait. This step's token (position pos, the last key of
   // the share that holds it, so in that share's last batch) is written during this step, by
@@ -381,7 +374,6 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
     }
   }
   cp_async_wait_group<0>();
-  DEC_MARK(2);
   // the key slots of the warp that share `sub` fold together
 #pragma unroll
   for (int o = TPK; o < 32; o <<= 1) {
@@ -399,7 +391,6 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
     for (int i = 0; i < 8; ++i) s_wacc[warp][lane][i] = acc[i];
   }
   __syncthreads();
-  DEC_MARK(4);
   if (clustered) dec_cluster_wait();  // every CTA of the cluster has started
   // fold the warps' shares, in warp order, into (max, sum, weighted values[head_dim]): into
   // c_share, or with a cluster straight into this CTA's row of rank 0's `recv`
@@ -466,22 +457,21 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
   if (splits == 1) {
     const float inv = 1.f / c_share[1];
     for (int d = tid; d < head_dim; d += DEC_THREADS) stf(dst + d, c_share[2 + d] * inv);
-    DEC_MARK(5);
     return;
   }
   // through scratch: every CTA stores its share; the last one to finish merges them
-  float* mine = partial + ((size_t)(row * num_heads + head) * splits + split) * (head_dim + 2);
+  float* mine = partial + (((size_t)row * num_heads + head) * splits + split) * (head_dim + 2);
   for (int d = tid; d < head_dim + 2; d += DEC_THREADS) mine[d] = c_share[d];
   __threadfence();
   __syncthreads();
   if (tid == 0) {
-    const int ticket = atomicAdd(&tickets[row * num_heads + head], 1);
+    const int ticket = atomicAdd(&tickets[(size_t)row * num_heads + head], 1);
     s_last = ticket == splits - 1;
   }
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  const float* shares = partial + (size_t)(row * num_heads + head) * splits * (head_dim + 2);
+  const float* shares = partial + ((size_t)row * num_heads + head) * splits * (head_dim + 2);
   float top = -INFINITY;
   for (int s = 0; s < splits; ++s) top = fmaxf(top, shares[s * (head_dim + 2)]);
   float denom = 0.f;
@@ -497,7 +487,7 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
     }
     stf(dst + d, sum / denom);
   }
-  if (tid == 0) tickets[row * num_heads + head] = 0;  // ready for the next launch
+  if (tid == 0) tickets[(size_t)row * num_heads + head] = 0;  // ready for the next launch
 }
 
 template <typename T, int TPK>
@@ -590,13 +580,6 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
 }  // namespace ayk
 
 AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
-
-#ifdef AYK_DEC_TRACE
-// Development aid: cycle stamps of CTA (0, 0, 0) of the last launch.
-AYK_API int ayk_decode_trace(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, ayk::dec_trace, sizeof(long long) * 64);
-}
-#endif
 
 // type: 0 = float32, 1 = bfloat16. Up to 8 splits need no scratch (pass null for `partial`
 // and `tickets`); with scratch, `partial` holds num_rows * num_heads * splits * (head_dim + 2)

@@ -20,7 +20,10 @@
  * What the caller must know:
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress,
  *     with that device current) and remembers it. Make that first call outside any stream
- *     capture.
+ *     capture, and before the host gives the device's free memory away: the driver may load
+ *     the library's device image, the array included, only at that first use, and that load
+ *     needs the 4.1 MiB to be free. If it fails the call returns the CUDA error and a later
+ *     call tries again.
  *   - All calls share the one array. It keeps whatever the last call left; the entry point
  *     zeroes the tickets it is about to use on the caller's stream before every launch, and
  *     every partial result is written before it is read, so stale contents never matter.

@@ -12,6 +12,7 @@
 #define AYK_BAD_ALIGNMENT (-2)  // a pointer or stride that breaks a vector or TMA rule
 #define AYK_TOO_LARGE (-3)      // beyond a stated maximum
 #define AYK_DRIVER (-4)         // a driver entry point is missing or failed
+#define AYK_NOT_TAKEN (-6)      // this entry point does not serve the case; nothing ran
 
 #define AYK_API extern "C" __attribute__((visibility("default")))
 

@@ -1355,7 +1355,7 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
 // above, of which the query columns go to `out` and the key and value columns (from q_width
 // on: kv_width of keys, then of values) of every row m go to the cache at slot slots[m] (see
 // KvScatter; a negative slot stores nothing) and *not* to `out`: the attention kernels for
-// prompt portions read them from the cache. Returns AYK_OK when it ran; 1 when this product
+// prompt portions read them from the cache. Returns AYK_OK when it ran; AYK_NOT_TAKEN when this product
 // cannot carry the store (few rows, a head size that is no multiple of 32, a query width that
 // is no multiple of 64, an output TMA cannot write): nothing ran then and the caller does the
 // product and the store on their own.
@@ -1374,7 +1374,7 @@ AYK_API int ayk_gemm_bf16_tc_kv(const void* a, int lda, const void* w, int ldw,
   if (M <= 64 || head_dim % 32 || q_width % 64 || ((uintptr_t)a % 16) || ((uintptr_t)w % 16) ||
       (lda % 8) || (ldw % 8) || ((uintptr_t)out % 16) || (ldo % 8) ||
       ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16)) {
-    return 1;
+    return AYK_NOT_TAKEN;
   }
   const KvScatter kv{slots, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, q_width, kv_width,
                      num_kv_heads, head_dim, page_size};
@@ -1399,6 +1399,6 @@ AYK_API int ayk_gemm_bf16_tc_kv(const void* a, int lda, const void* w, int ldw,
       return launch_gemm_tc_persistent<256, 4, true>(a, lda, w, ldw, bias, out, ldo, M, N, K,
                                                      ACT_NONE, OUT_BF16, status, s, kv);
     default:
-      return 1;
+      return AYK_NOT_TAKEN;
   }
 }

@@ -104,12 +104,13 @@ class _Launch:
     """A step that was launched: where its result arrives and what it ran."""
 
     __slots__ = ("bucket", "ids", "positions", "rows", "out_host", "event", "count", "pick",
-                 "exact")
+                 "exact", "slot")
 
     def __init__(self, bucket: _Bucket, ids: tuple[str, ...], positions: list[int],
-                 rows: list[SampleRow], out_host: torch.Tensor, event: torch.cuda.Event) -> None:
+                 rows: list[SampleRow], out_host: torch.Tensor, event: torch.cuda.Event,
+                 slot: int) -> None:
         self.bucket, self.ids, self.positions, self.rows = bucket, ids, positions, rows
-        self.out_host, self.event = out_host, event
+        self.out_host, self.event, self.slot = out_host, event, slot
         self.count = len(ids)
         self.pick = list(range(self.count))  # the launch's row of each entry of its plan
         self.exact = True  # every row of the launch belongs to an entry, in plan order
@@ -152,6 +153,7 @@ class DecodeGraphs:
         self.sizes = tuple(sorted(set(min(size, limit) for size in buckets)))
         self._buckets: dict[int, _Bucket] = {}
         self._ahead: _Launch | None = None
+        self.flags = core.runner.flags
         self.replays = 0
         self.adopted = 0  # launches made ahead that the next plan took over
         self.dropped = 0  # launches made ahead that the next plan did not fit
@@ -221,8 +223,10 @@ class DecodeGraphs:
             self.dropped += 1
 
     def finish(self, launch: _Launch) -> list[int]:
-        """Wait for a launch and return the chosen id of each of its plan's entries."""
+        """Wait for a launch and return the chosen id of each of its plan's entries; raises
+        :class:`BackendError` if a kernel up to and including this launch gave up."""
         launch.event.synchronize()
+        self.flags.check(launch.slot)
         chosen = launch.out_host.tolist()
         return [chosen[index] for index in launch.pick]
 
@@ -246,10 +250,11 @@ class DecodeGraphs:
             self._capture(bucket, greedy)  # (runs the step it captures: the same stores)
         bucket.graphs[greedy].replay()
         bucket.out_host[slot].copy_(bucket.out, non_blocking=True)
+        self.flags.snapshot(slot)
         event = bucket.events[slot]
         event.record(torch.cuda.current_stream(self.core.device))
         self.replays += 1
-        return _Launch(bucket, ids, positions, rows, bucket.out_host[slot], event)
+        return _Launch(bucket, ids, positions, rows, bucket.out_host[slot], event, slot)
 
     def _capture(self, bucket: _Bucket, greedy: bool) -> None:
         core = self.core

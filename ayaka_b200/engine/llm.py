@@ -43,7 +43,7 @@ class LLM:
             core.manager, max_running=config.max_running,
             max_tokens_per_step=config.max_tokens_per_step, max_waiting=config.max_waiting,
             max_positions=spec.max_positions, eos_token_id=spec.eos_token_id)
-        self.sampler = Sampler(max(config.max_running, 1), core.device)
+        self.sampler = Sampler(max(config.max_running, 1), core.device, core.runner.flags)
         self._counter = 0
         self._pending: dict[str, deque[RequestEvent]] = {}
         self._requests: dict[str, object] = {}
@@ -92,19 +92,28 @@ class LLM:
             raise
         tokens: dict[str, list[int]] = {request_id: [] for request_id in ids}
         final: dict[str, RequestEvent] = {}
-        while len(final) < len(ids):
+        try:
+            while len(final) < len(ids):
+                for request_id in ids:
+                    queue = self._pending.get(request_id)
+                    while queue:
+                        event = queue.popleft()
+                        tokens[request_id].extend(event.tokens)
+                        if event.finish_reason is not None:
+                            final[request_id] = event
+                if len(final) == len(ids):
+                    break
+                if not self.scheduler.has_unfinished:
+                    raise EngineError("requests ended without a final event")
+                self._advance()
+        except BaseException:
+            # nothing of this call is left running or remembered
             for request_id in ids:
-                queue = self._pending.get(request_id)
-                while queue:
-                    event = queue.popleft()
-                    tokens[request_id].extend(event.tokens)
-                    if event.finish_reason is not None:
-                        final[request_id] = event
-            if len(final) == len(ids):
-                break
-            if not self.scheduler.has_unfinished:
-                raise EngineError("requests ended without a final event")
-            self._advance()
+                if request_id not in final:
+                    self.scheduler.abort(request_id)
+                self._forget(request_id)
+            self._dispatch(self.scheduler.take_events())
+            raise
         outputs = [self._output(request_id, tuple(tokens[request_id]), final[request_id], True)
                    for request_id in ids]
         for request_id in ids:
@@ -190,11 +199,21 @@ class LLM:
                     graphs.drop_ahead()
                 logits = self.core.runner.run(plan.entries)
                 picked = self.sampler.sample(logits, rows) if plan.sampled else []
-        except BackendError as error:
-            # a refused step ends its requests; the engine goes on (reference:
-            # python/ayaka/execution/runner.py:227-231)
-            self._dispatch(scheduler.update(plan, None, error=str(error)))
+        except Exception as error:
+            # A step that a kernel refused, or whose kernels gave up a wait, ends its requests
+            # and the engine goes on (reference: python/ayaka/execution/runner.py:227-231).
+            # Whatever else went wrong between schedule() and update() must still close the
+            # step, or the scheduler stays "in flight" and the requests keep their pages.
+            if self.graphs is not None:
+                try:
+                    self.graphs.drop_ahead()
+                except Exception:  # noqa: BLE001 - the first error is the one to report
+                    pass
+            text = str(error) if isinstance(error, AyakaError) else repr(error)
+            self._dispatch(scheduler.update(plan, None, error=text))
             self.core.manager.check_integrity()
+            if not isinstance(error, AyakaError):
+                raise
             return
         self._dispatch(scheduler.update(plan, dict(zip(plan.sampled, picked))))
 

@@ -23,6 +23,7 @@ import torch
 from ayaka_b200.cache.manager import CacheManager
 from ayaka_b200.cache.storage import CacheStorage
 from ayaka_b200.errors import CapacityError, EngineError, InvalidRequestError
+from ayaka_b200.kernels.flags import FlagReader
 from ayaka_b200.models.decoder import DecoderModel
 from ayaka_b200.parts.context import GroupStep, StepContext, Workspace
 
@@ -68,7 +69,9 @@ class ModelRunner:
         self._staging = [torch.empty(capacity, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._turn = 0
         self._device_meta = torch.zeros(capacity, dtype=torch.int32, device=device)
-        self._bad_index = torch.zeros(1, dtype=torch.int32, device=device)
+        #: the device's status word and bad-index word, read wherever a step synchronises
+        self.flags = FlagReader(device)
+        self._bad_index = self.flags.flags[1:2]
         self.steps_run = 0
 
     # ------------------------------------------------------------------------------------
@@ -85,11 +88,10 @@ class ModelRunner:
         return logits
 
     def check_device_flags(self) -> None:
-        """Raise if a kernel flagged an id outside its table since the last check (reads one
-        int from the device; tests and the replay program call it)."""
-        if int(self._bad_index.item()):
-            self._bad_index.zero_()
-            raise EngineError("a token or position id was outside its embedding table")
+        """Raise :class:`BackendError` if, since the last check, a kernel gave up a bounded
+        wait or flagged an id outside its table (a synchronising read of two ints; the
+        replay program and tests call it, generation reads the words with its token ids)."""
+        self.flags.read_now()
 
     # ------------------------------------------------------------------------------------
     def prepare(self, entries: Sequence[StepEntry]) -> tuple[StepContext, torch.Tensor, int]:

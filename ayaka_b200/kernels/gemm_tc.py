@@ -7,11 +7,13 @@ from ctypes import c_int, c_void_p
 import torch
 
 from ayaka_b200.errors import BackendError
+from ayaka_b200.kernels import flags
 from ayaka_b200.kernels.lib import check, entry, raw_stream
 
 __all__ = ["check_status", "linear_bf16", "linear_bf16_kv", "status_word"]
 
-_status: dict[int, torch.Tensor] = {}
+#: what ``ayk_gemm_bf16_tc_kv`` returns when it does not serve the case (nothing ran)
+NOT_TAKEN = -6
 
 #: tile width (columns of the output per CTA) the next calls use; 0 lets the library choose.
 TILE_N = 0
@@ -19,12 +21,7 @@ TILE_N = 0
 
 def status_word(device: torch.device) -> torch.Tensor:
     """One int32 per device that a kernel sets when a bounded wait ran out."""
-    index = device.index if device.index is not None else torch.cuda.current_device()
-    word = _status.get(index)
-    if word is None:
-        word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", index))
-        _status[index] = word
-    return word
+    return flags.status_word(device)
 
 
 def check_status(device: torch.device) -> None:
@@ -84,7 +81,7 @@ def linear_bf16_kv(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | N
                 c_int(kv_heads), c_int(head_dim), c_int(page_size),
                 c_void_p(status_word(a.device).data_ptr()),
                 c_void_p(raw_stream()))
-    if status == 1:
+    if status == NOT_TAKEN:
         return False
     ops._launches += 1
     check(status, "linear with key/value store (tcgen05)")

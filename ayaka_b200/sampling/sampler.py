@@ -14,6 +14,7 @@ import numpy as np
 import torch
 
 from ayaka_b200.kernels import ops
+from ayaka_b200.kernels.flags import FlagReader
 from ayaka_b200.sampling.params import SamplingParams
 
 __all__ = ["SampleRow", "Sampler"]
@@ -41,9 +42,12 @@ class SampleRow:
 
 
 class Sampler:
-    def __init__(self, max_rows: int, device: torch.device) -> None:
+    def __init__(self, max_rows: int, device: torch.device,
+                 flags: FlagReader | None = None) -> None:
         self.max_rows = max_rows
         self.device = device
+        #: the kernels' failure words, copied beside the ids and checked after the wait
+        self.flags = flags
         # layout of the staging buffer, in 4-byte words per row: temperature, top_p, min_p
         # (float32), top_k (int32), then seeds and positions (int64, two words each)
         self._host = torch.empty(8 * max_rows, dtype=torch.int32).pin_memory()
@@ -145,5 +149,9 @@ class Sampler:
                        dev[4 * n:6 * n].view(torch.int64), dev[6 * n:8 * n].view(torch.int64),
                        self._out, rows=count)
         self._out_host[:count].copy_(self._out[:count], non_blocking=True)
+        if self.flags is not None:
+            self.flags.snapshot(0)
         torch.cuda.current_stream(self.device).synchronize()
+        if self.flags is not None:
+            self.flags.check(0)  # raises BackendError: the ids of a failed step are not used
         return self._out_host[:count].tolist()

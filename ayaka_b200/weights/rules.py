@@ -10,10 +10,30 @@ __all__ = ["RandomInit", "WeightRule", "WeightRules"]
 
 @dataclass(frozen=True, slots=True)
 class WeightRule:
-    """One checkpoint tensor: the parameter it fills and whether it is stored transposed."""
+    """Where one checkpoint tensor goes.
+
+    The simplest rule fills a whole parameter, transposed on the way if the checkpoint stores
+    it so. A parameter may also be *stacked* from several stored tensors (separate query, key
+    and value matrices into one fused matrix; two feed-forward inputs into one), and a stored
+    tensor may give only a *slice* of itself, or feed several parameters (a tuple of rules
+    under one name). The reference describes the same with ``stored_parts``
+    (``python/ayaka/models/base.py:169-177, 202-263``).
+
+    Attributes:
+        parameter: the model parameter this tensor (or slice) lands in.
+        transposed: the checkpoint stores the transpose (Conv1D ``[in, out]``).
+        dim: the dimension of the parameter along which ``offset`` and ``take`` count.
+        offset: where along ``dim`` of the parameter the piece starts; ``None``: the piece is
+            the whole parameter.
+        take: ``(start, stop)`` along ``dim`` of the stored tensor (after transposition): only
+            that slice is used; ``None``: all of it.
+    """
 
     parameter: str
     transposed: bool = False
+    dim: int = 0
+    offset: int | None = None
+    take: tuple[int, int] | None = None
 
 
 @dataclass(frozen=True, slots=True)
@@ -27,10 +47,15 @@ class WeightRules:
         optional_prefixes: a name may start with one of these; it is stripped first.
     """
 
-    rules: dict[str, WeightRule]
+    rules: dict[str, WeightRule | tuple[WeightRule, ...]]
     ignore: tuple[str, ...] = ()
     optional_prefixes: tuple[str, ...] = ()
     _compiled: list[re.Pattern[str]] = field(default_factory=list, compare=False, repr=False)
+
+    def of(self, stripped: str) -> tuple[WeightRule, ...]:
+        """The rules of one checkpoint name (one stored tensor may feed several parameters)."""
+        found = self.rules[stripped]
+        return found if isinstance(found, tuple) else (found,)
 
     def strip(self, name: str) -> str:
         for prefix in self.optional_prefixes:

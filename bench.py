@@ -41,6 +41,7 @@ XL = {
     "tie_word_embeddings": True,
 }
 PROMPT = 512
+METRIC = "decode tok/s at batch 8 (GPT-2 XL, bf16, context 1024)"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -304,13 +305,25 @@ def workload_run(which: str) -> int:
     return 0
 
 
-def reference_arm() -> int:
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "gityuko-hb/ayaka cannot be installed offline here: its build backend "
-                       "(hatchling) is neither installed nor in the wheelhouse, and it requires "
-                       "Python >= 3.13 (this image has 3.12)"}))
-    return 0
+def config_record(cfg: dict, mean_context: float, prompt_len: int = PROMPT) -> dict:
+    """The ``config`` of the line: every size, flat; the same for both arms."""
+    return {
+        "model": "gpt2-xl", "n_layer": cfg["n_layer"], "n_layer_full": XL["n_layer"],
+        "n_embd": cfg["n_embd"], "n_head": cfg["n_head"], "n_inner": cfg["n_inner"],
+        "vocab_size": cfg["vocab_size"], "n_positions": cfg["n_positions"],
+        "global_batch": 8, "seq_len": cfg["n_positions"], "prompt_len": prompt_len,
+        "mean_context": round(mean_context, 1), "page_size": 16,
+        "parallelism": "single-gpu", "weights": "random bf16 seed 0",
+        "l2": "inputs larger than L2 (3.1 GB of weights per step)", "cuda_graph": True,
+    }
+
+
+def reference_arm(args: argparse.Namespace) -> int:
+    """The same measurement on the unmodified reference (``baseline/reference_arm.py``)."""
+    sys.path.insert(0, str(ROOT / "baseline"))
+    import reference_arm as arm
+
+    return arm.run(args, {**XL, "n_layer": args.layers})
 
 
 def main() -> int:
@@ -328,11 +341,11 @@ def main() -> int:
                              "(GPT-2 small with 64 ragged requests; GPT-2 large with prompt "
                              "portions beside 32 decoding requests)")
     args = parser.parse_args()
-    if args.impl == "reference":
-        return reference_arm()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.impl == "reference":
+        return reference_arm(args)
     import torch
 
     if not torch.cuda.is_available():
@@ -366,19 +379,12 @@ def main() -> int:
     flops = prefill_flops(cfg, layers, 2, cfg["n_positions"])
     value = 8 * 1000.0 / main_run["ms"]
     line = {
-        "metric": "decode tok/s at batch 8 (GPT-2 XL, bf16, context 1024)",
+        "metric": METRIC,
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": round(main_run["ms"], 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
-        "config": {
-            "model": "gpt2-xl", "n_layer": layers, "n_layer_full": 48, "n_embd": 1600,
-            "n_head": 25, "n_inner": 6400, "vocab_size": 50257, "n_positions": 1024,
-            "global_batch": 8, "seq_len": 1024, "prompt_len": PROMPT,
-            "mean_context": round(main_run["mean_context"], 1), "page_size": 16,
-            "parallelism": "single-gpu", "weights": "random bf16 seed 0",
-            "l2": "inputs larger than L2 (3.1 GB of weights per step)", "cuda_graph": True,
-        },
+        "config": config_record(cfg, main_run["mean_context"]),
         "prefill": {"value": round(prefill["tokens"] * 1000.0 / prefill["ms"], 1),
                     "tokens": prefill["tokens"], "ms": round(prefill["ms"], 3),
                     "frac": round(flops / (prefill["ms"] * 1e-3) / (peak["bf16_tflops"] * 1e12),
