@@ -44,7 +44,7 @@ TINY_D = {
     "tie_word_embeddings": True,
 }
 
-#: BASELINE-style initialisations (small deviations) and a "loud" one for sensitive tests.
+#: Initialisations with the small deviations a trained checkpoint has, and a "loud" one for sensitive tests.
 INIT_A = RandomInit(weight_std=0.02, scale_residual_projections=True, bias_std=0.0, norm_std=0.0)
 INIT_B = RandomInit(weight_std=0.02, scale_residual_projections=False, bias_std=0.02,
                     norm_std=0.02)

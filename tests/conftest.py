@@ -29,15 +29,13 @@ def pytest_collection_modifyitems(config: pytest.Config, items: list[pytest.Item
             item.add_marker(skip)
 
 
-@pytest.fixture(autouse=True, scope="session")
-def _bf16_gemm_choice():
-    """``AYK_TEST_BF16_GEMM=simt`` runs the bfloat16 engine tests on the CUDA-core matrix
-    product (a development aid for telling a tensor-core fault from a cache fault)."""
-    import os
-
-    choice = os.environ.get("AYK_TEST_BF16_GEMM")
-    if choice:
-        from ayaka_b200.kernels import ops
-
-        ops.BF16_GEMM = choice
-    yield
+def pytest_terminal_summary(terminalreporter: pytest.TerminalReporter) -> None:
+    """The largest engine-against-plain errors the run measured, per kind of test."""
+    try:
+        import engine_support
+    except ImportError:
+        return
+    if engine_support.MEASURED:
+        terminalreporter.write_sep("-", "largest errors, as a fraction of the largest |logit|")
+        for name, value in sorted(engine_support.MEASURED.items()):
+            terminalreporter.write_line(f"{name}\t{value:.2e}")

@@ -15,13 +15,12 @@ from ayaka_b200.weights.random_init import random_state, write_random_model
 PAGE = 16
 
 
+#: label -> largest error seen, as a fraction of the largest |logit| (printed after the run)
+MEASURED: dict[str, float] = {}
+
+
 def log_error(name: str, value: float) -> None:
-    """Append a measured error to the file the environment variable ``AYK_ERROR_LOG`` names
-    (nothing is written when it is not set)."""
-    target = os.environ.get("AYK_ERROR_LOG")
-    if target:
-        with open(target, "a", encoding="utf-8") as handle:
-            handle.write(f"{name}\t{value:.3e}\n")
+    MEASURED[name] = max(MEASURED.get(name, 0.0), value)
 
 
 def make_model(folder: Path, config: dict, seed: int, init, dtype: str) -> tuple[Path, dict]:
@@ -175,6 +174,37 @@ def plain_logits(state: dict, config: dict, sequences: dict[str, list[int]]
             for rid, tokens in sequences.items()}
 
 
+def rounded_logits(state: dict, config: dict, sequences: dict[str, list[int]],
+                   round_weights: bool = False) -> dict[str, torch.Tensor]:
+    """What a bfloat16 engine should give: the plain implementation with bfloat16 roundings
+    between its parts (``plain_rounded.py``), computed in float64."""
+    import plain_rounded
+
+    wide = plain.cast_state(state, torch.float64)
+    return {rid: plain_rounded.logits(wide, config, torch.tensor(tokens), round_weights).float()
+            for rid, tokens in sequences.items()}
+
+
+# The bfloat16 engine against the plain implementation that rounds where the engine does
+# (``plain_rounded.py``). What is left between the two is not a fault: the tensor-core
+# attention kernels round their attention weights exp(s - reference) to bfloat16 relative to
+# a running reference, so every weight is rounded differently from any oracle's (that alone
+# moves single logits of these loud models by 6e-3 to 8e-3 of the scale and a row's
+# root-mean-square by 1.3e-3: ``test_plain.py`` measures it on the plain implementation
+# itself); a rounding that falls on the other side of a tie is rare but lands on a sensitive
+# key now and then; the activation's tanh is the hardware's approximation. Rare large single
+# errors and a small error everywhere are told apart: every position's root-mean-square
+# error over the vocabulary must stay within 5e-3 of the logit scale (measured: 1.1e-3 to
+# 3.1e-3), which a fault that moves a row by one per cent breaks, and no single logit may
+# be off by more than 1.5e-2 (measured: up to 1.0e-2), half of what the float64 comparison
+# has to allow. Decode-only runs have no rounded attention weights and get tighter limits
+# (measured 4.2e-3 and 1.3e-3).
+ROUNDED_TOLERANCE = (1.5e-2, 1.5e-2)
+ROUNDED_ROW_RMS = 5e-3
+DECODE_ROUNDED_TOLERANCE = (6e-3, 6e-3)
+DECODE_ROUNDED_ROW_RMS = 2.5e-3
+
+
 def tolerance(dtype: str) -> tuple[float, float]:
     """(rtol, atol relative to the largest |logit|) of engine vs plain implementation.
 
@@ -186,10 +216,15 @@ def tolerance(dtype: str) -> tuple[float, float]:
 
 
 def assert_logits_close(got: dict[str, torch.Tensor], expected: dict[str, torch.Tensor],
-                        dtype: str, label: str) -> None:
-    rtol, atol_rel = tolerance(dtype)
+                        dtype: str, label: str, limits: tuple[float, float] | None = None,
+                        page: int = PAGE, row_rms: float | None = None) -> None:
+    """Every logit within ``atol`` (a fraction of the request's largest |logit|) plus ``rtol``
+    of its own size; with ``row_rms`` also every position's root-mean-square error over the
+    vocabulary within that fraction of the scale (a fault that moves a whole row a little
+    shows there long before it shows in the largest single error)."""
+    rtol, atol_rel = limits or tolerance(dtype)
     assert set(got) == set(expected)
-    worst = 0.0
+    worst, worst_rms = 0.0, 0.0
     for rid, want in expected.items():
         have = got[rid]
         assert have.shape == want.shape, (rid, have.shape, want.shape)
@@ -197,14 +232,21 @@ def assert_logits_close(got: dict[str, torch.Tensor], expected: dict[str, torch.
         scale = float(want.abs().max())
         error = (have - want).abs()
         worst = max(worst, float(error.max()) / scale)
-        bad = error > atol_rel * scale + rtol * want.abs()
+        rms = (error * error).mean(dim=1).sqrt() / scale
+        worst_rms = max(worst_rms, float(rms.max()))
+        bad = (error > atol_rel * scale + rtol * want.abs()).any(dim=1)
+        if row_rms is not None:
+            bad = bad | (rms > row_rms)
         if bad.any():
-            first = int(torch.nonzero(bad.any(dim=1))[0])
+            first = int(torch.nonzero(bad)[0])
             raise AssertionError(
                 f"{label}: request {rid} first differs at position {first} "
-                f"(page {first // PAGE}, slot {first % PAGE}): max error "
-                f"{float(error[first].max()):.3e} of scale {scale:.3e}")
-    log_error(f"{label}/{dtype}", worst)
+                f"(page {first // page}, slot {first % page}): max error "
+                f"{float(error[first].max()):.3e}, rms {float(rms[first]) * scale:.3e} of scale "
+                f"{scale:.3e}")
+    suffix = "/rounded-oracle" if limits else ""
+    log_error(f"{label}/{dtype}{suffix}", worst)
+    log_error(f"{label}/{dtype}{suffix}/row-rms", worst_rms)
 
 
 def write_trace(path: Path, steps: list[dict]) -> None:

@@ -99,3 +99,27 @@ def test_sampling_oracle() -> None:
     assert plain.sample_token(row, 1.0, 0.999999, top_k=2) == 2
     assert plain.sample_token(row, 1.0, 0.999999, top_p=0.5) == 2
     assert plain.sample_token(row, 1.0, 0.999999, min_p=0.3) == 4
+
+
+def test_bfloat16_attention_weights_alone_move_the_logits_by_this_much():
+    """The noise floor of every bfloat16 comparison. A tensor-core attention kernel rounds
+    its weights exp(s - reference) to bfloat16, and the reference is whatever running maximum
+    the kernel holds at that block; two valid kernels therefore round every weight
+    differently. Here the plain implementation with bfloat16 roundings runs twice, with the
+    reference moved by a fraction of a bit: the logits of the loud tiny model A move by
+    several thousandths of their scale at single places and by about a thousandth in a
+    row's root-mean-square. The engine tests' limits against this oracle stand on these
+    figures."""
+    import plain_rounded
+
+    case = CASES["golden_a"]
+    state = plain.cast_state(case_state(case, "bfloat16"), torch.float64)
+    config = case_config(case)
+    tokens = torch.tensor(case_sequences({**case, "lengths": (128,)})[0])
+    first = plain_rounded.logits(state, config, tokens, round_weights=True)
+    second = plain_rounded.logits(state, config, tokens, round_weights=True, reference_shift=0.37)
+    scale = float(first.abs().max())
+    largest = float((first - second).abs().max()) / scale
+    row_rms = float(((first - second) ** 2).mean(dim=1).sqrt().median()) / scale
+    assert 2e-3 < largest < 1.2e-2, largest
+    assert 3e-4 < row_rms < 3e-3, row_rms
