@@ -156,6 +156,24 @@ inline int launch_kernel_x(void (*kernel)(KArgs...), dim3 grid, dim3 block, size
   return launch_kernel_dims(kernel, grid, block, smem, stream, cluster_x, 1, args...);
 }
 
+// Streaming multiprocessors of the current device (asked once). Grid sizes and tile choices
+// are multiples of this, never a number of one GPU model; if the query fails the answer is
+// 1, which only makes the choices conservative.
+inline int sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int device = 0, found = 0;
+    if (cudaGetDevice(&device) == cudaSuccess &&
+        cudaDeviceGetAttribute(&found, cudaDevAttrMultiProcessorCount, device) == cudaSuccess &&
+        found > 0) {
+      count = found;
+    } else {
+      return 1;
+    }
+  }
+  return count;
+}
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? AYK_OK : (int)e;

@@ -259,18 +259,7 @@ inline int stream_splits(int M, int K) {
 #define AYK_STREAM_WIDE_FROM 4096
 #endif
 
-inline int stream_sms() {
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess ||
-        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device) !=
-            cudaSuccess) {
-      num_sms = 148;
-    }
-  }
-  return num_sms;
-}
+inline int stream_sms() { return sm_count(); }
 // Whether one column tile per CTA fits the SMs in one round.
 inline bool stream_one_round(int N) { return (N + ST_COLS - 1) / ST_COLS <= 4 * stream_sms(); }
 

@@ -1213,8 +1213,9 @@ inline int pick_splits(int tile_n, int N, int M) {
   // measured on GPT-2 XL's shapes: with more than 16 rows the cluster reduction of a
   // [32, 128] or [64, 128] tile costs more than it buys unless the tiles are very few
   if (M > 16) return tiles >= 32 ? 1 : 8;
+  // as many K splits as still leave two CTAs' worth of tiles per SM
   int splits = 1;
-  while (splits < 8 && tiles * splits * 2 <= 296) splits <<= 1;
+  while (splits < 8 && tiles * splits * 2 <= 2 * sm_count()) splits <<= 1;
   return splits;
 }
 
@@ -1222,15 +1223,7 @@ inline int pick_splits(int tile_n, int N, int M) {
 inline int choose_tile(int M, int N) {
   // measured at GPT-2 XL's shapes: with more 128 x 256 tiles than SMs the persistent kernel
   // wins (its epilogues hide under the next tile's main loop); with fewer, one tile per CTA
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int device = 0;
-    if (cudaGetDevice(&device) != cudaSuccess ||
-        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, device) !=
-            cudaSuccess) {
-      num_sms = 148;
-    }
-  }
+  const int num_sms = sm_count();
   // tile width 256, 192 or 128: the one with the least (rounds over the SMs) x (time of a
   // round). Measured at K = 1600: a round of 256-wide tiles takes only 7 % longer than one
   // of 192-wide tiles (9.8 against 9.2 microseconds), i.e. about (width + 768) units, so

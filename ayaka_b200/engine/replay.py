@@ -15,8 +15,6 @@ from pathlib import Path
 
 __all__ = ["main"]
 
-MAX_LIVE = 4
-
 
 def main(argv: list[str] | None = None) -> int:
     parser = argparse.ArgumentParser(prog="trace_run", description=__doc__)
@@ -27,6 +25,8 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time")
     parser.add_argument("--block-size", type=int, default=16, help="tokens per cache page (16)")
+    parser.add_argument("--max-running", type=int, default=4,
+                        help="most requests live at a time: rows of the block table (4)")
     parser.add_argument("--max-tokens-per-step", type=int, default=None,
                         help="largest step; default: --max-tokens")
     args = parser.parse_args(argv)
@@ -46,7 +46,7 @@ def main(argv: list[str] | None = None) -> int:
     try:
         config = EngineConfig(
             model=args.model, dtype=args.dtype, block_size=page, num_blocks=num_blocks,
-            max_running=min(MAX_LIVE, num_blocks - 1),
+            max_running=max(1, min(args.max_running, num_blocks - 1)),
             max_tokens_per_step=max(args.max_tokens_per_step or args.max_tokens, page))
         core = EngineCore.from_config(config)
     except AyakaError as error:

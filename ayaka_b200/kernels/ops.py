@@ -8,6 +8,8 @@ library or a refused argument raises :class:`~ayaka_b200.errors.BackendError`.
 
 from __future__ import annotations
 
+import contextlib
+from collections.abc import Iterator
 from ctypes import c_float, c_int, c_void_p
 
 import torch
@@ -25,12 +27,15 @@ __all__ = [
     "embed_rows",
     "kv_store",
     "launch_count",
+    "leaving_out",
     "layer_norm",
     "linear",
     "linear_normed",
     "logits_adjust",
     "sample",
     "set_pdl",
+    "sm_count",
+    "timed",
 ]
 
 ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2}
@@ -42,6 +47,62 @@ BF16_GEMM = "tcgen05"
 
 
 _launches = 0
+
+#: Kernel classes that launch nothing while a measurement runs; empty in normal use. A
+#: class is an operation's name, for matrix products with the weight's shape
+#: (``"linear:4800x1600"``). ``bench.py`` times a step with and without each class inside
+#: the same chain of dependent launches, which is what a kernel costs there; a step with a
+#: class left out computes nothing meaningful.
+_left_out: frozenset[str] = frozenset()
+
+
+@contextlib.contextmanager
+def leaving_out(*classes: str) -> Iterator[None]:
+    """Within the block the named kernel classes are not launched (for measurements only)."""
+    global _left_out
+    before = _left_out
+    _left_out = before | frozenset(classes)
+    try:
+        yield
+    finally:
+        _left_out = before
+
+
+_TIMED = ("embed_rows", "layer_norm", "linear", "linear_kv", "kv_store", "attention",
+          "attention_prefill", "attention_decode", "argmax", "sample")
+
+
+@contextlib.contextmanager
+def timed() -> Iterator[dict[str, list[tuple[torch.cuda.Event, torch.cuda.Event]]]]:
+    """Within the block every launch through this module is bracketed by two CUDA events,
+    gathered per kernel class (see ``leaving_out`` for the names); after a synchronisation
+    ``start.elapsed_time(stop)`` of each pair is that kernel's own duration. The events keep
+    a kernel from starting under its predecessor's tail, so this suits steps of large
+    kernels (prompt portions), not decode chains. For measurements only."""
+    module = globals()
+    originals = {name: module[name] for name in _TIMED}
+    record: dict[str, list[tuple[torch.cuda.Event, torch.cuda.Event]]] = {}
+
+    def wrap(name: str, function):  # noqa: ANN001, ANN202
+        def wrapped(*args, **kwargs):  # noqa: ANN002, ANN003, ANN202
+            klass = name
+            if name in ("linear", "linear_kv"):
+                klass = f"linear:{args[1].shape[0]}x{args[1].shape[1]}"
+            start = torch.cuda.Event(enable_timing=True)
+            stop = torch.cuda.Event(enable_timing=True)
+            start.record()
+            result = function(*args, **kwargs)
+            stop.record()
+            record.setdefault(klass, []).append((start, stop))
+            return result
+        return wrapped
+
+    for name, function in originals.items():
+        module[name] = wrap(name, function)
+    try:
+        yield record
+    finally:
+        module.update(originals)
 
 
 def set_pdl(enabled: bool) -> None:
@@ -95,6 +156,8 @@ def embed_rows(table: torch.Tensor, index: torch.Tensor, out: torch.Tensor, *,
     its table.
     """
     op = "embed_rows"
+    if _left_out and op in _left_out:
+        return
     _need(op, "table", table, ndim=2)
     _need(op, "index", index, torch.int32, 1)
     _need(op, "out", out, torch.float32, 2)
@@ -130,6 +193,8 @@ def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor | None, 
     number of output rows (default: all of ``rows`` or of ``x``).
     """
     op = "layer_norm"
+    if _left_out and op in _left_out:
+        return
     _need(op, "x", x, torch.float32, 2)
     _need(op, "gamma", gamma, torch.float32, 1)
     if beta is not None:
@@ -166,6 +231,8 @@ def linear(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, out
     tensor cores unless ``kernel="simt"``.
     """
     op = "linear"
+    if _left_out and f"linear:{weight.shape[0]}x{weight.shape[1]}" in _left_out:
+        return
     _need(op, "a", a, ndim=2)
     _need(op, "weight", weight, a.dtype, 2)
     _need(op, "out", out, ndim=2)
@@ -213,6 +280,8 @@ def linear_kv(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
     done nothing, when that cannot be had (float32, few rows, sizes the kernel does not
     take): the caller then runs :func:`linear` and :func:`kv_store`."""
     op = "linear_kv"
+    if _left_out and f"linear:{weight.shape[0]}x{weight.shape[1]}" in _left_out:
+        return True
     if a.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or BF16_GEMM != "tcgen05":
         return False
     _need(op, "a", a, torch.bfloat16, 2)
@@ -264,6 +333,8 @@ def kv_store(k: torch.Tensor, v: torch.Tensor, slot_mapping: torch.Tensor,
     are column ranges of one projection output).
     """
     op = "kv_store"
+    if _left_out and op in _left_out:
+        return
     _need(op, "k", k, ndim=2)
     _need(op, "v", v, k.dtype, 2)
     _need(op, "slot_mapping", slot_mapping, torch.int32, 1)
@@ -295,6 +366,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
     The keys of the step's own rows must already be stored.
     """
     op = "attention"
+    if _left_out and op in _left_out:
+        return
     _need(op, "q", q, ndim=2)
     _need(op, "out", out, q.dtype, 2)
     _need(op, "k_pages", k_pages, q.dtype, 4)
@@ -337,6 +410,8 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     sizes on a warp-level kernel compiled for the head size (``kernel`` forces one of them).
     """
     op = "attention_prefill"
+    if _left_out and op in _left_out:
+        return
     _need(op, "q", q, torch.bfloat16, 2)
     _need(op, "out", out, torch.bfloat16, 2)
     _need(op, "k_pages", k_pages, torch.bfloat16, 4)
@@ -382,12 +457,29 @@ def attention_prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     check(status, op)
 
 
-def decode_splits(num_rows: int, num_heads: int, max_kv_len: int) -> int:
-    """How many CTAs share one (request, head) of a decode step. Measured on a B200: the grid
-    should fill the GPU about once (the splits are cut for 1036 CTAs, tuned at GPT-2 XL's
-    shapes; six CTAs of this kernel are resident per SM, so that is a little over one round), a
-    cluster merges up to 8 shares on chip, and a warp wants at least 32 keys."""
-    fill = 1036 // max(1, num_rows * num_heads)
+#: CTAs of the decode attention kernel the grid aims at per SM: six are resident (32 KB of
+#: shared memory each), and a little over one round measured best
+DECODE_CTAS_PER_SM = 7
+_sm_counts: dict[int, int] = {}
+
+
+def sm_count(device: torch.device | None = None) -> int:
+    """Streaming multiprocessors of ``device`` (the current one when absent), asked once."""
+    index = torch.cuda.current_device() if device is None or device.index is None \
+        else device.index
+    found = _sm_counts.get(index)
+    if found is None:
+        found = torch.cuda.get_device_properties(index).multi_processor_count
+        _sm_counts[index] = found
+    return found
+
+
+def decode_splits(num_rows: int, num_heads: int, max_kv_len: int,
+                  device: torch.device | None = None) -> int:
+    """How many CTAs share one (request, head) of a decode step: the grid should fill the
+    device about once (``DECODE_CTAS_PER_SM`` CTAs per SM), a cluster merges up to 8 shares on
+    chip, and a warp wants at least 32 keys."""
+    fill = DECODE_CTAS_PER_SM * sm_count(device) // max(1, num_rows * num_heads)
     enough_keys = max(1, max_kv_len // 128)
     splits = max(1, min(fill, enough_keys, 8))
     while splits & (splits - 1):  # a power of two
@@ -411,6 +503,8 @@ def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     key and value are taken from there, and with ``store`` the kernel also writes them into
     the row's cache slot, so no separate KV store runs."""
     op = "attention_decode"
+    if _left_out and op in _left_out:
+        return
     _need(op, "q", q, ndim=2)
     _need(op, "out", out, q.dtype, 2)
     _need(op, "k_pages", k_pages, q.dtype, 4)
@@ -468,6 +562,8 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, *, rows: int | None = None,
     split over ``ARGMAX_PARTS`` CTAs and folded by a second small kernel: faster for a few
     rows of a large vocabulary."""
     op = "argmax"
+    if _left_out and op in _left_out:
+        return
     _need(op, "logits", logits, torch.float32, 2)
     _need(op, "out", out, torch.int32, 1)
     n = logits.shape[0] if rows is None else rows

@@ -72,9 +72,8 @@ class DecoderModel(Part):
                                        rows=num_want)
         logits = step.workspace.buffer("model.logits", spec.vocab_size, torch.float32,
                                        rows=num_want)
-        from ayaka_b200.parts.norm import LayerNorm
-
-        if hasattr(self.head, "forward_normed") and type(self.final_norm) is LayerNorm:
+        if hasattr(self.head, "forward_normed") and \
+                getattr(self.final_norm, "fusable_layer_norm", False):
             self.head.forward_normed(self.final_norm, residual, want_rows,  # type: ignore
                                      chosen, logits, count=num_want)
         else:

@@ -59,7 +59,6 @@ class PreNormBlock(Block):
 
 
 def _plain_norm(norm: Part) -> bool:
-    """Whether ``norm`` is the LayerNorm a fused kernel can apply from (weight, bias, eps)."""
-    from ayaka_b200.parts.norm import LayerNorm
-
-    return type(norm) is LayerNorm
+    """Whether ``norm`` declares itself a LayerNorm that a fused kernel can apply from its
+    (weight, bias, eps); see ``parts/norm.py``."""
+    return bool(getattr(norm, "fusable_layer_norm", False))

@@ -127,21 +127,14 @@ class Attention(Mixer):
             ops.kv_store(k, v, group.slot_mapping, cache.k_pages, cache.v_pages, rows=n)
         attended = step.workspace.buffer("attention.out", self.q_width, self.ctx.dtype)
         if step.decode_only:
-            # one row per request: the split-KV kernel; its scratch lives in the workspace
+            # one row per request: the split-KV kernel
             reach = min(step.max_kv_len, self.window) if self.window else step.max_kv_len
-            splits = ops.decode_splits(n, self.num_heads, reach)
-            partial = tickets = None
-            if splits > 8:  # beyond a cluster's size the shares are merged through scratch
-                # rows * heads * splits never exceeds 1036 + rows * heads (see decode_splits)
-                pairs = step.workspace.max_rows * self.num_heads
-                partial = step.workspace.buffer(
-                    "attention.partial", (1036 + pairs) * (self.head_dim + 2), torch.float32,
-                    rows=1)
-                tickets = step.workspace.buffer("attention.tickets", pairs, torch.int32, rows=1)
+            # (at most 8: a cluster merges the shares on chip, no scratch)
+            splits = ops.decode_splits(n, self.num_heads, reach, q.device)
             ops.attention_decode(q, cache.k_pages, cache.v_pages, group.block_table,
                                  step.request_of_row, step.positions, attended,
                                  num_heads=self.num_heads, scale=self.scale, window=self.window,
-                                 rows=n, splits=splits, partial=partial, tickets=tickets,
+                                 rows=n, splits=splits,
                                  k_new=k if cache.writes else None,
                                  v_new=v if cache.writes else None, store=cache.writes)
         elif self.ctx.dtype == torch.bfloat16:

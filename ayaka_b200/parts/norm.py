@@ -18,7 +18,14 @@ class LayerNorm(Part):
     dtype (formula: the reference's ``python/ayaka/layers/norm.py:59-100``).
 
     Spec parameters: ``width``, ``eps``, ``bias`` (bool).
+
+    ``fusable_layer_norm``: a norm part sets this when it is exactly the formula above with
+    the attributes ``weight``, ``bias`` (or ``None``) and ``eps``; a part whose first kernel
+    can normalise its input itself (``forward_normed``) may then be handed the norm instead
+    of its output. A norm part without the attribute is always applied on its own.
     """
+
+    fusable_layer_norm = True
 
     def __init__(self, spec: PartSpec, ctx: BuildContext) -> None:
         super().__init__(ctx)

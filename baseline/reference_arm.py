@@ -194,10 +194,9 @@ def run(args, cfg: dict, device: str = "cuda", dtype_name: str = "bf16",
                     point = decode_run(llm, bench.random_prompts(cfg, batch, prompt_len,
                                                                  10 + batch),
                                        warmup, steps, f"b{batch}", on_cuda)
-                    points[f"decode_b{batch}"] = {
-                        "value": round(batch * 1000.0 / point["ms"], 1),
-                        "ms": round(point["ms"], 4),
-                        "context": round(point["mean_context"], 1)}
+                    points[f"decode_b{batch}"] = round(batch * 1000.0 / point["ms"], 1)
+                    points[f"decode_b{batch}_ms"] = round(point["ms"], 4)
+                    points[f"decode_b{batch}_context"] = round(point["mean_context"], 1)
             tokens = 128 if cfg["n_positions"] - prompt_len > 128 else 8
             e2e_prompts = bench.random_prompts(cfg, 8, prompt_len, 4242)
             timed_generate(llm, e2e_prompts, 4)

@@ -15,8 +15,11 @@ time of 1 token) / (T - 1), the reference's method (``benchmarks/e2e/decode.py:1
 decode step must read (every weight once plus the live requests' keys and values) by its
 time and by the measured copy bandwidth. ``points`` holds decode at batch 1 and 64.
 
-``--workload small|large`` runs one of the two serving workloads of BASELINE.json's other
-configurations instead (see :func:`workload_run`) and prints a line of its own.
+``kernels`` holds, for the batch-8 decode step and for the prefill step, what each kernel
+class costs inside the step (the step replayed as a CUDA graph with and without the class)
+and its fraction of the roofline that bounds it. ``workloads`` holds the two serving
+workloads of BASELINE.json's other configurations (see :func:`workload_run`);
+``--workload small|large`` runs one of them alone and prints a line of its own.
 """
 
 from __future__ import annotations
@@ -72,7 +75,7 @@ class Clocks:
         try:
             self.process = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.process = None
@@ -248,7 +251,171 @@ def e2e_run(llm, cfg: dict, batch: int, tokens: int) -> dict:
             "ms_per_step": per_step * 1000}
 
 
-def workload_run(which: str) -> int:
+# ---- per-kernel times: a step with and without each kernel class --------------------------
+def _timed_graph(body, repeats: int) -> float:
+    """Milliseconds of one replay of ``body`` captured as a CUDA graph (best of ``repeats``;
+    the body has run twice before the capture)."""
+    import torch
+
+    body()
+    body()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        body()
+    graph.replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = math.inf
+    for _ in range(repeats):
+        start.record()
+        graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        best = min(best, start.elapsed_time(stop))
+    del graph
+    return best
+
+
+def kernel_classes(cfg: dict) -> dict[str, str]:
+    """Short name -> kernel class as ``ayaka_b200.kernels.ops`` names it."""
+    d, f, v = cfg["n_embd"], cfg["n_inner"], cfg["vocab_size"]
+    return {"qkv": f"linear:{3 * d}x{d}", "attn_out": f"linear:{d}x{d}", "fc": f"linear:{f}x{d}",
+            "proj": f"linear:{d}x{f}", "head": f"linear:{v}x{d}", "layer_norm": "layer_norm"}
+
+
+def profile_decode(llm, cfg: dict, batch: int, peak: dict) -> dict:
+    """What each kernel class costs inside a decode step of ``batch`` requests at context
+    ~530: the step's own CUDA graph body is captured again with one class left out
+    (``ops.leaving_out``) and the difference of the replay times is the class's share of the
+    dependent chain. ``frac`` is its bytes (weights read once, or the live keys and values)
+    over that time over the measured copy bandwidth."""
+    import torch
+
+    from ayaka_b200 import SamplingParams
+    from ayaka_b200.kernels import ops
+
+    scheduler = llm.scheduler
+    params = SamplingParams(temperature=0.0, max_tokens=None, ignore_eos=True)
+    for index, prompt in enumerate(random_prompts(cfg, batch, PROMPT, 77)):
+        scheduler.add_request(f"profile-{index}", prompt, params)
+    while any(r.prefilling for r in scheduler.running.values()) or scheduler.waiting:
+        llm._advance()
+    for _ in range(16):
+        llm._advance()
+    llm.graphs.drop_ahead()
+    torch.cuda.synchronize()
+    context = PROMPT + 17
+    bucket = llm.graphs.bucket_for(batch)
+    core = llm.core
+
+    def body() -> None:
+        bucket.launch_body(core, True)
+
+    d, f, v, layers = cfg["n_embd"], cfg["n_inner"], cfg["vocab_size"], cfg["n_layer"]
+    classes = {**kernel_classes(cfg), "attention": "attention_decode", "argmax": "argmax",
+               "embed": "embed_rows"}
+    nbytes = {"qkv": layers * 3 * d * d * 2, "attn_out": layers * d * d * 2,
+              "fc": layers * d * f * 2, "proj": layers * d * f * 2, "head": v * d * 2,
+              "attention": layers * batch * context * 2 * d * 2,
+              "layer_norm": (2 * layers + 1) * batch * d * 6,
+              "argmax": batch * v * 4, "embed": batch * d * 8}
+    full = _timed_graph(body, 10)
+    out = {"step_us": round(full * 1000, 1), "context": context, "batch": batch,
+           "method": "graph replay of the step with and without the class"}
+    for name, klass in classes.items():
+        with ops.leaving_out(klass):
+            without = _timed_graph(body, 10)
+        us = max(full - without, 1e-6) * 1000
+        per = layers if name not in ("head", "argmax", "embed") else 1
+        out[name] = {"us": round(us, 1), "per_layer_us": round(us / per, 2),
+                     "bytes": nbytes[name],
+                     "frac": round(nbytes[name] / (us * 1e-6) / 1e9 / peak["hbm_gbs"], 3),
+                     "peak": "hbm_gbs"}
+    for request_id in list(scheduler.running):
+        scheduler.abort(request_id)
+    scheduler.take_events()
+    return out
+
+
+def profile_prefill(llm, cfg: dict, peak: dict) -> dict:
+    """Each kernel class inside one 2,048-token prompt step (two prompts of 1,024), two ways.
+    ``alone_us``: the class's own kernels, from CUDA events around every launch of the step
+    (``ops.timed``), with the device kept busy ahead of the step so that no host time falls
+    between a launch's events; no kernel starts under its predecessor's tail then, so the
+    sum is more than the step. ``us``: what the step loses when the class is left out
+    (``ops.leaving_out``, the step replayed as a CUDA graph), i.e. the class's share of the
+    chain of dependent launches; a kernel whose time hides the start-up of its neighbours
+    measures little here. ``frac`` is the class's floating-point work over ``alone_us`` over
+    the measured bf16 matrix-product peak; for the norms, the embedding and the head (two
+    rows) its bytes over the copy bandwidth."""
+    import torch
+
+    from ayaka_b200.engine.runner import StepEntry
+    from ayaka_b200.kernels import ops
+
+    core = llm.core
+    length = cfg["n_positions"]
+    entries = [StepEntry(f"profile-prefill-{i}", prompt, (length - 1,))
+               for i, prompt in enumerate(random_prompts(cfg, 2, length, 990))]
+    d, f, v, layers = cfg["n_embd"], cfg["n_inner"], cfg["vocab_size"], cfg["n_layer"]
+    tokens = 2 * length
+    classes = {**kernel_classes(cfg), "attention": "attention_prefill", "embed": "embed_rows"}
+    names = {klass: name for name, klass in classes.items()}
+    alone: dict[str, float] = {}
+    for _ in range(4):
+        torch.cuda.synchronize()
+        torch.cuda._sleep(40_000_000)  # about 20 ms: the launches below queue up behind it
+        with ops.timed() as record:
+            core.step(entries)
+        torch.cuda.synchronize()
+        for klass, pairs in record.items():
+            total = sum(a.elapsed_time(b) for a, b in pairs) * 1000
+            name = names.get(klass, klass)
+            alone[name] = min(alone.get(name, math.inf), total)
+        for entry in entries:
+            core.release(entry.request_id)
+
+    for entry in entries:
+        if not core.manager.allocate(entry.request_id, length):
+            raise RuntimeError("no room for the prefill profile")
+    step, want_rows, num_want = core.runner.prepare(entries)
+    torch.cuda.synchronize()
+
+    def body() -> None:
+        core.model.forward(step, core.runner.caches, want_rows, num_want)
+
+    full = _timed_graph(body, 5)
+    flops = {"qkv": 2.0 * tokens * 3 * d * d * layers, "attn_out": 2.0 * tokens * d * d * layers,
+             "fc": 2.0 * tokens * d * f * layers, "proj": 2.0 * tokens * d * f * layers,
+             "attention": layers * 2 * 4.0 * d * (length * (length + 1) / 2)}
+    nbytes = {"layer_norm": 2 * layers * tokens * d * 6, "head": v * d * 2,
+              "embed": tokens * d * 8}
+    out = {"step_us": round(full * 1000, 1), "tokens": tokens,
+           "alone_sum_us": round(sum(alone.values()), 1),
+           "method": "alone_us: events around every launch; us: the step as a graph with "
+                     "and without the class"}
+    for name, klass in classes.items():
+        with ops.leaving_out(klass):
+            without = _timed_graph(body, 5)
+        own = alone.get(name, 0.0)
+        per = layers if name not in ("head", "embed") else 1
+        record = {"us": round(max(full - without, 0.0) * 1000, 1), "alone_us": round(own, 1),
+                  "alone_per_layer_us": round(own / per, 2)}
+        if own > 0 and name in flops:
+            record.update(flops=flops[name], peak="bf16_tflops (burst)",
+                          frac=round(flops[name] / (own * 1e-6) / 1e12 / peak["bf16_tflops"], 3))
+        elif own > 0 and name in nbytes:
+            record.update(bytes=nbytes[name], peak="hbm_gbs",
+                          frac=round(nbytes[name] / (own * 1e-6) / 1e9 / peak["hbm_gbs"], 3))
+        out[name] = record
+    for entry in entries:
+        core.manager.free(entry.request_id)
+    core.manager.check_integrity()
+    return out
+
+
+def workload_run(which: str) -> dict:
     """The two serving workloads BASELINE.json names beside the headline (``configs[3]`` and
     ``configs[4]``), through ``LLM.generate`` with host token ids in and out; one JSON line.
 
@@ -293,7 +460,9 @@ def workload_run(which: str) -> int:
         outputs = llm.generate(batch, params)
         best = min(best, time.perf_counter() - begin)
         generated = sum(len(o.outputs[0].token_ids) for o in outputs)
-    print(json.dumps({
+    del llm
+    torch.cuda.empty_cache()
+    return ({
         "metric": f"generated tok/s through LLM.generate ({name})", "impl": "ours",
         "value": round(generated / best, 1), "unit": "tok/s", "n_gpus": 1, "dtype": "bf16",
         "data": "synthetic", "ms": round(best * 1000, 1), "generated_tokens": generated,
@@ -301,8 +470,7 @@ def workload_run(which: str) -> int:
         "config": {"n_layer": cfg["n_layer"], "n_embd": cfg["n_embd"], "n_head": cfg["n_head"],
                    "n_inner": cfg["n_inner"], "vocab_size": cfg["vocab_size"],
                    "n_positions": cfg["n_positions"], "page_size": 16,
-                   "weights": "random bf16 seed 0", "cuda_graph": True}}))
-    return 0
+                   "weights": "random bf16 seed 0", "cuda_graph": True}})
 
 
 def config_record(cfg: dict, mean_context: float, prompt_len: int = PROMPT) -> dict:
@@ -336,6 +504,11 @@ def main() -> int:
                         help="layers to build (GPT-2 XL has 48); sizes of a layer never change")
     parser.add_argument("--skip-points", action="store_true",
                         help="leave out the batch 1 / batch 64 points and the e2e run")
+    parser.add_argument("--no-profile", action="store_true",
+                        help="leave out the per-kernel times (a step with and without each "
+                             "kernel class)")
+    parser.add_argument("--skip-workloads", action="store_true",
+                        help="leave out the two serving workloads of the other configurations")
     parser.add_argument("--workload", choices=("small", "large"),
                         help="instead of the headline run: one of the two serving workloads "
                              "(GPT-2 small with 64 ragged requests; GPT-2 large with prompt "
@@ -352,7 +525,8 @@ def main() -> int:
         print("bench.py: no CUDA device")
         return 1
     if args.workload:
-        return workload_run(args.workload)
+        print(json.dumps(workload_run(args.workload)))
+        return 0
     warmup = max(args.warmup, 3)
     steps = max(1, min(args.steps, XL["n_positions"] - PROMPT - 2 - warmup))
     cfg = {**XL, "n_layer": args.layers}
@@ -363,14 +537,34 @@ def main() -> int:
     clocks.start()
     main_run = decode_run(llm, cfg, 8, warmup, steps, seed=1)
     clock_record = clocks.stop()
+    clock_record["window"] = "prefill, warm-up and timed steps of the batch-8 run"
     prefill = prefill_run(llm, cfg, 2, 5)
-    points, e2e = {}, None
+    points, e2e, kernels, workloads = {}, None, None, None
     if not args.skip_points:
         for batch in (1, 64):
             run = decode_run(llm, cfg, batch, warmup, steps, seed=10 + batch)
             points[f"decode_b{batch}"] = round(batch * 1000.0 / run["ms"], 1)
             points[f"decode_b{batch}_ms"] = round(run["ms"], 4)
+            points[f"decode_b{batch}_context"] = round(run["mean_context"], 1)
+            batch_bytes = layer_weight_bytes(cfg, cfg["n_layer"]) + \
+                batch * run["mean_context"] * kv_bytes_per_token(cfg, cfg["n_layer"])
+            points[f"decode_b{batch}_hbm_frac"] = round(
+                batch_bytes / (run["ms"] * 1e-3) / 1e9 / peak["hbm_gbs"], 4)
         e2e = e2e_run(llm, cfg, 8, 128)
+    if not args.no_profile:
+        kernels = {"decode_b8": profile_decode(llm, cfg, 8, peak),
+                   "prefill_2048": profile_prefill(llm, cfg, peak)}
+    if not args.skip_workloads:
+        llm.close()
+        del llm
+        torch.cuda.empty_cache()
+        workloads = {}
+        for which in ("small", "large"):
+            record = workload_run(which)
+            workloads[which] = {"value": record["value"], "unit": "generated tok/s",
+                                "ms": record["ms"], "generated_tokens": record["generated_tokens"],
+                                "prompt_tokens": record["prompt_tokens"],
+                                "what": record["metric"]}
 
     layers = cfg["n_layer"]
     step_bytes = layer_weight_bytes(cfg, layers) + \
@@ -388,7 +582,7 @@ def main() -> int:
         "prefill": {"value": round(prefill["tokens"] * 1000.0 / prefill["ms"], 1),
                     "tokens": prefill["tokens"], "ms": round(prefill["ms"], 3),
                     "frac": round(flops / (prefill["ms"] * 1e-3) / (peak["bf16_tflops"] * 1e12),
-                                  4)},
+                                  4), "peak": "bf16_tflops (burst)"},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1),
                      "peak": peak["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peak["hbm_gbs"], 4), "peaks": peak_source},
@@ -400,6 +594,10 @@ def main() -> int:
     if e2e is not None:
         line["e2e"] = {key: (round(val, 2) if isinstance(val, float) else val)
                        for key, val in e2e.items()}
+    if kernels is not None:
+        line["kernels"] = kernels
+    if workloads is not None:
+        line["workloads"] = workloads
     print(json.dumps(line))
     return 0
 
