@@ -46,6 +46,10 @@ _TYPE = {torch.float32: 0, torch.bfloat16: 1}
 BF16_GEMM = "tcgen05"
 
 
+#: Whether parts that can hand a layer half (or a run of layers) to the C++ host code
+#: (``csrc/step_host.cu``) do so; tests switch it off to compare the two paths bit by bit.
+NATIVE_STEP = True
+
 _launches = 0
 
 #: Kernel classes that launch nothing while a measurement runs; empty in normal use. A

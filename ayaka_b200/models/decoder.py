@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import torch
 
+from ayaka_b200.kernels import native, ops
 from ayaka_b200.parts.base import BuildContext, CacheNeed, Part, StateNeed, build_part
 from ayaka_b200.parts.context import LayerCache, StepContext
 from ayaka_b200.parts.spec import ModelSpec
@@ -47,6 +48,8 @@ class DecoderModel(Part):
                                  "exist")
             if run.reads_cache_of is not None and not 0 <= run.reads_cache_of < position:
                 raise ValueError(f"order[{position}] must read the cache of an earlier run")
+        self._runs: dict[tuple[int, int], object] = {}
+        self._keep: list[object] = []
 
     def needs(self) -> list[tuple[CacheNeed | None, StateNeed | None]]:
         """For each run of the order: the pages and the state its mixer asks for."""
@@ -56,6 +59,25 @@ class DecoderModel(Part):
             out.append((mixer.cache_need(), mixer.state_need()))
         return out
 
+    def _native_runs(self, step: StepContext, caches: list[LayerCache]):  # noqa: ANN202
+        """The execution order packed for the C++ host code (once per list of caches and
+        workspace), or ``None`` when some layer has a part that code does not know."""
+        key = (id(caches), id(step.workspace))
+        if key not in self._runs:
+            entries = []
+            for index, run in enumerate(self.spec.order):
+                block = self.blocks[run.layer]
+                cache = caches[index]
+                halves = block.native_run(step.workspace) \
+                    if hasattr(block, "native_run") and cache.k_pages is not None else None
+                if halves is None:
+                    entries = None
+                    break
+                entries.append((*halves, cache))
+            self._runs[key] = None if entries is None else native.LayerRuns(entries)
+            self._keep.append(caches)  # the key is an id: keep its object alive
+        return self._runs[key]
+
     def forward(self, step: StepContext, caches: list[LayerCache],
                 want_rows: torch.Tensor | None, num_want: int) -> torch.Tensor | None:
         """Run the step's rows; return fp32 logits ``[num_want, vocab]`` (a view of a
@@ -64,8 +86,13 @@ class DecoderModel(Part):
         residual = step.workspace.buffer("model.residual", spec.hidden_size, torch.float32)
         self.embedding.forward(  # type: ignore[attr-defined]
             step, residual, self.position.added_rows(step))  # type: ignore[attr-defined]
-        for index, run in enumerate(spec.order):
-            self.blocks[run.layer].forward(residual, step, caches[index])  # type: ignore
+        runs = self._native_runs(step, caches) if ops.NATIVE_STEP else None
+        if runs is not None:
+            # every layer can run from the C++ host code: one call walks the whole order
+            native.run_layers(runs, native.step_args(step, residual.device), residual)
+        else:
+            for index, run in enumerate(spec.order):
+                self.blocks[run.layer].forward(residual, step, caches[index])  # type: ignore
         if num_want == 0 or want_rows is None:
             return None
         chosen = step.workspace.buffer("model.head_in", spec.hidden_size, self.ctx.dtype,

@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from ayaka_b200.parts.base import BuildContext, Part, build_part, register_part
-from ayaka_b200.parts.context import LayerCache, StepContext
+from ayaka_b200.parts.context import LayerCache, StepContext, Workspace
 from ayaka_b200.parts.spec import LayerSpec
 
 __all__ = ["Block", "PreNormBlock"]
@@ -40,6 +40,18 @@ class PreNormBlock(Block):
             "feed_forward",
             build_part("feed_forward", spec.feed_forward.kind, spec.feed_forward, ctx))
         self.width = int(spec.mixer_norm.width)  # type: ignore[arg-type]
+
+    def native_run(self, workspace: Workspace):  # noqa: ANN201
+        """``(attention part, feed-forward part)`` for the C++ host code when both halves of
+        this layer can run there (fusable norms, parts that know how to pack themselves),
+        else ``None``; see ``kernels/native.py``."""
+        if not (_plain_norm(self.mixer_norm) and _plain_norm(self.feed_forward_norm)
+                and hasattr(self.mixer, "native_part")
+                and hasattr(self.feed_forward, "native_part")):
+            return None
+        attention = self.mixer.native_part(self.mixer_norm, workspace)  # type: ignore
+        mlp = self.feed_forward.native_part(self.feed_forward_norm, workspace)  # type: ignore
+        return None if attention is None or mlp is None else (attention, mlp)
 
     def forward(self, residual: torch.Tensor, step: StepContext, cache: LayerCache) -> None:
         n = step.num_rows

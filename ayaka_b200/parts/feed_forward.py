@@ -6,7 +6,7 @@ import torch
 
 from ayaka_b200.kernels import ops
 from ayaka_b200.parts.base import BuildContext, Part, register_part
-from ayaka_b200.parts.context import StepContext
+from ayaka_b200.parts.context import StepContext, Workspace
 from ayaka_b200.parts.spec import PartSpec
 
 __all__ = ["DenseMLP", "FeedForward"]
@@ -42,6 +42,7 @@ class DenseMLP(FeedForward):
         self.up_bias = self.add_param("up.bias", (self.inner,), "vector") if bias else None
         self.down_weight = self.add_param("down.weight", (self.width, self.inner), "matrix")
         self.down_bias = self.add_param("down.bias", (self.width,), "vector") if bias else None
+        self._native: dict[tuple[int, int], object] = {}
 
     def forward(self, hidden: torch.Tensor, residual: torch.Tensor, step: StepContext) -> None:
         n = step.num_rows
@@ -50,7 +51,32 @@ class DenseMLP(FeedForward):
                    rows=n)
         ops.linear(inner, self.down_weight, self.down_bias, residual, residual=True, rows=n)
 
+    def native_part(self, norm: Part, workspace: Workspace):  # noqa: ANN201
+        """This feed-forward with ``norm`` in front of it as the C++ host code takes it
+        (packed once per workspace)."""
+        key = (id(norm), id(workspace))
+        found = self._native.get(key)
+        if found is None:
+            from ayaka_b200.kernels import native
+
+            dtype = self.ctx.dtype
+            found = native.mlp_part(
+                dtype=dtype, width=self.width, inner=self.inner, activation=self.activation,
+                eps=norm.eps, norm_weight=norm.weight, norm_bias=norm.bias,  # type: ignore
+                up_weight=self.up_weight, up_bias=self.up_bias, down_weight=self.down_weight,
+                down_bias=self.down_bias,
+                normed=workspace.buffer("block.normed", self.width, dtype),
+                inner_buf=workspace.buffer("feed_forward.inner", self.inner, dtype))
+            self._native[key] = found
+        return found
+
     def forward_normed(self, norm: Part, residual: torch.Tensor, step: StepContext) -> None:
+        if ops.NATIVE_STEP:
+            from ayaka_b200.kernels import native
+
+            native.run_mlp(self.native_part(norm, step.workspace),
+                           native.step_args(step, residual.device), residual)
+            return
         n = step.num_rows
         inner = step.workspace.buffer("feed_forward.inner", self.inner, self.ctx.dtype)
         scratch = step.workspace.buffer("block.normed", self.width, self.ctx.dtype)

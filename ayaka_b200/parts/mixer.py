@@ -6,7 +6,7 @@ import torch
 
 from ayaka_b200.kernels import ops
 from ayaka_b200.parts.base import BuildContext, CacheNeed, Part, StateNeed, register_part
-from ayaka_b200.parts.context import LayerCache, StepContext
+from ayaka_b200.parts.context import LayerCache, StepContext, Workspace
 from ayaka_b200.parts.embedding import PositionEncoding
 from ayaka_b200.parts.spec import PartSpec
 
@@ -79,6 +79,7 @@ class Attention(Mixer):
         self.qkv_bias = self.add_param("qkv.bias", (out_features,), "vector") if bias else None
         self.out_weight = self.add_param("out.weight", (self.width, self.q_width), "matrix")
         self.out_bias = self.add_param("out.bias", (self.width,), "vector") if bias else None
+        self._native: dict[tuple[int, int], object] = {}
 
     def cache_need(self) -> CacheNeed:
         return CacheNeed(self.num_kv_heads, self.head_dim, self.window)
@@ -90,8 +91,41 @@ class Attention(Mixer):
         stored = self._project(hidden, qkv, step, cache)
         self._attend(qkv, residual, step, cache, stored)
 
+    def native_part(self, norm: Part, workspace: Workspace):  # noqa: ANN201
+        """This mixer with ``norm`` in front of it as the C++ host code takes it (packed once
+        per workspace), or ``None`` when that code cannot run it: a position encoding that
+        rewrites queries and keys is a Python hook."""
+        if self.position is not None and not self._keys_as_projected:
+            return None
+        key = (id(norm), id(workspace))
+        found = self._native.get(key)
+        if found is None:
+            from ayaka_b200.kernels import native
+
+            dtype = self.ctx.dtype
+            found = native.attention_part(
+                dtype=dtype, width=self.width, num_heads=self.num_heads,
+                num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window,
+                scale=self.scale, eps=norm.eps, keys_as_projected=True,  # type: ignore
+                norm_weight=norm.weight, norm_bias=norm.bias,  # type: ignore[attr-defined]
+                qkv_weight=self.qkv_weight, qkv_bias=self.qkv_bias, out_weight=self.out_weight,
+                out_bias=self.out_bias,
+                normed=workspace.buffer("block.normed", self.width, dtype),
+                qkv=workspace.buffer("attention.qkv", self.q_width + 2 * self.kv_width, dtype),
+                attended=workspace.buffer("attention.out", self.q_width, dtype))
+            self._native[key] = found
+        return found
+
     def forward_normed(self, norm: Part, residual: torch.Tensor, step: StepContext,
                        cache: LayerCache) -> None:
+        if ops.NATIVE_STEP and cache.k_pages is not None:
+            part = self.native_part(norm, step.workspace)
+            if part is not None:
+                from ayaka_b200.kernels import native
+
+                native.run_attention(part, native.step_args(step, residual.device), residual,
+                                     cache)
+                return
         qkv = step.workspace.buffer("attention.qkv", self.q_width + 2 * self.kv_width,
                                     self.ctx.dtype)
         scratch = step.workspace.buffer("block.normed", self.width, self.ctx.dtype)

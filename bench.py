@@ -552,8 +552,16 @@ def main() -> int:
                 batch_bytes / (run["ms"] * 1e-3) / 1e9 / peak["hbm_gbs"], 4)
         e2e = e2e_run(llm, cfg, 8, 128)
     if not args.no_profile:
-        kernels = {"decode_b8": profile_decode(llm, cfg, 8, peak),
-                   "prefill_2048": profile_prefill(llm, cfg, peak)}
+        from ayaka_b200.kernels import ops
+
+        # the Python forward launches the same kernels as the C++ host code, one call each,
+        # which is where a kernel class can be left out or bracketed by events
+        ops.NATIVE_STEP = False
+        try:
+            kernels = {"decode_b8": profile_decode(llm, cfg, 8, peak),
+                       "prefill_2048": profile_prefill(llm, cfg, peak)}
+        finally:
+            ops.NATIVE_STEP = True
     if not args.skip_workloads:
         llm.close()
         del llm

@@ -253,3 +253,41 @@ def test_graph_buckets_of_32_and_64_rows_against_plain(models, live, dtype, slac
             row = logits[len(prompt) + index - 1]
             assert float(row[token]) >= float(row.max()) - slack * float(row.abs().max()), \
                 (index, token)
+
+
+# ---- the C++ host path and the Python path launch the same kernels ----------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_host_library_and_python_forward_give_the_same_bits(models, name, dtype):
+    """A step's layers run from the C++ host code (one call for the whole order) or kernel by
+    kernel from Python: the same launches with the same arguments, so the same bits, under
+    the mixed schedule (prompt portions beside single tokens, pages used again) and under
+    decode steps of 24 requests."""
+    from ayaka_b200.kernels import ops
+
+    folder, _, config = models[name, dtype]
+    sequences = sequences_of(name)
+    doubled = {**sequences, **{rid + "x": tokens for rid, tokens in sequences.items()}}
+    longest = max(len(tokens) for tokens in doubled.values())
+    mixed = es.schedule_mixed(doubled, 2 * (-(-longest // 64) * 64) + 64)
+    peak = es.peak_tokens(mixed, doubled)
+    decoders = {f"m{index}": random_tokens(config["vocab_size"], 3 + (7 * index) % 40 + 6,
+                                           6000 + index) for index in range(24)}
+    results = {}
+    for native in (True, False):
+        ops.NATIVE_STEP = native
+        try:
+            launches = ops.launch_count()
+            core = es.build_core(folder, dtype, num_blocks=peak // es.PAGE + 1)
+            got = es.replay(core, mixed)
+            core = es.build_core(folder, dtype, num_blocks=pages_for(decoders, es.PAGE),
+                                 max_running=24, max_tokens_per_step=2048)
+            got.update(es.replay(core, many_decoders_schedule(decoders, tail=6)))
+            results[native] = (got, ops.launch_count() - launches)
+        finally:
+            ops.NATIVE_STEP = True
+    (with_host, host_launches), (with_python, python_launches) = results[True], results[False]
+    assert host_launches == python_launches  # the same number of kernels
+    assert set(with_host) == set(with_python)
+    for rid, logits in with_host.items():
+        assert torch.equal(logits, with_python[rid]), rid
