@@ -392,6 +392,227 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------
+// The same product for a few hundred rows, where 128 x 128 tiles are too few to fill the
+// device (288 rows x 1280 columns are 30 tiles on 148 SMs, each walking all of K): the K
+// range is split over the 2 or 4 CTAs of a thread-block cluster. Every CTA accumulates its
+// share of K for the whole tile in tensor memory, then the cluster does a reduce-scatter
+// through distributed shared memory: CTA r owns columns r * 128 / R .. of the tile; every
+// CTA writes its partial sums of those columns into a slot of its own in CTA r's shared
+// memory (its own slot locally), one cluster barrier makes them visible, and CTA r adds the
+// R slots in rank order, so the sum's order is fixed whatever the batch. Then bias,
+// activation or residual sum, and the store (or, for the fused query/key/value projection,
+// the scatter of key and value columns into the cache), each lane on its own row. No CTA
+// reads or writes a peer's memory after the barrier, so nobody has to wait to leave; a CTA
+// whose wait ran out still takes part in the barrier (its peers would wait for it for ever
+// otherwise), skips its stores and reports through `status`.
+constexpr int SK_BN = 128;
+template <int STAGES>
+struct SplitKSmem {
+  static constexpr int STAGE_BYTES = TC_A_BYTES + SK_BN * TC_BK * 2;
+  static constexpr int RECV_OFFSET = STAGES * STAGE_BYTES;      // [src rank][row][own columns]
+  static constexpr int RECV_BYTES = TC_BM * SK_BN * 4;          // R * 128 * (128 / R) floats
+  static constexpr int BAR_OFFSET = RECV_OFFSET + RECV_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16;
+  static constexpr int DYNAMIC = TOTAL + 1024;
+};
+
+template <int STAGES, bool SCATTER>
+__global__ void __launch_bounds__(128)
+gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a,
+                      const __grid_constant__ CUtensorMap map_w, const float* __restrict__ bias,
+                      void* __restrict__ out, int ldo, int M, int N, int K, int act, int mode,
+                      int vec_ok, int kb_per_split, int* __restrict__ status, KvScatter kv) {
+  using L = SplitKSmem<STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty = full + STAGES;
+  uint64_t* accum = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* recv = reinterpret_cast<float*>(smem + L::RECV_OFFSET);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int R = gridDim.y;                 // the cluster spans grid.y
+  const int rank = (int)cluster_rank();    // == blockIdx.y
+  const int n0 = blockIdx.x * SK_BN, m0 = blockIdx.z * TC_BM;
+  const int num_kb = (K + TC_BK - 1) / TC_BK;
+  const int kb0 = rank * kb_per_split;
+  const int kb1 = kb0 + kb_per_split < num_kb ? kb0 + kb_per_split : num_kb;
+  const int my_kb = kb1 - kb0;             // at least 1 (the host chooses R so)
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    *failed = 0;
+    mbar_fence_init();
+    tma_prefetch_map(&map_a);
+    tma_prefetch_map(&map_w);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, tc_tmem_cols(SK_BN));
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  pdl_launch_dependents();
+  int issued = 0;
+  if (warp == 0 && lane == 0) {
+    const int ahead = my_kb < STAGES ? my_kb : STAGES;
+    for (int i = 0; i < ahead; ++i) {  // weight tiles do not depend on the kernel ahead
+      mbar_expect_tx(&full[i], L::STAGE_BYTES);
+      tma_load_2d(smem + i * L::STAGE_BYTES + TC_A_BYTES, &map_w, &full[i], (kb0 + i) * TC_BK,
+                  n0);
+    }
+    pdl_wait();
+    for (int i = 0; i < my_kb; ++i) {
+      const int s = i % STAGES;
+      uint8_t* a_tile = smem + s * L::STAGE_BYTES;
+      if (i >= STAGES) {
+        if (!mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) {
+          *failed = 1;
+          break;
+        }
+        mbar_expect_tx(&full[s], L::STAGE_BYTES);
+        tma_load_2d(a_tile + TC_A_BYTES, &map_w, &full[s], (kb0 + i) * TC_BK, n0);
+      }
+      tma_load_2d(a_tile, &map_a, &full[s], (kb0 + i) * TC_BK, m0);
+      issued = i + 1;
+    }
+  } else if (warp == 1 && lane == 0) {
+    constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, SK_BN);
+    bool ok = true;
+    for (int i = 0; i < my_kb && ok; ++i) {
+      const int s = i % STAGES;
+      if (!mbar_wait(&full[s], (i / STAGES) & 1)) {
+        *failed = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint8_t* a_tile = smem + s * L::STAGE_BYTES;
+      const uint8_t* b_tile = a_tile + TC_A_BYTES;
+#pragma unroll
+      for (int k = 0; k < TC_BK / 16; ++k) {
+        umma_f16(tmem_base, umma_desc_k128(a_tile, k * 32), umma_desc_k128(b_tile, k * 32),
+                 idesc, (i | k) != 0);
+      }
+      umma_commit(&empty[s]);
+    }
+    if (ok) umma_commit(accum);
+  }
+
+  // ---- reduce-scatter: this CTA's partial sums go to the owners of their columns ------
+  __syncwarp();
+  const int row = warp * 32 + lane;  // the tile row (tensor-memory lane) this thread owns
+  const long long kv_row = SCATTER ? kv_row_offset(kv, m0 + row, M) : -1;
+  pdl_wait();
+  bool have = mbar_wait(accum, 0);
+  if (!have) *failed = 1;
+  tc_fence_after();
+  const int chunks_own = 4 / R;      // 32-column chunks a rank owns (R is 2 or 4)
+  const int cols_own = SK_BN / R;
+  if (have && *failed == 0) {
+    const int swz = lane & 7;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t raw[32];
+      tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), raw);
+      tmem_ld_wait();
+      const int owner = c / chunks_own;
+      // slot [rank][row][(c % chunks_own) * 32 ..]; the eight 16-byte pieces of a chunk are
+      // permuted by the row so that a warp's stores spread over the banks
+      float* local = recv + ((size_t)rank * TC_BM + row) * cols_own + (c % chunks_own) * 32;
+      const uint32_t base = peer_address(local, (uint32_t)owner);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        st_cluster_v4(base + (uint32_t)(((q ^ swz) << 4)), raw[q * 4], raw[q * 4 + 1],
+                      raw[q * 4 + 2], raw[q * 4 + 3]);
+      }
+    }
+  }
+  cluster_sync_all();  // every CTA, failed or not: the partial sums are visible after it
+
+  // ---- this rank's columns: sum in rank order, then the epilogue ----------------------
+  if (have && *failed == 0 && m0 + row < M) {
+    const int swz = lane & 7;
+#pragma unroll 1
+    for (int oc = 0; oc < chunks_own; ++oc) {
+      const int n = n0 + rank * cols_own + oc * 32;
+      if (n >= N) break;
+      uint32_t raw[32];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int src = 0; src < R; ++src) {
+          const float4 part = *reinterpret_cast<const float4*>(
+              reinterpret_cast<const uint8_t*>(recv + ((size_t)src * TC_BM + row) * cols_own +
+                                               oc * 32) + ((q ^ swz) << 4));
+          sum.x += part.x; sum.y += part.y; sum.z += part.z; sum.w += part.w;
+        }
+        raw[q * 4] = __float_as_uint(sum.x);
+        raw[q * 4 + 1] = __float_as_uint(sum.y);
+        raw[q * 4 + 2] = __float_as_uint(sum.z);
+        raw[q * 4 + 3] = __float_as_uint(sum.w);
+      }
+      if (SCATTER && n >= kv.q_width) {
+        // a key or value chunk: bias, round, and into the row's slot of the cache
+        if (kv_row >= 0) {
+          const int col = n - kv.q_width;
+          const int value = col >= kv.kv_width ? 1 : 0;
+          const int hcol = col - value * kv.kv_width;
+          const int head = hcol / kv.head_dim;
+          __nv_bfloat16* dst = (value ? kv.v_pages : kv.k_pages) + (size_t)kv_row +
+                               (size_t)head * kv.page_size * kv.head_dim +
+                               (hcol - head * kv.head_dim);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              v[j] = __uint_as_float(raw[q * 8 + j]) +
+                     (bias != nullptr ? __ldg(bias + n + q * 8 + j) : 0.f);
+            }
+            uint4 packed;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
+            packed.x = *reinterpret_cast<uint32_t*>(&h0);
+            packed.y = *reinterpret_cast<uint32_t*>(&h1);
+            packed.z = *reinterpret_cast<uint32_t*>(&h2);
+            packed.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(dst + q * 8) = packed;
+          }
+        }
+      } else {
+        store_row_chunk(raw, m0 + row, n, N, bias, out, ldo, mode, act, vec_ok);
+      }
+    }
+  }
+
+  // ---- teardown ---------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*failed != 0) {
+    if (warp == 0 && lane == 0) {
+      for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i) {
+        mbar_wait(&full[i % STAGES], (i / STAGES) & 1);
+      }
+      atomicExch(status, AYK_WAIT_TIMEOUT);
+    }
+    __syncthreads();
+  }
+  if (warp == 0) tmem_dealloc(tmem_base, tc_tmem_cols(SK_BN));
+}
+
+// ---------------------------------------------------------------------------------------
 // The same product as a persistent kernel: one CTA per SM walks over output tiles, with two
 // accumulators in tensor memory so that the epilogue of one tile runs under the main loop of
 // the next. Six warps: warp 0's elected thread feeds the shared-memory ring by TMA without
@@ -1178,6 +1399,55 @@ int launch_gemm_tc_pair(const void* a, int lda, const void* w, int ldw, const fl
                          vec_ok, status);
 }
 
+// K splits for a product of more than 64 rows whose 128 x 128 tiles would leave most of the
+// device idle and whose K is long: the largest of 4, 2 that leaves every CTA of the cluster
+// at least SK_MIN_BLOCKS blocks of K and keeps all CTAs resident at once (one per SM: the
+// exchange buffer takes the room of a second); 1 when the plain kernels are the better
+// choice. Measured at 288 rows (GPT-2 large's sizes): K = 5120 over 4 CTAs 23 against 33
+// microseconds; K = 1280 over 4 CTAs 19 against 17, the exchange costs more than it saves.
+constexpr int SK_MIN_BLOCKS = 16;
+inline int splitk_ranks(int M, int N, int K) {
+  const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + SK_BN - 1) / SK_BN);
+  const int num_kb = (K + TC_BK - 1) / TC_BK;
+  const int sms = sm_count();
+  for (int r : {4, 2}) {
+    const int per = (num_kb + r - 1) / r;
+    if (per >= SK_MIN_BLOCKS && per * (r - 1) < num_kb && tiles * r <= sms) return r;
+  }
+  return 1;
+}
+
+template <int STAGES, bool SCATTER>
+int launch_gemm_tc_splitk(const void* a, int lda, const void* w, int ldw, const float* bias,
+                          void* out, int ldo, int M, int N, int K, int act, int mode, int ranks,
+                          int* status, cudaStream_t stream, const KvScatter& kv = KvScatter{}) {
+  using L = SplitKSmem<STAGES>;
+  if (ranks != 2 && ranks != 4) return AYK_BAD_ARGUMENT;
+  const int num_kb = (K + TC_BK - 1) / TC_BK;
+  const int per = (num_kb + ranks - 1) / ranks;
+  if (per * (ranks - 1) >= num_kb) return AYK_BAD_ARGUMENT;  // a rank without a block of K
+  CUtensorMap map_a, map_w;
+  int r = cached_map(a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, TC_BM, &map_a);
+  if (r != AYK_OK) return r;
+  r = cached_map(w, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, SK_BN, &map_w);
+  if (r != AYK_OK) return r;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_splitk_kernel<STAGES, SCATTER>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYNAMIC);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const size_t elem = mode == OUT_BF16 ? 2 : 4;
+  const int vec_ok = (((uintptr_t)out % 16) == 0 && ((size_t)ldo * elem) % 16 == 0) ? 1 : 0;
+  const long long gz = (M + TC_BM - 1) / TC_BM;
+  if (gz > 65535) return AYK_TOO_LARGE;
+  dim3 grid((N + SK_BN - 1) / SK_BN, ranks, (unsigned)gz);
+  return launch_kernel(gemm_tc_splitk_kernel<STAGES, SCATTER>, grid, dim3(128), L::DYNAMIC,
+                       stream, ranks, map_a, map_w, bias, out, ldo, M, N, K, act, mode, vec_ok,
+                       per, status, kv);
+}
+
 template <int MP, int STAGES>
 int launch_gemm_tc_small(const void* a, int lda, const void* w, int ldw, const float* bias,
                          void* out, int ldo, int M, int N, int K, int act, int mode, int splits,
@@ -1266,7 +1536,9 @@ AYK_API void ayk_set_stream_rows(int rows) {
 // kernel for CTA pairs (256-row tiles, 192 or 256 wide; measured level with 1192 / 1256 at
 // GPT-2 XL's shapes, so the choice never picks it); negative = the few-rows kernel (see
 // pick_splits; -200 = the kernel for at most 16 rows that holds its weights on chip before the
-// rows arrive, gemm_stream.cuh; -201 / -202 = the same with one / two column tiles per CTA). `status` is one device int that a CTA sets to AYK_WAIT_TIMEOUT if a wait ran
+// rows arrive, gemm_stream.cuh; -201 / -202 = the same with one / two column tiles per CTA);
+// 3002, 3004 = 128 x 128 tiles with K split over a cluster of 2 or 4 CTAs (chosen for a few
+// hundred rows, where whole tiles would leave most SMs idle). `status` is one device int that a CTA sets to AYK_WAIT_TIMEOUT if a wait ran
 // out; the host reads it when it checks a step.
 AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, const float* bias,
                              void* out, int ldo, int M, int N, int K, int act, int mode,
@@ -1311,6 +1583,14 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
     }
     return launch_gemm_tc_small<64, 6>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
                                        splits, status, s);
+  }
+  if (tile_n == 0) {
+    const int ranks = splitk_ranks(M, N, K);
+    if (ranks > 1) tile_n = 3000 + ranks;
+  }
+  if (tile_n == 3002 || tile_n == 3004) {
+    return launch_gemm_tc_splitk<4, false>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
+                                           tile_n - 3000, status, s);
   }
   if (tile_n == 0) tile_n = choose_tile(M, N);
   switch (tile_n) {
@@ -1372,6 +1652,11 @@ AYK_API int ayk_gemm_bf16_tc_kv(const void* a, int lda, const void* w, int ldw,
   const KvScatter kv{slots, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, q_width, kv_width,
                      num_kv_heads, head_dim, page_size};
   cudaStream_t s = (cudaStream_t)stream;
+  const int ranks = splitk_ranks(M, N, K);
+  if (ranks > 1) {
+    return launch_gemm_tc_splitk<4, true>(a, lda, w, ldw, bias, out, ldo, M, N, K, ACT_NONE,
+                                          OUT_BF16, ranks, status, s, kv);
+  }
   switch (choose_tile(M, N)) {
     case 128:
       return launch_gemm_tc<128, 4, true>(a, lda, w, ldw, bias, out, ldo, M, N, K, ACT_NONE,

@@ -178,10 +178,20 @@ int layer_norm(const AykKernels& k, AykStep* step, int type, const float* x, int
   return ((LayerNormFn)fn)(x, ldx, nullptr, gamma, beta, eps, out, ldo, n, width, step->stream);
 }
 
-// sum over the step's requests of ceil(rows / tile_rows), and the longest portion
-int tiles_of(const AykStep* step, int tile_rows) {
+// parts/mixer.py leading_single_rows: requests at the head of the step that bring one row
+// each, if there are at least LEADING_SINGLE_ROWS of them and something else follows
+constexpr int LEADING_SINGLE_ROWS = 4;
+int leading_single_rows(const AykStep* step) {
+  int lead = 0;
+  while (lead < step->num_requests && step->host_rows[lead] == 1) ++lead;
+  return (lead >= LEADING_SINGLE_ROWS && lead < step->num_requests) ? lead : 0;
+}
+
+// sum over the step's requests from `first` on of ceil(rows / tile_rows), and the longest
+// portion
+int tiles_of(const AykStep* step, int tile_rows, int first) {
   int tiles = 0;
-  for (int b = 0; b < step->num_requests; ++b) {
+  for (int b = first; b < step->num_requests; ++b) {
     tiles += (step->host_rows[b] + tile_rows - 1) / tile_rows;
   }
   return tiles;
@@ -267,24 +277,41 @@ int attention_half(const AykAttentionPart* p, AykStep* step, float* residual, vo
         writes ? vv : nullptr, writes ? ld_qkv : 0, writes ? 1 : 0, step->status, p->type,
         step->stream);
   } else if (p->type == 1) {
+    // leading single-row requests go to the split-KV kernel (their keys and values are in
+    // the cache by now), the rest to a prompt kernel
+    const int lead = leading_single_rows(step);
+    if (lead > 0) {
+      int reach = step->max_kv_len;
+      if (p->window > 0 && p->window < reach) reach = p->window;
+      if (k.attention_decode == nullptr) return AYK_DRIVER;
+      ++step->launches;
+      r = ((AttnDecodeFn)k.attention_decode)(
+          q, ld_qkv, k_pages, v_pages, g.block_table, g.table_stride, step->request_of_row,
+          step->positions, p->attended, q_width, lead, p->num_heads, p->num_kv_heads,
+          p->head_dim, g.page_size, p->scale, p->window,
+          decode_splits(step, lead, p->num_heads, reach), nullptr, nullptr, nullptr, nullptr, 0,
+          0, step->status, p->type, step->stream);
+      if (r != AYK_OK) return r;
+    }
+    const int* table = g.block_table + (size_t)lead * g.table_stride;
     const bool tc = p->head_dim == 64 && p->scale > 0.f && !step->prefill_mma &&
                     k.attention_prefill_tc != nullptr &&
                     k.attention_prefill_tc_rows != nullptr && longest_portion(step) >= 256;
     ++step->launches;
     if (tc) {
       r = ((AttnPrefillTcFn)k.attention_prefill_tc)(
-          q, ld_qkv, k_pages, v_pages, g.block_table, g.table_stride, step->row_start,
-          step->kv_len, p->attended, q_width, step->num_requests,
-          tiles_of(step, ((int (*)())k.attention_prefill_tc_rows)()), p->num_heads,
+          q, ld_qkv, k_pages, v_pages, table, g.table_stride, step->row_start + lead,
+          step->kv_len + lead, p->attended, q_width, step->num_requests - lead,
+          tiles_of(step, ((int (*)())k.attention_prefill_tc_rows)(), lead), p->num_heads,
           p->num_kv_heads, p->head_dim, g.page_size, num_pages, p->scale, p->window,
           step->status, step->stream);
     } else {
       if (k.attention_prefill == nullptr) return AYK_DRIVER;
       r = ((AttnPrefillFn)k.attention_prefill)(
-          q, ld_qkv, k_pages, v_pages, g.block_table, g.table_stride, step->row_start,
-          step->kv_len, p->attended, q_width, step->num_requests, tiles_of(step, 64),
-          p->num_heads,
-          p->num_kv_heads, p->head_dim, g.page_size, p->scale, p->window, step->stream);
+          q, ld_qkv, k_pages, v_pages, table, g.table_stride, step->row_start + lead,
+          step->kv_len + lead, p->attended, q_width, step->num_requests - lead,
+          tiles_of(step, 64, lead), p->num_heads, p->num_kv_heads, p->head_dim, g.page_size,
+          p->scale, p->window, step->stream);
     }
   } else {
     if (k.attention_simt == nullptr) return AYK_DRIVER;

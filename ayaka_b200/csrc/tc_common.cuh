@@ -300,6 +300,14 @@ __device__ __forceinline__ uint32_t peer_address(const void* local, uint32_t ran
                "r"(rank));
   return remote;
 }
+// 16 bytes into shared memory of this or another CTA of the cluster (a shared::cluster
+// address from peer_address()).
+__device__ __forceinline__ void st_cluster_v4(uint32_t address, uint32_t a, uint32_t b,
+                                              uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(a),
+               "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
 __device__ __forceinline__ float ld_cluster_f32(uint32_t address) {
   float v;
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(address) : "memory");

@@ -10,7 +10,23 @@ from ayaka_b200.parts.context import LayerCache, StepContext, Workspace
 from ayaka_b200.parts.embedding import PositionEncoding
 from ayaka_b200.parts.spec import PartSpec
 
-__all__ = ["Attention", "Mixer"]
+__all__ = ["Attention", "Mixer", "leading_single_rows"]
+
+
+#: From this many leading single-row requests on, a step that also holds prompt portions
+#: runs them through the decode attention kernel (``csrc/step_host.cu`` has the same rule).
+LEADING_SINGLE_ROWS = 4
+
+
+def leading_single_rows(host_rows: list[int]) -> int:
+    """How many requests at the head of the step bring exactly one row, if at least
+    ``LEADING_SINGLE_ROWS`` do and something else follows; else 0."""
+    lead = 0
+    for rows in host_rows:
+        if rows != 1:
+            break
+        lead += 1
+    return lead if LEADING_SINGLE_ROWS <= lead < len(host_rows) else 0
 
 
 class Mixer(Part):
@@ -172,11 +188,23 @@ class Attention(Mixer):
                                  k_new=k if cache.writes else None,
                                  v_new=v if cache.writes else None, store=cache.writes)
         elif self.ctx.dtype == torch.bfloat16:
-            # prompt portions (and any single rows beside them): tensor-core flash attention
-            ops.attention_prefill(q, cache.k_pages, cache.v_pages, group.block_table,
-                                  step.row_start, step.kv_len, attended,
+            # Prompt portions: tensor-core flash attention. The requests that lead the step
+            # with a single row each (the scheduler puts decoding requests first) go to the
+            # split-KV kernel instead: as tiles of a prompt kernel each would occupy a CTA
+            # built for 64 or 256 rows. Their keys and values are in the cache by now.
+            lead = leading_single_rows(step.host_rows)
+            if lead:
+                reach = min(step.max_kv_len, self.window) if self.window else step.max_kv_len
+                ops.attention_decode(q, cache.k_pages, cache.v_pages, group.block_table,
+                                     step.request_of_row, step.positions, attended,
+                                     num_heads=self.num_heads, scale=self.scale,
+                                     window=self.window, rows=lead,
+                                     splits=ops.decode_splits(lead, self.num_heads, reach,
+                                                              q.device))
+            ops.attention_prefill(q, cache.k_pages, cache.v_pages, group.block_table[lead:],
+                                  step.row_start[lead:], step.kv_len[lead:], attended,
                                   num_heads=self.num_heads, scale=self.scale,
-                                  host_rows=step.host_rows, window=self.window)
+                                  host_rows=step.host_rows[lead:], window=self.window)
         else:
             ops.attention(q, cache.k_pages, cache.v_pages, group.block_table,
                           step.request_of_row, step.positions, attended,

@@ -291,3 +291,49 @@ def test_host_library_and_python_forward_give_the_same_bits(models, name, dtype)
     assert set(with_host) == set(with_python)
     for rid, logits in with_host.items():
         assert torch.equal(logits, with_python[rid]), rid
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_decoding_requests_ahead_of_prompt_portions(models, name, dtype):
+    """Steps as the scheduler builds them: six requests that bring one token each, then
+    portions of two long prompts (for D of 256 rows and more). In bfloat16 the single rows
+    run through the decode attention kernel and the portions through a prompt kernel, in
+    the same step."""
+    folder, state, config = models[name, dtype]
+    vocab, limit = config["vocab_size"], config["n_positions"]
+    short = {f"s{i}": random_tokens(vocab, 9 + 5 * i + 8, 8000 + i) for i in range(6)}
+    long = {"la": random_tokens(vocab, limit - 3, 8100), "lb": random_tokens(vocab, limit // 2, 8101)}
+    sequences = {**short, **long}
+    heads = {rid: len(tokens) - 8 for rid, tokens in short.items()}
+    sizes = {"la": [(limit - 3) // 3 + 1, 2, (limit - 3) // 3, 5, 10 ** 6],
+             "lb": [40, limit // 2 - 50, 3, 10 ** 6]}
+    fed = dict.fromkeys(long, 0)
+
+    def portion(rid, turn):
+        tokens, at = long[rid], fed[rid]
+        if at >= len(tokens) or turn >= len(sizes[rid]):
+            return None
+        size = min(sizes[rid][turn], len(tokens) - at)
+        fed[rid] = at + size
+        return {"id": rid, "tokens": tokens[at:at + size], "want": list(range(size))}
+
+    steps = [{"entries": [{"id": rid, "tokens": tokens[:heads[rid]],
+                           "want": list(range(heads[rid]))} for rid, tokens in short.items()],
+              "end": []}]
+    for turn in range(8):
+        entries = [{"id": rid, "tokens": [tokens[heads[rid] + turn]], "want": [0]}
+                   for rid, tokens in short.items()]
+        entries += [entry for entry in (portion(rid, turn) for rid in long) if entry]
+        steps.append({"entries": entries, "end": []})
+    assert all(fed[rid] == len(long[rid]) for rid in long)
+    steps[-1]["end"] = list(sequences)
+    core = es.build_core(folder, dtype, num_blocks=pages_for(sequences, es.PAGE),
+                         max_running=8, max_tokens_per_step=1024)
+    got = es.replay(core, steps)
+    es.assert_logits_close(got, es.plain_logits(state, config, sequences), dtype,
+                           f"decoders-then-portions/{name}")
+    if dtype == "bfloat16":
+        es.assert_logits_close(got, es.rounded_logits(state, config, sequences), dtype,
+                               f"decoders-then-portions/{name}", limits=es.ROUNDED_TOLERANCE,
+                               row_rms=es.ROUNDED_ROW_RMS)

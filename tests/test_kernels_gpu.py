@@ -136,7 +136,8 @@ def test_linear_bfloat16(kernel, m, n, k):
         gemm_tc.check_status(a.device)
 
 
-@pytest.mark.parametrize("tile_n", [32, 64, 128, 192, 256, 1128, 1192, 1256, 2192, 2256])
+@pytest.mark.parametrize("tile_n", [32, 64, 128, 192, 256, 1128, 1192, 1256, 2192, 2256, 3002,
+                                    3004])
 def test_linear_tcgen05_tiles_and_strides(tile_n):
     """Every tile width, operands that are column ranges of wider buffers, rows limited."""
     ops = _ops()
@@ -191,8 +192,48 @@ def test_linear_tcgen05_many_tiles(tile_n, m, n, k):
             torch.testing.assert_close(outs[1].double(), exact + 1.0, rtol=1e-4, atol=1e-4)
 
 
+@pytest.mark.parametrize("ranks", [2, 4])
+@pytest.mark.parametrize("m,n,k", [(288, 1280, 5120), (288, 1600, 1600), (65, 136, 200),
+                                   (300, 712, 136), (129, 100, 72), (500, 333, 6400)])
+def test_linear_tcgen05_k_split_over_a_cluster(ranks, m, n, k):
+    """A few hundred rows: 128 x 128 tiles whose K range is split over a cluster of 2 or 4
+    CTAs and reduced through distributed shared memory in rank order. Every epilogue, ragged
+    edges in M, N and K, rows beyond the product untouched, and the same bits on a second
+    run and whatever else is in the batch (the order of the sum is fixed)."""
+    from ayaka_b200.kernels import gemm_tc
+    if -(-k // 64) <= -(-(-(-k // 64)) // ranks) * (ranks - 1):
+        pytest.skip("fewer blocks of K than ranks")
+    code = 3000 + ranks
+    a = _randn(m, k, seed=24, dtype=torch.bfloat16)
+    w = _randn(n, k, seed=25, dtype=torch.bfloat16, scale=1 / math.sqrt(k))
+    bias = _randn(n, seed=26)
+    exact = a.double() @ w.double().t() + bias.double()
+    out = torch.full((m + 3, n), 7.0, device=DEV)
+    gemm_tc.linear_bf16(a, w, bias, out, m, 0, False, tile_n=code)
+    gemm_tc.check_status(a.device)
+    assert bool((out[m:] == 7.0).all())
+    torch.testing.assert_close(out[:m].double(), exact, rtol=1e-4, atol=1e-4)
+    again = torch.zeros(m, n, device=DEV)
+    gemm_tc.linear_bf16(a, w, bias, again, m, 0, False, tile_n=code)
+    assert torch.equal(again, out[:m])
+    last = min(70, m - 1)
+    fewer = torch.zeros(last, n, device=DEV)
+    gemm_tc.linear_bf16(a[m - last:].contiguous(), w, bias, fewer, last, 0, False, tile_n=code)
+    assert torch.equal(fewer, out[m - last:m])  # a row's sum does not depend on the batch
+    half = torch.full((m + 3, n), 7.0, dtype=torch.bfloat16, device=DEV)
+    gemm_tc.linear_bf16(a, w, bias, half, m, 1, False, tile_n=code)
+    assert bool((half[m:] == 7.0).all())
+    torch.testing.assert_close(half[:m].double(), plain.gelu(exact, "gelu_new"), rtol=2e-2,
+                               atol=2e-2)
+    acc = torch.ones(m + 3, n, device=DEV)
+    gemm_tc.linear_bf16(a, w, bias, acc, m, 0, True, tile_n=code)
+    assert bool((acc[m:] == 1.0).all())
+    torch.testing.assert_close(acc[:m].double(), exact + 1.0, rtol=1e-4, atol=1e-4)
+    gemm_tc.check_status(a.device)
+
+
 @pytest.mark.parametrize("splits", [-100, -2, -4, -8, 0])
-@pytest.mark.parametrize("m", [1, 8, 16, 17, 40, 64])
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 24, 33, 40, 57, 64])
 def test_linear_tcgen05_few_rows(m, splits):
     """The weight-streaming kernel of decode steps: every padded row count, every K split
     (a negative tile selects it: -100 one CTA per tile, -2/-4/-8 that many cluster CTAs)."""
