@@ -25,6 +25,7 @@
 #include <mutex>
 
 #include "tc_common.cuh"
+#include "attention_decode_mma.cuh"
 
 namespace ayk {
 
@@ -530,6 +531,11 @@ int launch_decode(const void* q, int ld_q, const void* k_pages, const void* v_pa
                          page_shift);
 }
 
+// From this many (row, head) pairs per SM on, bfloat16 rows with a head size the tensor-core
+// kernel is built for go there (attention_decode_mma.cuh): the split-KV kernel above is then
+// bound by instruction issue, not by its chain of dependent steps.
+constexpr int DM_PAIRS_PER_SM = 4;
+
 template <typename T>
 int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v_pages,
                      const int* block_table, int table_stride, const int* request_of_row,
@@ -549,7 +555,7 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
     return AYK_BAD_ALIGNMENT;
   }
   if (num_rows < 0 || num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads ||
-      page_size < 1 || table_stride < 1 || window < 0 || splits < 1) {
+      page_size < 1 || table_stride < 1 || window < 0 || (splits < 1 && splits != -1)) {
     return AYK_BAD_ARGUMENT;
   }
   if (head_dim < 16 || head_dim % 16) return AYK_BAD_ARGUMENT;
@@ -562,6 +568,24 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
   if (((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16) || ((uintptr_t)q % vec) ||
       ((size_t)ld_q * sizeof(T)) % vec) {
     return AYK_BAD_ALIGNMENT;
+  }
+  // splits == -1 asks for the tensor-core kernel (tests); otherwise it is chosen for many rows
+  const bool many = splits == 1 && partial == nullptr &&
+                    (long long)num_rows * num_heads >= (long long)DM_PAIRS_PER_SM * sm_count();
+  if (splits == -1 || many) {
+    if (sizeof(T) == 2 && (head_dim == 64 || head_dim == 128) && partial == nullptr) {
+      if (head_dim == 64) {
+        return launch_decode_mma<64>(q, ld_q, k_pages, v_pages, block_table, table_stride,
+                                     request_of_row, positions, out, ld_out, num_rows, num_heads,
+                                     num_kv_heads, page_size, scale, window, k_new, v_new,
+                                     ld_new, store, stream);
+      }
+      return launch_decode_mma<128>(q, ld_q, k_pages, v_pages, block_table, table_stride,
+                                    request_of_row, positions, out, ld_out, num_rows, num_heads,
+                                    num_kv_heads, page_size, scale, window, k_new, v_new, ld_new,
+                                    store, stream);
+    }
+    if (splits == -1) return AYK_BAD_ARGUMENT;  // asked for, but not this kernel's case
   }
   const int frags = head_dim / 8;
 #define AYK_DECODE(TPK)                                                                        \

@@ -750,6 +750,60 @@ def test_attention_decode_split_kv(dtype, splits, case):
     assert torch.equal(wiped_v.nan_to_num(7.0), v_pages.nan_to_num(7.0))
 
 
+@pytest.mark.parametrize("case", [
+    # lengths, heads, kv_heads, head_dim, page, window
+    ((1000, 17), 25, 25, 64, 16, 0),
+    ((300, 5), 2, 1, 128, 16, 0),
+    ((1, 2, 16, 17, 33, 130), 4, 2, 64, 8, 0),
+    ((100, 257, 3), 4, 4, 64, 16, 24),
+    ((67, 400), 6, 2, 128, 4, 50),
+    ((70, 31, 48), 3, 3, 64, 12, 0),
+])
+def test_attention_decode_on_tensor_cores(case):
+    """The decode kernel for many rows (both products as warp-level MMAs over tiles of 16
+    keys; ``splits=-1`` asks for it whatever the row count): against plain attention, with a
+    padding row, twice in a row, then with each row's own key and value handed in from the
+    projection and stored by the kernel."""
+    ops = _ops()
+    dtype = torch.bfloat16
+    lengths, heads, kv_heads, head_dim, page, window = case
+    rows = (1,) * len(lengths)
+    q, k_pages, v_pages, table, req, pos, seqs = _paged_case(
+        lengths, rows, heads, kv_heads, head_dim, page, dtype, seed=27, boost=(999, 2))
+    n = q.shape[0]
+    q = torch.cat([q[:1], torch.full_like(q[:1], float("nan")), q[1:]])
+    req = torch.cat([req[:1], torch.tensor([-1], dtype=torch.int32, device=DEV), req[1:]])
+    pos = torch.cat([pos[:1], torch.zeros(1, dtype=torch.int32, device=DEV), pos[1:]])
+    scale = 0.9 / math.sqrt(head_dim)
+    expected = _attention_reference(seqs, lengths, rows, heads, kv_heads, scale, window)
+    tol = dict(rtol=2e-2, atol=2e-2)
+    for _ in range(2):
+        out = torch.full((n + 1, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
+        ops.attention_decode(q, k_pages, v_pages, table, req, pos, out, num_heads=heads,
+                             scale=scale, window=window, splits=-1)
+        got = torch.cat([out[:1], out[2:]]).double().cpu()
+        torch.testing.assert_close(got, expected, **tol)
+        assert torch.equal(out[1].float(), torch.zeros(heads * head_dim, device=DEV))
+    kv_width = kv_heads * head_dim
+    k_new = torch.zeros(n + 1, kv_width, dtype=dtype, device=DEV)
+    v_new = torch.zeros_like(k_new)
+    wiped_k, wiped_v = k_pages.clone(), v_pages.clone()
+    for b, length in enumerate(lengths):
+        row = b if b == 0 else b + 1  # the padding row sits at index 1
+        where, slot = int(table[b, (length - 1) // page]), (length - 1) % page
+        k_new[row] = k_pages[where, :, slot].reshape(-1)
+        v_new[row] = v_pages[where, :, slot].reshape(-1)
+        wiped_k[where, :, slot] = float("nan")
+        wiped_v[where, :, slot] = float("nan")
+    out = torch.full((n + 1, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
+    ops.attention_decode(q, wiped_k, wiped_v, table, req, pos, out, num_heads=heads, scale=scale,
+                         window=window, splits=-1, k_new=k_new, v_new=v_new, store=True)
+    got = torch.cat([out[:1], out[2:]]).double().cpu()
+    torch.testing.assert_close(got, expected, **tol)
+    assert torch.equal(wiped_k.nan_to_num(7.0), k_pages.nan_to_num(7.0))
+    assert torch.equal(wiped_v.nan_to_num(7.0), v_pages.nan_to_num(7.0))
+
+
 def test_attention_refuses_what_it_cannot_do():
     ops = _ops()
     from ayaka_b200.errors import BackendError
