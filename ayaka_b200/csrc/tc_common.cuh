@@ -308,6 +308,16 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t address, uint32_t a, uint
                "r"(b), "r"(c), "r"(d)
                : "memory");
 }
+__device__ __forceinline__ void st_cluster_b32(uint32_t address, uint32_t v) {
+  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(address), "r"(v) : "memory");
+}
+// The two halves of a cluster barrier, for CTAs that have something to do in between.
+__device__ __forceinline__ void cluster_arrive_release() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ float ld_cluster_f32(uint32_t address) {
   float v;
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(address) : "memory");

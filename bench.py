@@ -502,6 +502,9 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--layers", type=int, default=48,
                         help="layers to build (GPT-2 XL has 48); sizes of a layer never change")
+    parser.add_argument("--batch", type=int, default=8,
+                        help="requests of the headline decode run (8; other values are for "
+                             "profiling a batch size under ncu)")
     parser.add_argument("--skip-points", action="store_true",
                         help="leave out the batch 1 / batch 64 points and the e2e run")
     parser.add_argument("--no-profile", action="store_true",
@@ -535,22 +538,23 @@ def main() -> int:
     llm = build(cfg, 64, 2048)
     clocks = Clocks()
     clocks.start()
-    main_run = decode_run(llm, cfg, 8, warmup, steps, seed=1)
+    batch = max(1, min(args.batch, 64))
+    main_run = decode_run(llm, cfg, batch, warmup, steps, seed=1)
     clock_record = clocks.stop()
     clock_record["window"] = "prefill, warm-up and timed steps of the batch-8 run"
     prefill = prefill_run(llm, cfg, 2, 5)
     points, e2e, kernels, workloads = {}, None, None, None
     if not args.skip_points:
-        for batch in (1, 64):
-            run = decode_run(llm, cfg, batch, warmup, steps, seed=10 + batch)
-            points[f"decode_b{batch}"] = round(batch * 1000.0 / run["ms"], 1)
-            points[f"decode_b{batch}_ms"] = round(run["ms"], 4)
-            points[f"decode_b{batch}_context"] = round(run["mean_context"], 1)
+        for point in (1, 64):
+            run = decode_run(llm, cfg, point, warmup, steps, seed=10 + point)
+            points[f"decode_b{point}"] = round(point * 1000.0 / run["ms"], 1)
+            points[f"decode_b{point}_ms"] = round(run["ms"], 4)
+            points[f"decode_b{point}_context"] = round(run["mean_context"], 1)
             batch_bytes = layer_weight_bytes(cfg, cfg["n_layer"]) + \
-                batch * run["mean_context"] * kv_bytes_per_token(cfg, cfg["n_layer"])
-            points[f"decode_b{batch}_hbm_frac"] = round(
+                point * run["mean_context"] * kv_bytes_per_token(cfg, cfg["n_layer"])
+            points[f"decode_b{point}_hbm_frac"] = round(
                 batch_bytes / (run["ms"] * 1e-3) / 1e9 / peak["hbm_gbs"], 4)
-        e2e = e2e_run(llm, cfg, 8, 128)
+        e2e = e2e_run(llm, cfg, batch, 128)
     if not args.no_profile:
         from ayaka_b200.kernels import ops
 
@@ -576,17 +580,17 @@ def main() -> int:
 
     layers = cfg["n_layer"]
     step_bytes = layer_weight_bytes(cfg, layers) + \
-        8 * main_run["mean_context"] * kv_bytes_per_token(cfg, layers)
+        batch * main_run["mean_context"] * kv_bytes_per_token(cfg, layers)
     achieved = step_bytes / (main_run["ms"] * 1e-3) / 1e9
     flops = prefill_flops(cfg, layers, 2, cfg["n_positions"])
-    value = 8 * 1000.0 / main_run["ms"]
+    value = batch * 1000.0 / main_run["ms"]
     line = {
-        "metric": METRIC,
+        "metric": METRIC if batch == 8 else METRIC.replace("batch 8", f"batch {batch}"),
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": round(main_run["ms"], 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
-        "config": config_record(cfg, main_run["mean_context"]),
+        "config": {**config_record(cfg, main_run["mean_context"]), "global_batch": batch},
         "prefill": {"value": round(prefill["tokens"] * 1000.0 / prefill["ms"], 1),
                     "tokens": prefill["tokens"], "ms": round(prefill["ms"], 3),
                     "frac": round(flops / (prefill["ms"] * 1e-3) / (peak["bf16_tflops"] * 1e12),
