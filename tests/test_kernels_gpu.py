@@ -5,6 +5,7 @@ every dimension, pages handed out in scrambled order and poisoned with NaN."""
 from __future__ import annotations
 
 import math
+from pathlib import Path
 
 import pytest
 import torch
@@ -911,3 +912,58 @@ def test_decode_chain_same_bits_with_and_without_dependent_launch(rows):
     torch.cuda.synchronize()
     assert bool(torch.isfinite(results[0]).all())
     assert all(torch.equal(results[0], other) for other in results[1:])
+
+
+def test_an_empty_kernel_boundary_costs_about_a_microsecond(tmp_path, capsys):
+    """What a decode step pays for being ≈ 340 kernels and not one: a chain of empty kernels
+    (``tests/csrc/null_chain.cu``: wait for the predecessor, release the successor) replayed
+    from a CUDA graph, with the launch attribute the engine's kernels use and without it.
+    The figures are printed (run with ``-s``); the assertion is only that a boundary stays
+    well under the two microseconds a kernel's own dependent chain takes."""
+    import ctypes
+    import subprocess
+
+    from ayaka_b200.kernels.build import CSRC, _nvcc
+
+    out = tmp_path / "libnull_chain.so"
+    subprocess.run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
+                    "--shared", "-Xcompiler", "-fPIC", "-I", str(CSRC), "-o", str(out),
+                    str(Path(__file__).resolve().parent / "csrc" / "null_chain.cu")], check=True)
+    library = ctypes.CDLL(str(out))
+    sink = torch.zeros(4, dtype=torch.int32, device=DEV)
+    count = 340
+
+    def per_kernel_us(blocks, threads, pdl):
+        library.set_pdl(pdl)
+        side = torch.cuda.Stream()
+
+        def body():
+            status = library.null_chain(count, blocks, threads, ctypes.c_void_p(sink.data_ptr()),
+                                        0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+            assert status == 0
+
+        with torch.cuda.stream(side):
+            body()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                body()
+        graph.replay()
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(10):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            graph.replay()
+            stop.record()
+            torch.cuda.synchronize()
+            best = min(best, start.elapsed_time(stop))
+        return best * 1000 / count
+
+    with capsys.disabled():
+        print()
+        for blocks, threads in ((1, 32), (148, 256), (600, 256), (888, 256)):
+            with_pdl, without = per_kernel_us(blocks, threads, 1), per_kernel_us(blocks, threads, 0)
+            print(f"empty kernel, {blocks} CTAs x {threads}: {with_pdl:.2f} us with programmatic "
+                  f"dependent launch, {without:.2f} us without")
+            assert with_pdl < 2.0
