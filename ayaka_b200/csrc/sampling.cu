@@ -555,6 +555,36 @@ AYK_API int ayk_sample(const float* logits, int ld, int rows, int vocab, const f
                             top_p, min_p, seeds, positions, out);
 }
 
+namespace ayk {
+// x = scale * x, then with cap > 0: x = cap * tanh(x / cap), on rows of fp32 logits in place.
+__global__ void logits_scale_cap_kernel(float* __restrict__ logits, int ld, int vocab,
+                                        float scale, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  float* row = logits + (size_t)blockIdx.y * ld;
+  const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < vocab; c += gridDim.x * blockDim.x) {
+    float v = row[c] * scale;
+    if (cap > 0.f) v = cap * tanhf(v * inv_cap);
+    row[c] = v;
+  }
+}
+}  // namespace ayk
+
+// The head's output as some architectures want it: scaled, then squashed into (-cap, cap).
+AYK_API int ayk_logits_scale_cap(float* logits, int ld, int vocab, int num_rows, float scale,
+                                 float cap, void* stream) {
+  using namespace ayk;
+  if (num_rows == 0) return AYK_OK;
+  if (num_rows < 0 || num_rows > 65535 || vocab < 1 || ld < vocab || logits == nullptr ||
+      cap < 0.f) {
+    return AYK_BAD_ARGUMENT;
+  }
+  const int blocks = (vocab + 1023) / 1024 < 64 ? (vocab + 1023) / 1024 : 64;
+  return launch_kernel(logits_scale_cap_kernel, dim3(blocks, num_rows), dim3(256), 0,
+                       (cudaStream_t)stream, 1, logits, ld, vocab, scale, cap);
+}
+
 // Adjust `num_rows` rows of fp32 logits in place as `desc` says (see logits_adjust_kernel).
 // `mask_scratch` holds num_rows * ceil(vocab / 32) words (needed only by rows with an allowed
 // list; may be null when no row has one).

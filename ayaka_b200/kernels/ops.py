@@ -32,6 +32,7 @@ __all__ = [
     "linear",
     "linear_normed",
     "logits_adjust",
+    "logits_scale_cap",
     "sample",
     "set_pdl",
     "sm_count",
@@ -153,8 +154,8 @@ def _need(op: str, name: str, tensor: torch.Tensor, dtype: torch.dtype | None = 
 
 def embed_rows(table: torch.Tensor, index: torch.Tensor, out: torch.Tensor, *,
                add_table: torch.Tensor | None = None, add_index: torch.Tensor | None = None,
-               bad_index: torch.Tensor) -> None:
-    """``out[i] = table[index[i]] (+ add_table[add_index[i]])`` as fp32 rows.
+               bad_index: torch.Tensor, scale: float = 1.0) -> None:
+    """``out[i] = scale * table[index[i]] (+ add_table[add_index[i]])`` as fp32 rows.
 
     ``bad_index`` is one int32 on the device that the kernel sets to 1 if an id is outside
     its table.
@@ -183,8 +184,8 @@ def embed_rows(table: torch.Tensor, index: torch.Tensor, out: torch.Tensor, *,
     fn = getattr(library("embed"), name)
     status = fn(_ptr(table), _ptr(index), c_int(table.shape[0]), _ptr(add_table),
                 _ptr(add_index), c_int(0 if add_table is None else add_table.shape[0]),
-                _ptr(out), c_int(out.stride(0)), c_int(rows), c_int(width), _ptr(bad_index),
-                _stream())
+                _ptr(out), c_int(out.stride(0)), c_int(rows), c_int(width), c_float(scale),
+                _ptr(bad_index), _stream())
     check(status, op)
 
 
@@ -627,6 +628,21 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor 
 
 #: words of a row's header in the descriptor of :func:`logits_adjust`
 ADJUST_WORDS = 16
+
+
+def logits_scale_cap(logits: torch.Tensor, *, rows: int, scale: float = 1.0,
+                     softcap: float = 0.0) -> None:
+    """``x = scale * x`` and then, with ``softcap`` > 0, ``x = softcap * tanh(x / softcap)``
+    on ``rows`` rows of fp32 ``logits`` in place (what some architectures do to the head's
+    output; GPT-2 does neither and never launches this)."""
+    op = "logits_scale_cap"
+    _need(op, "logits", logits, torch.float32, 2)
+    if rows < 0 or rows > logits.shape[0] or softcap < 0:
+        raise BackendError(f"{op}: rows={rows}, softcap={softcap} do not fit")
+    status = library("sampling").ayk_logits_scale_cap(
+        _ptr(logits), c_int(logits.stride(0)), c_int(logits.shape[1]), c_int(rows),
+        c_float(scale), c_float(softcap), _stream())
+    check(status, op)
 
 
 def logits_adjust(logits: torch.Tensor, desc: torch.Tensor, num_rows: int,

@@ -59,15 +59,17 @@ class NoPositions(PositionEncoding):
 
 @register_part("embedding", "token")
 class TokenEmbedding(Part):
-    """Row gather from ``[vocab_size, width]`` into the fp32 residual stream.
+    """Row gather from ``[vocab_size, width]`` into the fp32 residual stream, times ``scale``.
 
-    Spec parameters: ``vocab_size``, ``width``.
+    Spec parameters: ``vocab_size``, ``width``, ``scale`` (a factor on the table's rows, in
+    fp32 inside the kernel; 1 when absent, as for GPT-2).
     """
 
     def __init__(self, spec: PartSpec, ctx: BuildContext) -> None:
         super().__init__(ctx)
         self.vocab_size = int(spec.vocab_size)  # type: ignore[arg-type]
         self.width = int(spec.width)  # type: ignore[arg-type]
+        self.scale = float(spec.get("scale", 1.0))  # type: ignore[arg-type]
         self.weight = self.add_param("weight", (self.vocab_size, self.width), "table")
 
     def forward(self, step: StepContext, out: torch.Tensor,
@@ -76,7 +78,7 @@ class TokenEmbedding(Part):
         ops.embed_rows(self.weight, step.tokens[:step.num_rows], out,
                        add_table=table,
                        add_index=None if index is None else index[:step.num_rows],
-                       bad_index=step.bad_index)
+                       bad_index=step.bad_index, scale=self.scale)
 
 
 @register_part("head", "linear")
@@ -84,7 +86,9 @@ class LinearHead(Part):
     """``logits = hidden @ weight.T`` in fp32, no bias; ``weight`` is the embedding table when
     tied (``python/ayaka/layers/embedding/token.py:81-100``).
 
-    Spec parameters: ``vocab_size``, ``width``, ``tied`` (bool).
+    Spec parameters: ``vocab_size``, ``width``, ``tied`` (bool); ``logit_scale`` (a factor on
+    the logits, 1 when absent) and ``logit_softcap`` (``cap * tanh(x / cap)`` after the
+    factor, off when absent or 0): GPT-2 has neither, and then nothing more is launched.
     """
 
     def __init__(self, spec: PartSpec, ctx: BuildContext,
@@ -92,6 +96,8 @@ class LinearHead(Part):
         super().__init__(ctx)
         self.vocab_size = int(spec.vocab_size)  # type: ignore[arg-type]
         self.tied = bool(spec.get("tied", True))
+        self.logit_scale = float(spec.get("logit_scale", 1.0))  # type: ignore[arg-type]
+        self.logit_softcap = float(spec.get("logit_softcap", 0.0))  # type: ignore[arg-type]
         if self.tied:
             if embedding is None:
                 raise ValueError("a tied head needs the embedding it shares")
@@ -102,6 +108,12 @@ class LinearHead(Part):
 
     def forward(self, hidden: torch.Tensor, logits: torch.Tensor, *, count: int) -> None:
         ops.linear(hidden, self.weight, None, logits, rows=count)
+        self._finish(logits, count)
+
+    def _finish(self, logits: torch.Tensor, count: int) -> None:
+        if self.logit_scale != 1.0 or self.logit_softcap > 0.0:
+            ops.logits_scale_cap(logits, rows=count, scale=self.logit_scale,
+                                 softcap=self.logit_softcap)
 
     def forward_normed(self, norm: Part, residual: torch.Tensor, rows: torch.Tensor,
                        scratch: torch.Tensor, logits: torch.Tensor, *, count: int) -> None:
@@ -109,3 +121,4 @@ class LinearHead(Part):
         ops.linear_normed(residual, norm.weight, norm.bias, norm.eps,  # type: ignore
                           self.weight, None, logits, scratch=scratch, count=count,
                           row_index=rows)
+        self._finish(logits, count)

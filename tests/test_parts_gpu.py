@@ -5,6 +5,7 @@ touching the package's files."""
 
 from __future__ import annotations
 
+import dataclasses
 import math
 
 import pytest
@@ -375,3 +376,27 @@ def test_an_unknown_part_kind_says_what_is_registered():
     with pytest.raises(ConfigError) as caught:
         build_part("mixer", "mamba", PartSpec("mamba"), BuildContext(torch.float32, DEV))
     assert "attention" in str(caught.value) and "toy_decay" in str(caught.value)
+
+
+def test_an_embedding_scale_and_a_logit_cap_are_parameters_of_the_parts():
+    """What architectures other than GPT-2 do at the two ends of the model: the token rows
+    times a factor (here sqrt(width)) before the positions are added, and the head's logits
+    times a factor and squashed into (-cap, cap). Both are parameters of the embedding and
+    head parts; a spec that sets them runs with no change to the package."""
+    width, vocab = 48, 61
+    scale, logit_scale, cap = math.sqrt(width), 0.5, 3.0
+    spec = model_spec([attention_layer(width, 3, 3, 16, 0.25, 64)], [Run(0)], width, vocab=vocab)
+    spec = dataclasses.replace(
+        spec, embedding=PartSpec("token", vocab_size=vocab, width=width, scale=scale),
+        head=PartSpec("linear", vocab_size=vocab, width=width, tied=True,
+                      logit_scale=logit_scale, logit_softcap=cap))
+    for dtype, tol in (("float32", 1e-4), ("bfloat16", 3e-2)):
+        core, w = core_of(spec, dtype=dtype)
+        tokens = [(5 * i + 1) % vocab for i in range(40)]
+        x = w["embedding.weight"][tokens] * scale + w["position.weight"][:len(tokens)]
+        x, _ = plain_attention_layer(x, w, "layers.0.", 3, 3, 16, 0.25, "gelu_tanh")
+        expected = cap * torch.tanh(plain_head(x, w) * logit_scale / cap)
+        got = feed(core, "s", tokens, [17, 1, 22])
+        # (as in the engine tests: a fraction of the logit scale, which the cap bounds)
+        torch.testing.assert_close(got, expected.float(), rtol=tol, atol=tol * cap)
+        assert float(got.abs().max()) < cap
