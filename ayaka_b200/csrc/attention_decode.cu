@@ -531,10 +531,12 @@ int launch_decode(const void* q, int ld_q, const void* k_pages, const void* v_pa
                          page_shift);
 }
 
-// From this many (row, head) pairs per SM on, bfloat16 rows with a head size the tensor-core
-// kernel is built for go there (attention_decode_mma.cuh): the split-KV kernel above is then
-// bound by instruction issue, not by its chain of dependent steps.
-constexpr int DM_PAIRS_PER_SM = 4;
+// From one (row, head) pair per SM on, bfloat16 rows with a head size the tensor-core kernel
+// is built for go there (attention_decode_mma.cuh): it needs no cluster to merge its shares
+// and a sixth of the instructions. Measured, GPT-2 XL decode step: 8 requests (200 pairs)
+// 1.48 against 1.64 ms, 64 requests 4.61 against 4.82; one request (25 pairs, where the
+// split-KV kernel spreads a pair over eight CTAs) 1.25 against 1.20, hence the threshold.
+constexpr int DM_PAIRS_PER_SM = 1;
 
 template <typename T>
 int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v_pages,
@@ -555,7 +557,8 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
     return AYK_BAD_ALIGNMENT;
   }
   if (num_rows < 0 || num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads ||
-      page_size < 1 || table_stride < 1 || window < 0 || (splits < 1 && splits != -1)) {
+      page_size < 1 || table_stride < 1 || window < 0 ||
+      (splits < 1 && splits != -1 && splits != -4 && splits != -8)) {
     return AYK_BAD_ARGUMENT;
   }
   if (head_dim < 16 || head_dim % 16) return AYK_BAD_ARGUMENT;
@@ -569,23 +572,26 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
       ((size_t)ld_q * sizeof(T)) % vec) {
     return AYK_BAD_ALIGNMENT;
   }
-  // splits == -1 asks for the tensor-core kernel (tests); otherwise it is chosen for many rows
-  const bool many = splits == 1 && partial == nullptr &&
-                    (long long)num_rows * num_heads >= (long long)DM_PAIRS_PER_SM * sm_count();
-  if (splits == -1 || many) {
+  // splits == -1 (or -4, -8: with that many warps per CTA) asks for the tensor-core kernel
+  // (tests); otherwise it is chosen for many rows, whatever `splits` says
+  const long long pairs = (long long)num_rows * num_heads;
+  const bool asked = splits == -1 || splits == -4 || splits == -8;
+  const bool many = partial == nullptr && pairs >= (long long)DM_PAIRS_PER_SM * sm_count();
+  if (asked || many) {
     if (sizeof(T) == 2 && (head_dim == 64 || head_dim == 128) && partial == nullptr) {
-      if (head_dim == 64) {
-        return launch_decode_mma<64>(q, ld_q, k_pages, v_pages, block_table, table_stride,
-                                     request_of_row, positions, out, ld_out, num_rows, num_heads,
-                                     num_kv_heads, page_size, scale, window, k_new, v_new,
-                                     ld_new, store, stream);
-      }
-      return launch_decode_mma<128>(q, ld_q, k_pages, v_pages, block_table, table_stride,
-                                    request_of_row, positions, out, ld_out, num_rows, num_heads,
-                                    num_kv_heads, page_size, scale, window, k_new, v_new, ld_new,
-                                    store, stream);
+      const int warps = splits == -4 ? 4 : (splits == -8 ? 8 : decode_mma_warps(pairs, head_dim));
+#define AYK_DECODE_MMA(HD, W)                                                                  \
+  return launch_decode_mma<HD, W>(q, ld_q, k_pages, v_pages, block_table, table_stride,       \
+                                  request_of_row, positions, out, ld_out, num_rows, num_heads, \
+                                  num_kv_heads, page_size, scale, window, k_new, v_new,        \
+                                  ld_new, store, stream)
+      if (head_dim == 64 && warps == 8) AYK_DECODE_MMA(64, 8);
+      if (head_dim == 64) AYK_DECODE_MMA(64, 4);
+      if (warps == 8) AYK_DECODE_MMA(128, 8);
+      AYK_DECODE_MMA(128, 4);
+#undef AYK_DECODE_MMA
     }
-    if (splits == -1) return AYK_BAD_ARGUMENT;  // asked for, but not this kernel's case
+    if (asked) return AYK_BAD_ARGUMENT;  // asked for, but not this kernel's case
   }
   const int frags = head_dim / 8;
 #define AYK_DECODE(TPK)                                                                        \

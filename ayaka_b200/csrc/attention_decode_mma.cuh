@@ -11,11 +11,13 @@
 // operand is the score accumulator as it lies in registers. About 30 instructions per 16
 // keys instead of about 180.
 //
-// A CTA of four warps serves one (row, head); warp w takes tiles w, w + 4, ... of the row's
-// keys, each with its own ring of three 16-key stages of K and V in shared memory (cp.async,
-// 128-byte rows with the usual XOR swizzle for ldmatrix), started before the dependency wait
-// for the keys of earlier steps. The four partial results merge through shared memory in warp
-// order. The row's own key and value come from the projection's output (k_new / v_new) and,
+// A CTA of four or eight warps serves one (row, head); warp w takes tiles w, w + WARPS, ... of
+// the row's keys, each with its own ring of three 16-key stages of K and V in shared memory
+// (cp.async, 128-byte rows with the usual XOR swizzle for ldmatrix), started before the
+// dependency wait for the keys of earlier steps. The warps' partial results merge through
+// shared memory in warp order. Eight warps finish a (row, head) in about half the time but
+// only two such CTAs fit an SM where four of the four-warp kind do; the host picks by which
+// of the two needs less time for all its rounds over the SMs (decode_mma_warps). The row's own key and value come from the projection's output (k_new / v_new) and,
 // with `store`, are written to the cache by the warp that owns the last tile.
 #pragma once
 
@@ -23,14 +25,7 @@
 
 namespace ayk {
 
-#ifndef AYK_DM_WARPS
-#define AYK_DM_WARPS 4
-#endif
-#ifndef AYK_DM_STAGES
-#define AYK_DM_STAGES 3
-#endif
-constexpr int DM_WARPS = AYK_DM_WARPS;
-constexpr int DM_STAGES = AYK_DM_STAGES;
+constexpr int DM_STAGES = 3;
 constexpr int DM_TILE = 16;  // keys per tile
 
 __device__ __forceinline__ void dm_cp_async_16(void* dst, const void* src, bool valid) {
@@ -70,7 +65,7 @@ __device__ __forceinline__ uint32_t dm_pack(float lo, float hi) {
 
 // grid (num_heads, num_rows); HD = head size (64 or 128). Shared memory: DM_WARPS rings of
 // DM_STAGES x (K tile + V tile) of 16 x HD bfloat16, then the merge area.
-template <int HD>
+template <int HD, int DM_WARPS>
 __global__ void __launch_bounds__(DM_WARPS * 32)
 attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
                             const __nv_bfloat16* __restrict__ k_pages,
@@ -289,7 +284,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   }
 }
 
-template <int HD>
+template <int HD, int DM_WARPS>
 int launch_decode_mma(const void* q, int ld_q, const void* k_pages, const void* v_pages,
                       const int* block_table, int table_stride, const int* request_of_row,
                       const int* positions, void* out, int ld_out, int num_rows, int num_heads,
@@ -301,7 +296,7 @@ int launch_decode_mma(const void* q, int ld_q, const void* k_pages, const void* 
                       (size_t)DM_WARPS * (HD + 2) * sizeof(float);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD>,
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, DM_WARPS>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -311,13 +306,28 @@ int launch_decode_mma(const void* q, int ld_q, const void* k_pages, const void* 
     page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
   }
-  return launch_kernel(attention_decode_mma_kernel<HD>, dim3(num_heads, num_rows), dim3(DM_WARPS * 32),
+  return launch_kernel(attention_decode_mma_kernel<HD, DM_WARPS>, dim3(num_heads, num_rows),
+                       dim3(DM_WARPS * 32),
                        smem, stream, 1, (const bf*)q, ld_q, (const bf*)k_pages,
                        (const bf*)v_pages, block_table, table_stride, request_of_row, positions,
                        (bf*)out, ld_out, num_kv_heads, num_heads / num_kv_heads, page_size,
                        page_shift, scale, window, (const bf*)k_new, (const bf*)v_new, ld_new,
                        store ? (bf*)const_cast<void*>(k_pages) : (bf*)nullptr,
                        store ? (bf*)const_cast<void*>(v_pages) : (bf*)nullptr);
+}
+
+// Four or eight warps per (row, head): the CTAs of either kind make ceil(pairs / resident)
+// rounds over the device (resident: shared memory allows 4 four-warp or 2 eight-warp CTAs of
+// head size 64 per SM, half as many of head size 128), and a round of eight-warp CTAs takes
+// about 0.55 of a round of four-warp ones. Measured, GPT-2 XL, decode step in ms with four /
+// eight warps: 8 requests 1.66 / 1.48, 16: 2.18 / 2.23, 32: 3.39 / 3.23, 64: 4.61 / 4.91; the
+// rule picks the faster of each.
+inline int decode_mma_warps(long long pairs, int head_dim) {
+  const long long sms = sm_count();
+  const long long per_sm4 = head_dim <= 64 ? 4 : 2, per_sm8 = head_dim <= 64 ? 2 : 1;
+  const long long rounds4 = (pairs + per_sm4 * sms - 1) / (per_sm4 * sms);
+  const long long rounds8 = (pairs + per_sm8 * sms - 1) / (per_sm8 * sms);
+  return rounds8 * 55 < rounds4 * 100 ? 8 : 4;
 }
 
 }  // namespace ayk

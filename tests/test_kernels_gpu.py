@@ -760,9 +760,11 @@ def test_attention_decode_split_kv(dtype, splits, case):
     ((67, 400), 6, 2, 128, 4, 50),
     ((70, 31, 48), 3, 3, 64, 12, 0),
 ])
-def test_attention_decode_on_tensor_cores(case):
+@pytest.mark.parametrize("ask", [-4, -8])
+def test_attention_decode_on_tensor_cores(case, ask):
     """The decode kernel for many rows (both products as warp-level MMAs over tiles of 16
-    keys; ``splits=-1`` asks for it whatever the row count): against plain attention, with a
+    keys; ``splits=-4`` / ``-8`` ask for it with four / eight warps per (row, head) whatever
+    the row count): against plain attention, with a
     padding row, twice in a row, then with each row's own key and value handed in from the
     projection and stored by the kernel."""
     ops = _ops()
@@ -781,7 +783,7 @@ def test_attention_decode_on_tensor_cores(case):
     for _ in range(2):
         out = torch.full((n + 1, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
         ops.attention_decode(q, k_pages, v_pages, table, req, pos, out, num_heads=heads,
-                             scale=scale, window=window, splits=-1)
+                             scale=scale, window=window, splits=ask)
         got = torch.cat([out[:1], out[2:]]).double().cpu()
         torch.testing.assert_close(got, expected, **tol)
         assert torch.equal(out[1].float(), torch.zeros(heads * head_dim, device=DEV))
@@ -798,7 +800,7 @@ def test_attention_decode_on_tensor_cores(case):
         wiped_v[where, :, slot] = float("nan")
     out = torch.full((n + 1, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
     ops.attention_decode(q, wiped_k, wiped_v, table, req, pos, out, num_heads=heads, scale=scale,
-                         window=window, splits=-1, k_new=k_new, v_new=v_new, store=True)
+                         window=window, splits=ask, k_new=k_new, v_new=v_new, store=True)
     got = torch.cat([out[:1], out[2:]]).double().cpu()
     torch.testing.assert_close(got, expected, **tol)
     assert torch.equal(wiped_k.nan_to_num(7.0), k_pages.nan_to_num(7.0))
