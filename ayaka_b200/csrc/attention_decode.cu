@@ -312,7 +312,7 @@ attention_decode_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__
   // 64 rows (12 batches a share: 114.4 against 113.0), hence the limit.
   const bool one_more = DEC_DEPTH < early && num_batches <= 4;
   if (one_more) issue(k_lo + DEC_DEPTH * STEP, DEC_DEPTH);
-  pdl_wait();
+  pdl_wait_for(q, k_new, v_new, k_pages, v_pages);
   Raw8<T> q_raw;
   q_raw.zero();
   if (dims_ok) q_raw.fetch(q + (size_t)row * ld_q + (size_t)head * head_dim + sub * 8);
@@ -531,12 +531,19 @@ int launch_decode(const void* q, int ld_q, const void* k_pages, const void* v_pa
                          page_shift);
 }
 
-// From one (row, head) pair per SM on, bfloat16 rows with a head size the tensor-core kernel
-// is built for go there (attention_decode_mma.cuh): it needs no cluster to merge its shares
-// and a sixth of the instructions. Measured, GPT-2 XL decode step: 8 requests (200 pairs)
-// 1.48 against 1.64 ms, 64 requests 4.61 against 4.82; one request (25 pairs, where the
-// split-KV kernel spreads a pair over eight CTAs) 1.25 against 1.20, hence the threshold.
-constexpr int DM_PAIRS_PER_SM = 1;
+// bfloat16 rows with a head size the tensor-core kernel is built for go there
+// (attention_decode_mma.cuh) whatever their number: it needs no cluster to merge its shares
+// and a sixth of the instructions. Measured, GPT-2 XL decode step in ms against the split-KV
+// kernel above: 1 request 1.16 / 1.22, 2: 1.20 / 1.27, 4: 1.32 / 1.50, 8: 1.48 / 1.64, 64:
+// 4.61 / 4.82. The split-KV kernel serves float32, the other head sizes and callers that bring
+// scratch.
+
+// Off: every call goes to the split-KV kernel (tests of that kernel at the sizes the
+// tensor-core kernel would take; measurements of one against the other).
+inline int& decode_tensor_cores() {
+  static int on = 1;
+  return on;
+}
 
 template <typename T>
 int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v_pages,
@@ -558,7 +565,7 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
   }
   if (num_rows < 0 || num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads ||
       page_size < 1 || table_stride < 1 || window < 0 ||
-      (splits < 1 && splits != -1 && splits != -4 && splits != -8)) {
+      (splits < 1 && splits != -1 && splits != -4 && splits != -8 && splits != -16)) {
     return AYK_BAD_ARGUMENT;
   }
   if (head_dim < 16 || head_dim % 16) return AYK_BAD_ARGUMENT;
@@ -572,19 +579,21 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
       ((size_t)ld_q * sizeof(T)) % vec) {
     return AYK_BAD_ALIGNMENT;
   }
-  // splits == -1 (or -4, -8: with that many warps per CTA) asks for the tensor-core kernel
-  // (tests); otherwise it is chosen for many rows, whatever `splits` says
+  // splits == -1 (or -4, -8, -16: with that many warps per CTA) asks for the tensor-core
+  // kernel and fails if it does not serve the case (tests); otherwise it is taken whenever
+  // it serves the case, whatever `splits` says
   const long long pairs = (long long)num_rows * num_heads;
-  const bool asked = splits == -1 || splits == -4 || splits == -8;
-  const bool many = partial == nullptr && pairs >= (long long)DM_PAIRS_PER_SM * sm_count();
-  if (asked || many) {
+  const bool asked = splits == -1 || splits == -4 || splits == -8 || splits == -16;
+  if (asked || (partial == nullptr && decode_tensor_cores())) {
     if (sizeof(T) == 2 && (head_dim == 64 || head_dim == 128) && partial == nullptr) {
-      const int warps = splits == -4 ? 4 : (splits == -8 ? 8 : decode_mma_warps(pairs, head_dim));
+      int warps = splits < -1 ? -splits : decode_mma_warps(pairs, head_dim);
+      if (head_dim > 64 && warps > 8) warps = 8;  // sixteen rings of head size 128 do not fit
 #define AYK_DECODE_MMA(HD, W)                                                                  \
   return launch_decode_mma<HD, W>(q, ld_q, k_pages, v_pages, block_table, table_stride,       \
                                   request_of_row, positions, out, ld_out, num_rows, num_heads, \
                                   num_kv_heads, page_size, scale, window, k_new, v_new,        \
                                   ld_new, store, stream)
+      if (head_dim == 64 && warps == 16) AYK_DECODE_MMA(64, 16);
       if (head_dim == 64 && warps == 8) AYK_DECODE_MMA(64, 8);
       if (head_dim == 64) AYK_DECODE_MMA(64, 4);
       if (warps == 8) AYK_DECODE_MMA(128, 8);
@@ -610,6 +619,7 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
 }  // namespace ayk
 
 AYK_API void ayk_set_pdl(int on) { ayk::pdl_enabled() = on; }
+AYK_API void ayk_set_decode_tensor_cores(int on) { ayk::decode_tensor_cores() = on; }
 
 // type: 0 = float32, 1 = bfloat16. Up to 8 splits need no scratch (pass null for `partial`
 // and `tickets`); with scratch, `partial` holds num_rows * num_heads * splits * (head_dim + 2)

@@ -11,10 +11,10 @@
 // operand is the score accumulator as it lies in registers. About 30 instructions per 16
 // keys instead of about 180.
 //
-// A CTA of four or eight warps serves one (row, head); warp w takes tiles w, w + WARPS, ... of
+// A CTA of four, eight or sixteen warps serves one (row, head); warp w takes tiles w, w + WARPS, ... of
 // the row's keys, each with its own ring of three 16-key stages of K and V in shared memory
 // (cp.async, 128-byte rows with the usual XOR swizzle for ldmatrix), started before the
-// dependency wait for the keys of earlier steps. The warps' partial results merge through
+// dependency wait for the keys of earlier steps (when the row's own key comes from k_new). The warps' partial results merge through
 // shared memory in warp order. Eight warps finish a (row, head) in about half the time but
 // only two such CTAs fit an SM where four of the four-warp kind do; the host picks by which
 // of the two needs less time for all its rounds over the SMs (decode_mma_warps). The row's own key and value come from the projection's output (k_new / v_new) and,
@@ -138,14 +138,16 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
     }
   };
 
-  // keys of earlier steps do not depend on the kernel ahead: the first stages start now
+  // Keys of earlier steps do not depend on the kernel ahead: the first stages start before
+  // the wait. That holds only while the row's own key comes from k_new; when it is read from
+  // the cache, the kernel ahead is the one that wrote it there, and the wait comes first.
+  if (!patch) pdl_wait_for(q, k_pages, v_pages);
 #pragma unroll
   for (int i = 0; i < DM_STAGES - 1; ++i) {
     if (i < my_tiles) issue(i);
     dm_commit();
   }
-
-  pdl_wait();
+  if (patch) pdl_wait_for(q, k_new, v_new);
 
   // the query row as the A operand: rows other than row 0 of the 16 are zero
   uint32_t qa[KSTEPS][2];
@@ -250,7 +252,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
     __syncwarp();  // the stage may be refilled by the next iteration's copies
   }
 
-  // ---- merge the four warps' shares (warp order) -----------------------------------------
+  // ---- merge the warps' shares (warp order) -----------------------------------------
   run_sum += __shfl_xor_sync(0xffffffffu, run_sum, 1);
   run_sum += __shfl_xor_sync(0xffffffffu, run_sum, 2);
   float* mine = merge + warp * (HD + 2);
@@ -316,14 +318,17 @@ int launch_decode_mma(const void* q, int ld_q, const void* k_pages, const void* 
                        store ? (bf*)const_cast<void*>(v_pages) : (bf*)nullptr);
 }
 
-// Four or eight warps per (row, head): the CTAs of either kind make ceil(pairs / resident)
-// rounds over the device (resident: shared memory allows 4 four-warp or 2 eight-warp CTAs of
-// head size 64 per SM, half as many of head size 128), and a round of eight-warp CTAs takes
-// about 0.55 of a round of four-warp ones. Measured, GPT-2 XL, decode step in ms with four /
-// eight warps: 8 requests 1.66 / 1.48, 16: 2.18 / 2.23, 32: 3.39 / 3.23, 64: 4.61 / 4.91; the
-// rule picks the faster of each.
+// Warps per (row, head). With few pairs (at most two for every five SMs) sixteen: the pair's
+// keys are then spread over as many warps as one CTA can hold rings for. Else four or eight:
+// the CTAs of either kind make ceil(pairs / resident) rounds over the device (shared memory
+// allows 4 four-warp or 2 eight-warp CTAs of head size 64 per SM, half as many of head size
+// 128), and a round of eight-warp CTAs takes about 0.55 of a round of four-warp ones.
+// Measured, GPT-2 XL (25 heads), decode step in ms with four / eight / sixteen warps: 1
+// request - / 1.25 / 1.16, 2: - / 1.23 / 1.20, 8: 1.66 / 1.48 / 1.62, 16: 2.18 / 2.23 / -,
+// 32: 3.39 / 3.23 / -, 64: 4.61 / 4.91 / 5.86; the rule picks the fastest of each.
 inline int decode_mma_warps(long long pairs, int head_dim) {
   const long long sms = sm_count();
+  if (head_dim <= 64 && pairs * 5 <= 2 * sms) return 16;
   const long long per_sm4 = head_dim <= 64 ? 4 : 2, per_sm8 = head_dim <= 64 ? 2 : 1;
   const long long rounds4 = (pairs + per_sm4 * sms - 1) / (per_sm4 * sms);
   const long long rounds8 = (pairs + per_sm8 * sms - 1) / (per_sm8 * sms);

@@ -109,7 +109,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   __nv_bfloat16* v_s = k_s + 2 * PF_TILE;   // two stages
 
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_for(q, k_pages, v_pages);
   // Which request and which 64-row tile of it. Heads run along grid.x and tiles along grid.y
   // from the last tile down: a tile's work grows with its position in the sequence, and the
   // longest tiles must start first or they finish alone at the end.

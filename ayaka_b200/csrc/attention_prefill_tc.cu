@@ -222,7 +222,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_for(q, k_pages, v_pages);
 
   // Which request and which 256-row tile of it: heads along grid.x, tiles along grid.y from
   // the last one down (the longest first).

@@ -52,7 +52,7 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
   __shared__ float p_s[ATT_WARPS][32];
   __shared__ long long off_s[ATT_WARPS][32];
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_for(q, k_pages, v_pages);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * ATT_WARPS + warp;
   const int head = blockIdx.y;
@@ -134,7 +134,7 @@ __global__ void kv_store_kernel(const T* __restrict__ k, const T* __restrict__ v
                                 T* __restrict__ v_pages, int num_kv_heads, int head_dim,
                                 int page_size) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_for(k, v);
   const int row = blockIdx.x;
   const int slot = slot_mapping[row];
   if (slot < 0) return;
@@ -160,7 +160,7 @@ kv_store_wide_kernel(const T* __restrict__ k, const T* __restrict__ v, int ld_kv
   pdl_launch_dependents();
   const int row = blockIdx.x;
   const int slot = slot_mapping[row];  // the step's metadata: not written by the kernel ahead
-  pdl_wait();
+  pdl_wait_for(k, v);
   if (slot < 0) return;
   const int page = slot / page_size, within = slot % page_size;
   const int pieces = num_kv_heads * head_dim / EL;

@@ -101,9 +101,29 @@ __device__ __forceinline__ float activate_to_bf16(float x, int act) {
 // predecessor in the stream is still running; pdl_wait() blocks until the predecessor has
 // finished and its writes are visible, so everything before it (barrier set-up, tensor-memory
 // allocation, weight prefetch) overlaps the predecessor's tail. Every kernel launched through
-// launch_kernel() calls pdl_wait() before it touches anything another kernel produces or
-// reads, which keeps the chain transitive.
+// launch_kernel() calls pdl_wait() (pdl_wait_for() where it then reads through read-only
+// pointers) before it touches anything another kernel produces or reads, which keeps the
+// chain transitive.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// The wait, with the pointers to what the kernel ahead wrote passed through it. A load through
+// a const __restrict__ pointer (or __ldg) promises the compiler that nothing writes that
+// memory while the kernel runs, so it may be started above the wait's "memory" clobber, where
+// a kernel that begins before its predecessor ends reads what is not written yet (seen: the
+// query loads of the tensor-core decode attention, moved up beside its prefetch of old keys,
+// gave wrong rows in about one run of three on a two-layer model). An address that is the
+// output of a volatile asm statement behind the wait cannot be formed earlier.
+template <typename P>
+__device__ __forceinline__ void pdl_behind_wait(P& pointer) {  // P: a (restrict) pointer type
+  static_assert(sizeof(P) == 8, "pointers only");
+  unsigned long long bits = reinterpret_cast<unsigned long long>(pointer);
+  asm volatile("" : "+l"(bits)::"memory");
+  pointer = reinterpret_cast<P>(bits);
+}
+template <typename... P>
+__device__ __forceinline__ void pdl_wait_for(P&... pointers) {
+  pdl_wait();
+  (pdl_behind_wait(pointers), ...);
+}
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }

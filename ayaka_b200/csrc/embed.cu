@@ -12,7 +12,7 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
                                   float* __restrict__ out, int ld_out, int width, float scale,
                                   int* __restrict__ bad_index) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_for(index, add_index);  // a graph's ids come from the kernel that advanced them
   const int row = blockIdx.x;
   int id = index[row];
   if (id < 0 || id >= table_rows) {

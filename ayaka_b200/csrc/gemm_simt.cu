@@ -20,7 +20,7 @@ gemm_simt_kernel(const TA* __restrict__ a, int lda, const TW* __restrict__ w, in
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_for(a);
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int ty = tid >> 4, tx = tid & 15;

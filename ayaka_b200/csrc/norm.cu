@@ -13,7 +13,7 @@ __global__ void layer_norm_kernel(const float* __restrict__ x, int ld_x,
                                   TOut* __restrict__ out, int ld_out, int width) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_for(x);
   const int r = blockIdx.x;
   const float* src = x + (size_t)(rows != nullptr ? rows[r] : r) * ld_x;
   float s = 0.f;
@@ -71,7 +71,7 @@ layer_norm_held_kernel(const float* __restrict__ x, int ld_x, const int* __restr
       if (beta != nullptr) b[i] = __ldg(reinterpret_cast<const float4*>(beta + c));
     }
   }
-  pdl_wait();
+  pdl_wait_for(x);
   const float* src = x + (size_t)row * ld_x;
   float4 held[VEC];
   float s = 0.f;

@@ -58,7 +58,7 @@ argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restri
   __shared__ float sv[8];
   __shared__ int si[8];
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_for(logits);
   const int best = block_argmax(logits + (size_t)blockIdx.x * ld, vocab, sv, si);
   if (threadIdx.x == 0) out[blockIdx.x] = best;
 }
@@ -72,7 +72,7 @@ argmax_parts_kernel(const float* __restrict__ logits, int ld, int vocab, int par
   __shared__ float sv[8];
   __shared__ int si[8];
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_for(logits);
   const int row = blockIdx.x, part = blockIdx.y;
   const int span = (vocab + parts - 1) / parts;
   const int lo = part * span;
@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(32)
 argmax_fold_kernel(const float* __restrict__ part_value, const int* __restrict__ part_id,
                    int parts, int vocab, int* __restrict__ out) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_for(part_value, part_id);
   const int row = blockIdx.x;
   float bv = -INFINITY;
   int bi = vocab;
@@ -323,7 +323,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
   extern __shared__ __align__(16) unsigned char sample_smem[];
   SampleShared& sh = *reinterpret_cast<SampleShared*>(sample_smem);
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait_for(logits);
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * ld;
   const float temp = temperature[r];

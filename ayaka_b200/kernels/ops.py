@@ -34,6 +34,7 @@ __all__ = [
     "logits_adjust",
     "logits_scale_cap",
     "sample",
+    "set_decode_tensor_cores",
     "set_pdl",
     "sm_count",
     "timed",
@@ -116,6 +117,13 @@ def set_pdl(enabled: bool) -> None:
     from ayaka_b200.kernels import lib
 
     lib.set_pdl(enabled)
+
+
+def set_decode_tensor_cores(enabled: bool) -> None:
+    """Let decode attention choose its tensor-core kernel where that serves the case (the
+    default), or keep every call on the split-KV kernel (tests of that kernel at head sizes
+    64 and 128 in bfloat16, and measurements of one kernel against the other)."""
+    library("attention_decode").ayk_set_decode_tensor_cores(c_int(1 if enabled else 0))
 
 
 def launch_count() -> int:

@@ -255,6 +255,29 @@ def test_graph_buckets_of_32_and_64_rows_against_plain(models, live, dtype, slac
                 (index, token)
 
 
+# ---- kernels that start before their predecessor has ended -------------------------------------
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_the_same_steps_give_the_same_bits_every_time(models, name):
+    """Every kernel may start while the one ahead still runs and waits for it before it reads
+    what that one writes. A load that slips ahead of the wait reads the layer before, or the
+    step before, now and then: two layers launched from the C++ host code run close enough
+    behind one another for that to show (it did: one run in three, when the compiler moved
+    the query loads of the tensor-core decode attention above the wait), and nothing in the
+    engine is allowed to depend on timing, so eight runs of the decode-heavy schedule must
+    agree to the bit."""
+    folder, _, _ = models[name, "bfloat16"]
+    sequences = sequences_of(name)
+    first = None
+    for _ in range(8):
+        core = es.build_core(folder, "bfloat16", num_blocks=pages_for(sequences, es.PAGE))
+        got = es.replay(core, es.schedule_tail(sequences, 32))
+        if first is None:
+            first = got
+            continue
+        for rid, logits in got.items():
+            assert torch.equal(logits, first[rid]), rid
+
+
 # ---- the C++ host path and the Python path launch the same kernels ----------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", list(CONFIGS))

@@ -698,6 +698,14 @@ def test_attention_decode_split_kv(dtype, splits, case):
     """One row per request, the keys split over several CTAs and merged by the last one;
     twice in a row on the same scratch, which the kernel must leave ready for reuse."""
     ops = _ops()
+    ops.set_decode_tensor_cores(False)  # this kernel also where the other would be chosen
+    try:
+        _split_kv_case(ops, dtype, splits, case)
+    finally:
+        ops.set_decode_tensor_cores(True)
+
+
+def _split_kv_case(ops, dtype, splits, case):
     lengths, heads, kv_heads, head_dim, page, window = case
     # a negative count: that many splits merged on chip by a thread-block cluster (no
     # scratch); positive: through the scratch buffers and a ticket
@@ -760,7 +768,7 @@ def test_attention_decode_split_kv(dtype, splits, case):
     ((67, 400), 6, 2, 128, 4, 50),
     ((70, 31, 48), 3, 3, 64, 12, 0),
 ])
-@pytest.mark.parametrize("ask", [-4, -8])
+@pytest.mark.parametrize("ask", [-4, -8, -16])
 def test_attention_decode_on_tensor_cores(case, ask):
     """The decode kernel for many rows (both products as warp-level MMAs over tiles of 16
     keys; ``splits=-4`` / ``-8`` ask for it with four / eight warps per (row, head) whatever
@@ -770,6 +778,8 @@ def test_attention_decode_on_tensor_cores(case, ask):
     ops = _ops()
     dtype = torch.bfloat16
     lengths, heads, kv_heads, head_dim, page, window = case
+    if ask == -16 and head_dim > 64:
+        pytest.skip("sixteen warps are for head size 64")
     rows = (1,) * len(lengths)
     q, k_pages, v_pages, table, req, pos, seqs = _paged_case(
         lengths, rows, heads, kv_heads, head_dim, page, dtype, seed=27, boost=(999, 2))
