@@ -1535,7 +1535,7 @@ AYK_API void ayk_set_stream_rows(int rows) {
 }
 
 // mode: 0 = bf16 out with activation, 1 = fp32 out with activation, 2 = fp32 out += (residual).
-// tile_n: 0 = choose; 32, 64, 128, 192, 256 = one tile of that width per CTA; 1128, 1192,
+// tile_n: 0 = choose; 64, 128, 192, 256 = one tile of that width per CTA; 1128, 1192,
 // 1256 = the persistent kernel with tiles 128, 192 or 256 wide; 2192, 2256 = the persistent
 // kernel for CTA pairs (256-row tiles, 192 or 256 wide; measured level with 1192 / 1256 at
 // GPT-2 XL's shapes, so the choice never picks it); negative = the few-rows kernel (see
@@ -1615,8 +1615,6 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
     case 2256:
       return launch_gemm_tc_pair<256, 6>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
                                          status, s);
-    case 32:
-      return launch_gemm_tc<32, 8>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
     case 64:
       return launch_gemm_tc<64, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
     case 128:

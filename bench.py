@@ -298,7 +298,7 @@ def profile_decode(llm, cfg: dict, batch: int, peak: dict) -> dict:
     scheduler = llm.scheduler
     params = SamplingParams(temperature=0.0, max_tokens=None, ignore_eos=True)
     for index, prompt in enumerate(random_prompts(cfg, batch, PROMPT, 77)):
-        scheduler.add_request(f"profile-{index}", prompt, params)
+        scheduler.add_request(f"profile{batch}-{index}", prompt, params)
     while any(r.prefilling for r in scheduler.running.values()) or scheduler.waiting:
         llm._advance()
     for _ in range(16):
@@ -541,7 +541,7 @@ def main() -> int:
     batch = max(1, min(args.batch, 64))
     main_run = decode_run(llm, cfg, batch, warmup, steps, seed=1)
     clock_record = clocks.stop()
-    clock_record["window"] = "prefill, warm-up and timed steps of the batch-8 run"
+    clock_record["window"] = f"prefill, warm-up and timed steps of the batch-{batch} run"
     prefill = prefill_run(llm, cfg, 2, 5)
     points, e2e, kernels, workloads = {}, None, None, None
     if not args.skip_points:
@@ -562,8 +562,10 @@ def main() -> int:
         # which is where a kernel class can be left out or bracketed by events
         ops.NATIVE_STEP = False
         try:
-            kernels = {"decode_b8": profile_decode(llm, cfg, 8, peak),
-                       "prefill_2048": profile_prefill(llm, cfg, peak)}
+            kernels = {f"decode_b{batch}": profile_decode(llm, cfg, batch, peak)}
+            if batch != 64:
+                kernels["decode_b64"] = profile_decode(llm, cfg, 64, peak)
+            kernels["prefill_2048"] = profile_prefill(llm, cfg, peak)
         finally:
             ops.NATIVE_STEP = True
     if not args.skip_workloads:

@@ -137,7 +137,7 @@ def test_linear_bfloat16(kernel, m, n, k):
         gemm_tc.check_status(a.device)
 
 
-@pytest.mark.parametrize("tile_n", [32, 64, 128, 192, 256, 1128, 1192, 1256, 2192, 2256, 3002,
+@pytest.mark.parametrize("tile_n", [64, 128, 192, 256, 1128, 1192, 1256, 2192, 2256, 3002,
                                     3004])
 def test_linear_tcgen05_tiles_and_strides(tile_n):
     """Every tile width, operands that are column ranges of wider buffers, rows limited."""
@@ -153,6 +153,12 @@ def test_linear_tcgen05_tiles_and_strides(tile_n):
     torch.testing.assert_close(out[:m].double(), a[:m].double() @ w.double().t(),
                                rtol=1e-4, atol=1e-4)
     assert torch.isnan(out[m:]).all()
+    half = torch.full((96, n + 3), float("nan"), device=DEV, dtype=torch.bfloat16)[:, :n]
+    gemm_tc.linear_bf16(a, w, None, half, m, 0, False, tile_n=tile_n)
+    gemm_tc.check_status(a.device)
+    torch.testing.assert_close(half[:m].double(), a[:m].double() @ w.double().t(),
+                               rtol=1e-2, atol=1e-2)
+    assert torch.isnan(half[m:]).all()
 
 
 @pytest.mark.parametrize("tile_n", [1192, 1256, 2192, 2256])
@@ -234,7 +240,7 @@ def test_linear_tcgen05_k_split_over_a_cluster(ranks, m, n, k):
 
 
 @pytest.mark.parametrize("splits", [-100, -2, -4, -8, 0])
-@pytest.mark.parametrize("m", [1, 8, 16, 17, 24, 33, 40, 57, 64])
+@pytest.mark.parametrize("m", [1, 2, 8, 16, 17, 24, 33, 40, 57, 64])
 def test_linear_tcgen05_few_rows(m, splits):
     """The weight-streaming kernel of decode steps: every padded row count, every K split
     (a negative tile selects it: -100 one CTA per tile, -2/-4/-8 that many cluster CTAs)."""
