@@ -1,24 +1,25 @@
-// Decode attention for many rows at once (a step of dozens of requests), bfloat16, with both
-// products on the warp-level tensor cores.
+// Decode attention (one row a request), bfloat16, head size 64 or 128, with both products on
+// the warp-level tensor cores.
 //
-// With a few rows the split-KV kernel of attention_decode.cu is bound by the chain of its
-// dependent steps and its CUDA-core dot products cost nothing. With 64 requests x 25 heads it
-// is bound by instruction issue (measured on a B200: issue slots 68 % busy, DRAM at 55 %):
-// eight conversions and eight multiply-adds per 16 bytes of keys, and again per 16 bytes of
-// values. Here a warp takes tiles of 16 keys: S = q K^T as m16n8k16 MMAs whose 16 query rows
-// are the one real row and 15 rows of zeros (the tensor pipe has room for that many times
-// over), the softmax on the four lanes that hold the real row, O += P V as MMAs whose A
-// operand is the score accumulator as it lies in registers. About 30 instructions per 16
-// keys instead of about 180.
+// The split-KV kernel of attention_decode.cu does its dot products on the CUDA cores: eight
+// conversions and eight multiply-adds per 16 bytes of keys, and again per 16 bytes of values.
+// With 64 requests x 25 heads that binds it to instruction issue (measured on a B200: issue
+// slots 68 % busy, DRAM at 55 %), and with a few requests it spreads a pair over a cluster,
+// whose launch and barrier cost about 3 microseconds in a chain of dependent kernels. Here a
+// warp takes tiles of 16 keys: S = q K^T as m16n8k16 MMAs whose 16 query rows are the one
+// real row and 15 rows of zeros (the tensor pipe has room for that many times over), the
+// softmax on the four lanes that hold the real row, O += P V as MMAs whose A operand is the
+// score accumulator as it lies in registers. About 30 instructions per 16 keys instead of
+// about 180, and one CTA per (row, head) at every batch size.
 //
-// A CTA of four, eight or sixteen warps serves one (row, head); warp w takes tiles w, w + WARPS, ... of
-// the row's keys, each with its own ring of three 16-key stages of K and V in shared memory
-// (cp.async, 128-byte rows with the usual XOR swizzle for ldmatrix), started before the
-// dependency wait for the keys of earlier steps (when the row's own key comes from k_new). The warps' partial results merge through
-// shared memory in warp order. Eight warps finish a (row, head) in about half the time but
-// only two such CTAs fit an SM where four of the four-warp kind do; the host picks by which
-// of the two needs less time for all its rounds over the SMs (decode_mma_warps). The row's own key and value come from the projection's output (k_new / v_new) and,
-// with `store`, are written to the cache by the warp that owns the last tile.
+// A CTA of four, eight or sixteen warps serves one (row, head); warp w takes tiles w,
+// w + WARPS, ... of the row's keys, each with its own ring of three 16-key stages of K and V
+// in shared memory (cp.async, 128-byte rows with the usual XOR swizzle for ldmatrix), started
+// before the dependency wait for the keys of earlier steps (when the row's own key comes from
+// k_new). The warps' partial results merge through shared memory in warp order. More warps
+// finish a pair sooner and fewer such CTAs fit an SM; the host picks by the number of pairs
+// (decode_mma_warps). The row's own key and value come from the projection's output (k_new /
+// v_new) and, with `store`, are written to the cache by the warp that owns the last tile.
 #pragma once
 
 #include "common.cuh"

@@ -277,7 +277,7 @@ int attention_half(const AykAttentionPart* p, AykStep* step, float* residual, vo
         writes ? vv : nullptr, writes ? ld_qkv : 0, writes ? 1 : 0, step->status, p->type,
         step->stream);
   } else if (p->type == 1) {
-    // leading single-row requests go to the split-KV kernel (their keys and values are in
+    // leading single-row requests go to the decode kernel (their keys and values are in
     // the cache by now), the rest to a prompt kernel
     const int lead = leading_single_rows(step);
     if (lead > 0) {

@@ -177,7 +177,8 @@ class Attention(Mixer):
             ops.kv_store(k, v, group.slot_mapping, cache.k_pages, cache.v_pages, rows=n)
         attended = step.workspace.buffer("attention.out", self.q_width, self.ctx.dtype)
         if step.decode_only:
-            # one row per request: the split-KV kernel
+            # one row per request: a decode kernel (which one, and how a pair's keys are
+            # shared out, is the library's choice; `splits` is what the split-KV one takes)
             reach = min(step.max_kv_len, self.window) if self.window else step.max_kv_len
             # (at most 8: a cluster merges the shares on chip, no scratch)
             splits = ops.decode_splits(n, self.num_heads, reach, q.device)
@@ -190,7 +191,7 @@ class Attention(Mixer):
         elif self.ctx.dtype == torch.bfloat16:
             # Prompt portions: tensor-core flash attention. The requests that lead the step
             # with a single row each (the scheduler puts decoding requests first) go to the
-            # split-KV kernel instead: as tiles of a prompt kernel each would occupy a CTA
+            # decode kernel instead: as tiles of a prompt kernel each would occupy a CTA
             # built for 64 or 256 rows. Their keys and values are in the cache by now.
             lead = leading_single_rows(step.host_rows)
             if lead:
