@@ -1616,9 +1616,9 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
       return launch_gemm_tc_pair<256, 6>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode,
                                          status, s);
     case 64:
-      return launch_gemm_tc<64, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
+      return launch_gemm_tc<64, 8>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
     case 128:
-      return launch_gemm_tc<128, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
+      return launch_gemm_tc<128, 6>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
     case 256:
       return launch_gemm_tc<256, 4>(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, status, s);
     default:
@@ -1661,7 +1661,7 @@ AYK_API int ayk_gemm_bf16_tc_kv(const void* a, int lda, const void* w, int ldw,
   }
   switch (choose_tile(M, N)) {
     case 128:
-      return launch_gemm_tc<128, 4, true>(a, lda, w, ldw, bias, out, ldo, M, N, K, ACT_NONE,
+      return launch_gemm_tc<128, 6, true>(a, lda, w, ldw, bias, out, ldo, M, N, K, ACT_NONE,
                                           OUT_BF16, status, s, kv);
     case 192:
       return launch_gemm_tc<192, 5, true>(a, lda, w, ldw, bias, out, ldo, M, N, K, ACT_NONE,
