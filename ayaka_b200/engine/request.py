@@ -5,6 +5,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from enum import Enum
 
+import numpy as np
+
 from ayaka_b200.engine.outputs import FinishReason
 from ayaka_b200.errors import EngineError
 from ayaka_b200.sampling.params import SamplingParams
@@ -47,6 +49,8 @@ class Request:
 
     request_id: str
     prompt: tuple[int, ...]
+    #: the prompt once more as an array: a step takes its portions as views of it
+    prompt_ids: np.ndarray
     params: SamplingParams
     seed: int
     arrival: int

@@ -29,6 +29,8 @@ from __future__ import annotations
 from collections import deque
 from dataclasses import dataclass, field
 
+import numpy as np
+
 from ayaka_b200.cache.manager import CacheManager
 from ayaka_b200.engine.outputs import FinishReason
 from ayaka_b200.engine.request import Request, RequestEvent, RequestStatus
@@ -120,8 +122,8 @@ class Scheduler:
                 "engine can give one request")
         if len(self.waiting) >= self.max_waiting:
             raise CapacityError(f"the waiting queue is full ({self.max_waiting} requests)")
-        request = Request(request_id, prompt, params, resolve_seed(request_id, params.seed),
-                          self._arrivals)
+        request = Request(request_id, prompt, np.asarray(prompt, dtype=np.int64), params,
+                          resolve_seed(request_id, params.seed), self._arrivals)
         self._arrivals += 1
         self._known.add(request_id)
         self.waiting.append(request)
@@ -220,7 +222,7 @@ class Scheduler:
         if size == 0:
             return 0
         start = request.computed
-        tokens = request.prompt[start:start + size]
+        tokens = request.prompt_ids[start:start + size]
         ends_prompt = start + size == len(request.prompt)
         entries.append(StepEntry(request.request_id, tokens, (size - 1,) if ends_prompt else ()))
         if ends_prompt:
