@@ -66,7 +66,12 @@ class ModelRunner:
                     + groups * _align4(manager.max_requests * manager.max_pages_per_request)
                     + 64)
         self._capacity = capacity
+        # Two pinned buffers in turn. A step that returns no logits ends without waiting for
+        # the device (a prompt cut into many portions: dozens of such steps in a row), so the
+        # host may be several steps ahead of the copies it queued: before a buffer is filled
+        # again, the copy that last read it must have run (an event per buffer).
         self._staging = [torch.empty(capacity, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._staging_read: list[torch.cuda.Event | None] = [None, None]
         self._turn = 0
         self._device_meta = torch.zeros(capacity, dtype=torch.int32, device=device)
         #: the device's status word and bad-index word, read wherever a step synchronises
@@ -127,8 +132,11 @@ class ModelRunner:
         self.storage.zero_state_rows(manager.take_fresh_rows())
 
         page_size = manager.page_size
-        staging = self._staging[self._turn]
+        turn = self._turn
+        staging = self._staging[turn]
         self._turn ^= 1
+        if self._staging_read[turn] is not None:
+            self._staging_read[turn].synchronize()  # type: ignore[union-attr]
         host = staging.numpy()
         cursor = 0
 
@@ -195,6 +203,10 @@ class ModelRunner:
 
         meta = self._device_meta
         meta[:cursor].copy_(staging[:cursor], non_blocking=True)
+        if self._staging_read[turn] is None:
+            self._staging_read[turn] = torch.cuda.Event()
+        self._staging_read[turn].record(  # type: ignore[union-attr]
+            torch.cuda.current_stream(self.device))
 
         def view(offset: int, length: int) -> torch.Tensor:
             return meta[offset:offset + max(length, 1)][:length] if length else \

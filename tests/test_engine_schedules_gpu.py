@@ -278,6 +278,33 @@ def test_the_same_steps_give_the_same_bits_every_time(models, name):
             assert torch.equal(logits, first[rid]), rid
 
 
+# ---- the host far ahead of the device ----------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_steps_that_return_nothing_queue_up_behind_a_busy_device(models, expected, dtype):
+    """A step that wants no logits does not wait for the device, so a prompt cut into small
+    portions is dozens of steps the host queues one behind the other. Here the device is
+    kept busy first (a spin of some tens of milliseconds), every portion of two tokens is
+    queued behind it, and only the last step wants logits: what each step copied to the
+    device must still be what it wrote (the step's metadata goes through two pinned buffers
+    in turn; a buffer filled again before its copy had run gave later steps' positions and
+    slots to earlier ones: wrong tokens now and then, once an illegal address)."""
+    from ayaka_b200.engine.runner import StepEntry
+
+    folder, _, _ = models["B", dtype]
+    rid, tokens = next((rid, tokens) for rid, tokens in sequences_of("B").items()
+                       if len(tokens) >= 190)
+    core = es.build_core(folder, dtype, num_blocks=pages_for({rid: tokens}, es.PAGE) + 1)
+    torch.cuda._sleep(80_000_000)  # the device is busy while the host queues every step
+    for at in range(0, len(tokens) - 2, 2):
+        assert core.step([StepEntry(rid, tokens[at:at + 2], ())]) is None
+    at = len(tokens) - 2 if len(tokens) % 2 == 0 else len(tokens) - 1
+    last = core.step([StepEntry(rid, tokens[at:], (len(tokens) - at - 1,))])
+    core.runner.check_device_flags()
+    got = {rid: last.cpu()}
+    want = {rid: expected["B", dtype][rid][-1:]}
+    es.assert_logits_close(got, want, dtype, "queued-portions/B")
+
+
 # ---- the C++ host path and the Python path launch the same kernels ----------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", list(CONFIGS))
