@@ -1482,11 +1482,18 @@ inline int pick_splits(int tile_n, int N, int M) {
   if (tile_n == -100) return 1;
   if (tile_n != -1) return -tile_n;
   const int tiles = (N + TC_BM - 1) / TC_BM;
-  // measured on GPT-2 XL's shapes: with more than 16 rows the cluster reduction of a
-  // [32, 128] or [64, 128] tile costs more than it buys unless the tiles are very few (64
-  // rows, 38 and 50 tiles split in two: 5.29 against 4.61 ms a decode step; and pushing the
-  // partial sums to the rows' owners instead of fetching them: 5.19 against 4.61)
-  if (M > 16) return tiles >= 32 ? 1 : 8;
+  // More than 16 rows: a CTA takes most of an SM's shared memory and a cluster lies inside
+  // one GPC, so a GPC of 18 SMs holds two clusters of eight or four of four at a time, and
+  // clusters beyond one round wait for a whole round. Eight splits while the tiles are at
+  // most 16, four up to 32, else none: the reduction (each rank fetches its rows of every
+  // peer's tile) costs more the fewer ranks share the rows, which is why two splits lose to
+  // none. Measured in a chain of such products at 64 rows, microseconds with 1 / 2 / 4 / 8
+  // splits: GPT-2 small's QKV (18 tiles, K 768) 7.9 / 10.3 / 7.6 / 12.1 and its output
+  // projection (6 tiles) 16.6 / 13.7 / 9.2 / 5.7; GPT-2 large's QKV at 32 rows (30 tiles)
+  // 8.6 / 8.9 / 7.4 / 12.3 and its feed-forward (40 tiles) 8.7 / 9.3 / 13.1 / 17.6; GPT-2
+  // XL's QKV (38 tiles) 11.4 / 13.1 / 17.3 / 21.1 and its output projection (13 tiles) 37 /
+  // 24 / 14 / 7.6.
+  if (M > 16) return tiles <= 16 ? 8 : (tiles <= 32 ? 4 : 1);
   // as many K splits as still leave two CTAs' worth of tiles per SM
   int splits = 1;
   while (splits < 8 && tiles * splits * 2 <= 2 * sm_count()) splits <<= 1;
@@ -1572,6 +1579,18 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
     if (splits == 0) return AYK_BAD_ARGUMENT;
     return launch_gemm_stream(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, splits,
                               tile_n == -200 ? -1 : (tile_n == -202 ? 1 : 0), s);
+  }
+  // 49 to 64 rows of a product so wide that the weight-streaming kernel would run it without
+  // a K split (more than 32 tiles of 128 columns), while its 64-column tiles are still one
+  // round: the rows as the 128-row operand and one 64-column tile per CTA, which has twice
+  // the CTAs and needs no cluster. Measured, a decode step of 64 requests with and without
+  // this choice: GPT-2 XL 4.22 against 4.58 ms, GPT-2 large 3.02 against 3.18; where the
+  // weight-streaming kernel splits K in four (GPT-2 small and medium: at most 32 tiles) it
+  // stays ahead (0.77 against 0.79 ms, 1.56 against 1.60), and at 48 rows and fewer it is
+  // level or ahead everywhere (its rows operand shrinks with the rows, this one's does not).
+  if (tile_n == 0 && M > 48 && M <= 64 && (N + TC_BM - 1) / TC_BM > 32 &&
+      (N + 63) / 64 <= sm_count()) {
+    tile_n = 64;
   }
   if (tile_n == 0 && M <= 64) tile_n = -1;  // few rows: the weight-streaming kernel
   if (tile_n < 0) {
