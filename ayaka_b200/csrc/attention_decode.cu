@@ -551,9 +551,8 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
                      const int* positions, void* out, int ld_out, int num_rows, int num_heads,
                      int num_kv_heads, int head_dim, int page_size, float scale, int window,
                      int splits, float* partial, int* tickets, const void* k_new,
-                     const void* v_new, int ld_new, int store, int* status,
+                     const void* v_new, int ld_new, int store, int* status, int num_pages,
                      cudaStream_t stream) {
-  (void)status;  // this kernel has no wait that could run out
   if (num_rows == 0) return AYK_OK;
   if ((k_new == nullptr) != (v_new == nullptr) || (store && k_new == nullptr)) {
     return AYK_BAD_ARGUMENT;
@@ -592,7 +591,7 @@ int attention_decode(const void* q, int ld_q, const void* k_pages, const void* v
   return launch_decode_mma<HD, W>(q, ld_q, k_pages, v_pages, block_table, table_stride,       \
                                   request_of_row, positions, out, ld_out, num_rows, num_heads, \
                                   num_kv_heads, page_size, scale, window, k_new, v_new,        \
-                                  ld_new, store, stream)
+                                  ld_new, store, num_pages, status, stream)
       if (head_dim == 64 && warps == 16) AYK_DECODE_MMA(64, 16);
       if (head_dim == 64 && warps == 8) AYK_DECODE_MMA(64, 8);
       if (head_dim == 64) AYK_DECODE_MMA(64, 4);
@@ -626,8 +625,9 @@ AYK_API void ayk_set_decode_tensor_cores(int on) { ayk::decode_tensor_cores() = 
 // floats and `tickets` num_rows * num_heads zeroed ints. With k_new/v_new ([rows, kv_heads *
 // head_dim], row stride ld_new) each row's own key and value are read from there instead of
 // the cache, and with `store` they are also written into the row's cache slot (the step's KV
-// store, fused). `status` is unused (the kernel has no wait that could run out); it is kept
-// so that every attention entry point has the same tail of arguments.
+// store, fused). `num_pages` is the number of pages k_pages and v_pages hold (0 if the caller
+// does not know): with it the tensor-core kernel fetches its tiles by TMA where the layout
+// allows, and a wait of that path that runs out is reported through `status`.
 AYK_API int ayk_attention_decode(const void* q, int ld_q, const void* k_pages,
                                  const void* v_pages, const int* block_table, int table_stride,
                                  const int* request_of_row, const int* positions, void* out,
@@ -635,19 +635,19 @@ AYK_API int ayk_attention_decode(const void* q, int ld_q, const void* k_pages,
                                  int head_dim, int page_size, float scale, int window,
                                  int splits, float* partial, int* tickets, const void* k_new,
                                  const void* v_new, int ld_new, int store, int* status,
-                                 int type, void* stream) {
+                                 int type, void* stream, int num_pages) {
   if (type == 0) {
     return ayk::attention_decode<float>(q, ld_q, k_pages, v_pages, block_table, table_stride,
                                         request_of_row, positions, out, ld_out, num_rows,
                                         num_heads, num_kv_heads, head_dim, page_size, scale,
                                         window, splits, partial, tickets, k_new, v_new, ld_new,
-                                        store, status, (cudaStream_t)stream);
+                                        store, status, num_pages, (cudaStream_t)stream);
   }
   if (type == 1) {
     return ayk::attention_decode<__nv_bfloat16>(
         q, ld_q, k_pages, v_pages, block_table, table_stride, request_of_row, positions, out,
         ld_out, num_rows, num_heads, num_kv_heads, head_dim, page_size, scale, window, splits,
-        partial, tickets, k_new, v_new, ld_new, store, status, (cudaStream_t)stream);
+        partial, tickets, k_new, v_new, ld_new, store, status, num_pages, (cudaStream_t)stream);
   }
   return AYK_BAD_ARGUMENT;
 }
@@ -722,13 +722,13 @@ AYK_API int ayk_attention_decode_noalloc(const void* q, int ld_q, const void* k_
     return attention_decode<float>(q, ld_q, k_pages, v_pages, block_table, table_stride,
                                    request_of_row, positions, out, ld_out, num_rows, num_heads,
                                    num_kv_heads, head_dim, page_size, scale, window, splits,
-                                   partial, tickets, nullptr, nullptr, 0, 0, &unused_status, s);
+                                   partial, tickets, nullptr, nullptr, 0, 0, &unused_status, 0, s);
   }
   if (type == 1) {
     return attention_decode<__nv_bfloat16>(
         q, ld_q, k_pages, v_pages, block_table, table_stride, request_of_row, positions, out,
         ld_out, num_rows, num_heads, num_kv_heads, head_dim, page_size, scale, window, splits,
-        partial, tickets, nullptr, nullptr, 0, 0, &unused_status, s);
+        partial, tickets, nullptr, nullptr, 0, 0, &unused_status, 0, s);
   }
   return AYK_BAD_ARGUMENT;
 }

@@ -14,20 +14,35 @@
 //
 // A CTA of four, eight or sixteen warps serves one (row, head); warp w takes tiles w,
 // w + WARPS, ... of the row's keys, each with its own ring of three 16-key stages of K and V
-// in shared memory (cp.async, 128-byte rows with the usual XOR swizzle for ldmatrix), started
+// in shared memory (128-byte rows with the usual XOR swizzle for ldmatrix), all three started
 // before the dependency wait for the keys of earlier steps (when the row's own key comes from
-// k_new). The warps' partial results merge through shared memory in warp order. More warps
+// k_new) and each refilled as soon as its tile has been used. Where the layout allows (head
+// size 64, pages of a multiple of 16 tokens, no window, the caller names the number of pages)
+// a tile is two TMA boxes of 16 rows, one of K and one of V, issued by one lane and awaited
+// on a barrier per stage; else every lane copies its 16-byte pieces with cp.async. Cycle
+// stamps in the kernel showed why that matters: issuing one tile's 256 cp.async took 0.75
+// microseconds each time, with the table lookup ahead of it or without (the SM's queue of
+// outstanding requests was full), five times in a row for a warp of a 528-key context; a TMA
+// box costs its issuer nothing. A decode step of GPT-2 XL at 8 requests: 1.40 against 1.49 ms.
+// The row's pages are read once into shared memory (up to DM_TABLE_ROOM entries). The warps' partial results merge through shared memory in warp order. More warps
 // finish a pair sooner and fewer such CTAs fit an SM; the host picks by the number of pairs
 // (decode_mma_warps). The row's own key and value come from the projection's output (k_new /
 // v_new) and, with `store`, are written to the cache by the warp that owns the last tile.
 #pragma once
 
-#include "common.cuh"
+#include <mutex>
+#include <unordered_map>
+
+#include "tc_common.cuh"
 
 namespace ayk {
 
 constexpr int DM_STAGES = 3;
 constexpr int DM_TILE = 16;  // keys per tile
+#ifndef AYK_DM_TMA
+#define AYK_DM_TMA 1
+#endif
+constexpr int DM_TABLE_ROOM = 512;  // table entries a CTA holds in shared memory (2 KB)
 
 __device__ __forceinline__ void dm_cp_async_16(void* dst, const void* src, bool valid) {
   const uint32_t bytes = valid ? 16u : 0u;
@@ -66,9 +81,11 @@ __device__ __forceinline__ uint32_t dm_pack(float lo, float hi) {
 
 // grid (num_heads, num_rows); HD = head size (64 or 128). Shared memory: DM_WARPS rings of
 // DM_STAGES x (K tile + V tile) of 16 x HD bfloat16, then the merge area.
-template <int HD, int DM_WARPS>
+template <int HD, int DM_WARPS, bool TMA>
 __global__ void __launch_bounds__(DM_WARPS * 32)
-attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
+attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, int* status,
+                            const __nv_bfloat16* __restrict__ q, int ld_q,
                             const __nv_bfloat16* __restrict__ k_pages,
                             const __nv_bfloat16* __restrict__ v_pages,
                             const int* __restrict__ block_table, int table_stride,
@@ -79,13 +96,16 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
                             const __nv_bfloat16* __restrict__ k_new,
                             const __nv_bfloat16* __restrict__ v_new, int ld_new,
                             __nv_bfloat16* __restrict__ k_store,
-                            __nv_bfloat16* __restrict__ v_store) {
+                            __nv_bfloat16* __restrict__ v_store, int table_room) {
   constexpr int ROW_BYTES = HD * 2;          // one key's bytes
   constexpr int PIECES = ROW_BYTES / 16;     // 16-byte pieces per key
   constexpr int TILE_BYTES = DM_TILE * ROW_BYTES;
   constexpr int KSTEPS = HD / 16;            // k-steps of S = q K^T
   constexpr int NT = HD / 8;                 // 8-wide tiles of O
-  extern __shared__ __align__(128) uint8_t dm_smem[];
+  extern __shared__ __align__(128) uint8_t dm_raw[];
+  // (tiles start on 1024 bytes: the 128-byte swizzle of a TMA box is a function of the
+  // shared-memory address, and the index arithmetic below assumes a tile starts a pattern)
+  uint8_t* dm_smem = dm_raw + ((1024 - (smem_u32(dm_raw) & 1023)) & 1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, qd = lane & 3;
   const int head = blockIdx.x, row = blockIdx.y;
@@ -93,6 +113,18 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
 
   uint8_t* ring = dm_smem + (size_t)warp * DM_STAGES * 2 * TILE_BYTES;
   float* merge = reinterpret_cast<float*>(dm_smem + (size_t)DM_WARPS * DM_STAGES * 2 * TILE_BYTES);
+  int* table_s = reinterpret_cast<int*>(merge + DM_WARPS * (HD + 2));  // table_room entries
+  // one barrier per stage of this warp's ring (TMA only), behind the table on 8 bytes
+  uint64_t* bars = reinterpret_cast<uint64_t*>(table_s + DM_TABLE_ROOM) + warp * DM_STAGES;
+  bool gave_up = false;
+  if (TMA) {
+    if (lane == 0) {
+#pragma unroll
+      for (int st = 0; st < DM_STAGES; ++st) mbar_init(&bars[st], 1);
+      mbar_fence_init();
+    }
+    __syncwarp();
+  }
 
   pdl_launch_dependents();
   const int req = __ldg(request_of_row + row);
@@ -108,6 +140,22 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   const int tiles = (nkeys + DM_TILE - 1) / DM_TILE;
   const int my_tiles = tiles > warp ? (tiles - warp + DM_WARPS - 1) / DM_WARPS : 0;
   const int* table = block_table + (size_t)req * table_stride;
+  // The row's pages, once, into shared memory: a table entry fetched where a tile's copies
+  // are issued is a trip to L2 (0.7 microseconds, measured with cycle stamps) ahead of every
+  // tile, five times in a row for a warp of a 528-key context. Contexts of more pages than
+  // the launch made room for keep the direct lookups.
+  const int page_lo = page_shift >= 0 ? lo >> page_shift : lo / page_size;
+  const int page_hi = page_shift >= 0 ? pos >> page_shift : pos / page_size;
+  const bool table_held = page_hi - page_lo < table_room;
+  if (table_held) {
+    for (int i = threadIdx.x; i <= page_hi - page_lo; i += DM_WARPS * 32) {
+      table_s[i] = __ldg(table + page_lo + i);
+    }
+    __syncthreads();
+  }
+  auto page_at = [&](int page_index) {
+    return table_held ? table_s[page_index - page_lo] : __ldg(table + page_index);
+  };
   const size_t head_off = (size_t)kv_head * page_size * HD;
   const size_t page_elems = (size_t)num_kv_heads * page_size * HD;
   const bool patch = k_new != nullptr;  // the row's own key and value are not in the cache yet
@@ -118,6 +166,21 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
     const int tile = warp + i * DM_WARPS;
     uint8_t* k_tile = ring + (size_t)(i % DM_STAGES) * 2 * TILE_BYTES;
     uint8_t* v_tile = k_tile + TILE_BYTES;
+    if (TMA) {
+      // the tile's 16 keys lie in one page (a page is a multiple of 16 keys and the first key
+      // is key 0): one box of 16 rows of K and one of V, whatever of them is beyond the row
+      if (lane == 0) {
+        const int key = tile * DM_TILE;
+        const int page_index = page_shift >= 0 ? key >> page_shift : key / page_size;
+        const int slot = key - page_index * page_size;
+        const int first = (page_at(page_index) * num_kv_heads + kv_head) * page_size + slot;
+        uint64_t* bar = &bars[i % DM_STAGES];
+        mbar_expect_tx(bar, 2 * TILE_BYTES);
+        tma_load_2d(k_tile, &map_k, bar, 0, first);
+        tma_load_2d(v_tile, &map_v, bar, 0, first);
+      }
+      return;
+    }
 #pragma unroll
     for (int j = 0; j < PIECES / 2; ++j) {
       const int idx = j * 32 + lane;
@@ -129,7 +192,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
       if (valid) {
         const int page_index = page_shift >= 0 ? key >> page_shift : key / page_size;
         const int slot = page_shift >= 0 ? key & (page_size - 1) : key - page_index * page_size;
-        off = (size_t)__ldg(table + page_index) * page_elems + head_off + (size_t)slot * HD +
+        off = (size_t)page_at(page_index) * page_elems + head_off + (size_t)slot * HD +
               (size_t)piece * 8;
       }
       const int swz = (piece & ~7) | ((piece ^ key_in_tile) & 7);
@@ -144,9 +207,9 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   // the cache, the kernel ahead is the one that wrote it there, and the wait comes first.
   if (!patch) pdl_wait_for(q, k_pages, v_pages);
 #pragma unroll
-  for (int i = 0; i < DM_STAGES - 1; ++i) {
+  for (int i = 0; i < DM_STAGES; ++i) {  // every stage: a stage is refilled once it is used
     if (i < my_tiles) issue(i);
-    dm_commit();
+    if (!TMA) dm_commit();
   }
   if (patch) pdl_wait_for(q, k_new, v_new);
 
@@ -168,13 +231,28 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
   float run_max = -INFINITY, run_sum = 0.f;
 
   for (int i = 0; i < my_tiles; ++i) {
-    if (i + DM_STAGES - 1 < my_tiles) issue(i + DM_STAGES - 1);
-    dm_commit();
-    dm_wait<DM_STAGES - 1>();
-    __syncwarp();  // every lane's copies of this tile have landed
     const int tile = warp + i * DM_WARPS;
     uint8_t* k_tile = ring + (size_t)(i % DM_STAGES) * 2 * TILE_BYTES;
     uint8_t* v_tile = k_tile + TILE_BYTES;
+    if (TMA) {
+      if (!mbar_wait(&bars[i % DM_STAGES], (uint32_t)(i / DM_STAGES) & 1u)) gave_up = true;
+      if (tile == tiles - 1) {
+        // what the boxes brought from beyond the row (slots not written yet, or another
+        // request's leavings) must not meet the zero weights of its keys: 0 x NaN is NaN
+        const int have = pos - tile * DM_TILE + 1;  // keys of the row in this tile, 1 to 16
+#pragma unroll
+        for (int j = 0; j < PIECES / 2; ++j) {
+          const int idx = j * 32 + lane;
+          if (idx / PIECES >= have) {
+            *reinterpret_cast<uint4*>(k_tile + idx * 16) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(v_tile + idx * 16) = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+      }
+    } else {
+      dm_wait<DM_STAGES - 1>();  // DM_STAGES + i groups committed: the first i + 1 are done
+    }
+    __syncwarp();  // every lane's copies of this tile have landed
     if (patch && tile == tiles - 1) {
       // the row's own key and value: from the projection's output into the tile (and the
       // cache); the copy above left their 16-byte pieces zero
@@ -190,7 +268,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
         if (k_store != nullptr && head == kv_head * group) {  // one head of a group stores
           const int page_index = page_shift >= 0 ? pos >> page_shift : pos / page_size;
           const int slot = pos - page_index * page_size;
-          const size_t off = (size_t)__ldg(table + page_index) * page_elems + head_off +
+          const size_t off = (size_t)page_at(page_index) * page_elems + head_off +
                              (size_t)slot * HD + (size_t)lane * 8;
           *reinterpret_cast<uint4*>(k_store + off) = kv;
           *reinterpret_cast<uint4*>(v_store + off) = vv;
@@ -250,7 +328,9 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
       dm_mma(o[2 * t2], pa0, 0u, pa2, 0u, b[0], b[1]);
       dm_mma(o[2 * t2 + 1], pa0, 0u, pa2, 0u, b[2], b[3]);
     }
-    __syncwarp();  // the stage may be refilled by the next iteration's copies
+    __syncwarp();  // every lane has read the stage: it takes the tile DM_STAGES on
+    if (i + DM_STAGES < my_tiles) issue(i + DM_STAGES);
+    if (!TMA) dm_commit();
   }
 
   // ---- merge the warps' shares (warp order) -----------------------------------------
@@ -285,22 +365,66 @@ attention_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q,
     }
     dst[d] = __float2bfloat16_rn(sum / denom);
   }
+  if (TMA && gave_up) atomicExch(status, AYK_WAIT_TIMEOUT);
 }
 
+// Tensor maps of the cache pages as rows of one key each ([pages * kv_heads * page_size,
+// head size], 128-byte swizzle, boxes of 16 rows), encoded once per cache tensor.
+struct DmMapKey {
+  const void* base;
+  uint64_t rows;
+  bool operator==(const DmMapKey& o) const { return base == o.base && rows == o.rows; }
+};
+struct DmMapKeyHash {
+  size_t operator()(const DmMapKey& k) const { return (size_t)k.base * 1000003u ^ k.rows; }
+};
+inline int dm_cached_map(const void* base, uint64_t rows, int head_dim, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<DmMapKey, CUtensorMap, DmMapKeyHash> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  const DmMapKey key{base, rows};
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    CUtensorMap map;
+    const int r = make_map_128b(&map, base, rows, (uint64_t)head_dim, (uint64_t)head_dim,
+                                DM_TILE, 2);
+    if (r != AYK_OK) return r;
+    if (cache.size() > 4096) cache.clear();
+    it = cache.emplace(key, map).first;
+  }
+  *out = it->second;
+  return AYK_OK;
+}
+
+// `num_pages` (0 if the caller does not know): with it, head size 64, pages of a multiple of
+// 16 tokens and no window, the tiles come by TMA.
 template <int HD, int DM_WARPS>
 int launch_decode_mma(const void* q, int ld_q, const void* k_pages, const void* v_pages,
                       const int* block_table, int table_stride, const int* request_of_row,
                       const int* positions, void* out, int ld_out, int num_rows, int num_heads,
                       int num_kv_heads, int page_size, float scale, int window,
                       const void* k_new, const void* v_new, int ld_new, int store,
-                      cudaStream_t stream) {
+                      int num_pages, int* status, cudaStream_t stream) {
   using bf = __nv_bfloat16;
+  // room for the pages of a row: the table's width, up to DM_TABLE_ROOM entries
+  const int table_room = table_stride < DM_TABLE_ROOM ? table_stride : DM_TABLE_ROOM;
   const size_t smem = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TILE * HD * 2 +
-                      (size_t)DM_WARPS * (HD + 2) * sizeof(float);
+                      (size_t)DM_WARPS * (HD + 2) * sizeof(float) +
+                      (size_t)DM_TABLE_ROOM * sizeof(int) + (size_t)DM_WARPS * DM_STAGES * 8 +
+                      1024;
+  const long long rows_of_cache = (long long)num_pages * num_kv_heads * page_size;
+  const bool tma = HD == 64 && num_pages > 0 && page_size % DM_TILE == 0 && window == 0 &&
+                   status != nullptr && rows_of_cache < (1ll << 31) &&
+                   ((uintptr_t)k_pages % 128) == 0 && ((uintptr_t)v_pages % 128) == 0 &&
+                   AYK_DM_TMA;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, DM_WARPS>,
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, DM_WARPS, false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess && HD == 64) {
+      e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, DM_WARPS, HD == 64>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -309,31 +433,40 @@ int launch_decode_mma(const void* q, int ld_q, const void* k_pages, const void* 
     page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
   }
-  return launch_kernel(attention_decode_mma_kernel<HD, DM_WARPS>, dim3(num_heads, num_rows),
-                       dim3(DM_WARPS * 32),
-                       smem, stream, 1, (const bf*)q, ld_q, (const bf*)k_pages,
+  CUtensorMap map_k = {}, map_v = {};
+  if (tma) {
+    int r = dm_cached_map(k_pages, (uint64_t)rows_of_cache, HD, &map_k);
+    if (r == AYK_OK) r = dm_cached_map(v_pages, (uint64_t)rows_of_cache, HD, &map_v);
+    if (r != AYK_OK) return r;
+  }
+  auto kernel = tma ? attention_decode_mma_kernel<HD, DM_WARPS, HD == 64>
+                    : attention_decode_mma_kernel<HD, DM_WARPS, false>;
+  return launch_kernel(kernel, dim3(num_heads, num_rows), dim3(DM_WARPS * 32), smem, stream, 1,
+                       map_k, map_v, status, (const bf*)q, ld_q, (const bf*)k_pages,
                        (const bf*)v_pages, block_table, table_stride, request_of_row, positions,
                        (bf*)out, ld_out, num_kv_heads, num_heads / num_kv_heads, page_size,
                        page_shift, scale, window, (const bf*)k_new, (const bf*)v_new, ld_new,
                        store ? (bf*)const_cast<void*>(k_pages) : (bf*)nullptr,
-                       store ? (bf*)const_cast<void*>(v_pages) : (bf*)nullptr);
+                       store ? (bf*)const_cast<void*>(v_pages) : (bf*)nullptr, table_room);
 }
 
-// Warps per (row, head). With few pairs (at most two for every five SMs) sixteen: the pair's
-// keys are then spread over as many warps as one CTA can hold rings for. Else four or eight:
-// the CTAs of either kind make ceil(pairs / resident) rounds over the device (shared memory
-// allows 4 four-warp or 2 eight-warp CTAs of head size 64 per SM, half as many of head size
-// 128), and a round of eight-warp CTAs takes about 0.55 of a round of four-warp ones.
-// Measured, GPT-2 XL (25 heads), decode step in ms with four / eight / sixteen warps: 1
-// request - / 1.25 / 1.16, 2: - / 1.23 / 1.20, 8: 1.66 / 1.48 / 1.62, 16: 2.18 / 2.23 / -,
-// 32: 3.39 / 3.23 / -, 64: 4.61 / 4.91 / 5.86; the rule picks the fastest of each.
+// Warps per (row, head). While one round of sixteen-warp CTAs holds every pair (at most one
+// pair an SM), sixteen: the pair's keys are then spread over as many warps as one CTA can hold
+// rings for. Else four or eight: the CTAs of either kind make ceil(pairs / resident) rounds
+// over the device (shared memory allows 4 four-warp or 2 eight-warp CTAs of head size 64 per
+// SM, half as many of head size 128), and a round of eight-warp CTAs takes about 0.7 of a
+// round of four-warp ones. Measured with the tiles fetched by TMA, GPT-2 XL (25 heads, 528
+// keys), decode step in ms with four / eight / sixteen warps: 1 request 1.27 / 1.19 / 1.15,
+// 2: 1.29 / 1.19 / 1.20, 4: 1.33 / 1.28 / 1.26, 8: 1.51 / 1.41 / 1.54, 12: 1.98 / 1.99 / 2.14,
+// 16: 2.03 / 2.17 / 2.38, 24: 2.97 / 3.03 / 3.27, 32: 3.17 / 3.30 / 3.64, 64: 4.13 / 4.37 /
+// 5.15; the rule picks the fastest of each but at 2 requests (level).
 inline int decode_mma_warps(long long pairs, int head_dim) {
   const long long sms = sm_count();
-  if (head_dim <= 64 && pairs * 5 <= 2 * sms) return 16;
+  if (head_dim <= 64 && pairs <= sms) return 16;
   const long long per_sm4 = head_dim <= 64 ? 4 : 2, per_sm8 = head_dim <= 64 ? 2 : 1;
   const long long rounds4 = (pairs + per_sm4 * sms - 1) / (per_sm4 * sms);
   const long long rounds8 = (pairs + per_sm8 * sms - 1) / (per_sm8 * sms);
-  return rounds8 * 55 < rounds4 * 100 ? 8 : 4;
+  return rounds8 * 70 < rounds4 * 100 ? 8 : 4;
 }
 
 }  // namespace ayk

@@ -34,7 +34,7 @@ typedef int (*KvStoreFn)(const void*, const void*, int, const int*, void*, void*
 typedef int (*AttnDecodeFn)(const void*, int, const void*, const void*, const int*, int,
                             const int*, const int*, void*, int, int, int, int, int, int, float,
                             int, int, float*, int*, const void*, const void*, int, int, int*,
-                            int, void*);
+                            int, void*, int);
 typedef int (*AttnSimtFn)(const void*, int, const void*, const void*, const int*, int,
                           const int*, const int*, void*, int, int, int, int, int, int, float, int,
                           int, void*);
@@ -275,7 +275,7 @@ int attention_half(const AykAttentionPart* p, AykStep* step, float* residual, vo
         step->positions, p->attended, q_width, n, p->num_heads, p->num_kv_heads, p->head_dim,
         g.page_size, p->scale, p->window, splits, nullptr, nullptr, writes ? kk : nullptr,
         writes ? vv : nullptr, writes ? ld_qkv : 0, writes ? 1 : 0, step->status, p->type,
-        step->stream);
+        step->stream, num_pages);
   } else if (p->type == 1) {
     // leading single-row requests go to the decode kernel (their keys and values are in
     // the cache by now), the rest to a prompt kernel
@@ -290,7 +290,7 @@ int attention_half(const AykAttentionPart* p, AykStep* step, float* residual, vo
           step->positions, p->attended, q_width, lead, p->num_heads, p->num_kv_heads,
           p->head_dim, g.page_size, p->scale, p->window,
           decode_splits(step, lead, p->num_heads, reach), nullptr, nullptr, nullptr, nullptr, 0,
-          0, step->status, p->type, step->stream);
+          0, step->status, p->type, step->stream, num_pages);
       if (r != AYK_OK) return r;
     }
     const int* table = g.block_table + (size_t)lead * g.table_stride;

@@ -560,7 +560,8 @@ def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         c_int(page_size), c_float(scale), c_int(window), c_int(splits), _ptr(partial),
         _ptr(tickets), _ptr(k_new), _ptr(v_new),
         c_int(0 if k_new is None else k_new.stride(0)), c_int(1 if store else 0),
-        _ptr(_status_word(q.device)), c_int(_TYPE[q.dtype]), _stream())
+        _ptr(_status_word(q.device)), c_int(_TYPE[q.dtype]), _stream(),
+        c_int(k_pages.shape[0]))
     check(status, op)
 
 
