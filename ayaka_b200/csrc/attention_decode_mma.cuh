@@ -39,9 +39,6 @@ namespace ayk {
 
 constexpr int DM_STAGES = 3;
 constexpr int DM_TILE = 16;  // keys per tile
-#ifndef AYK_DM_TMA
-#define AYK_DM_TMA 1
-#endif
 constexpr int DM_TABLE_ROOM = 512;  // table entries a CTA holds in shared memory (2 KB)
 
 __device__ __forceinline__ void dm_cp_async_16(void* dst, const void* src, bool valid) {
@@ -415,8 +412,7 @@ int launch_decode_mma(const void* q, int ld_q, const void* k_pages, const void* 
   const long long rows_of_cache = (long long)num_pages * num_kv_heads * page_size;
   const bool tma = HD == 64 && num_pages > 0 && page_size % DM_TILE == 0 && window == 0 &&
                    status != nullptr && rows_of_cache < (1ll << 31) &&
-                   ((uintptr_t)k_pages % 128) == 0 && ((uintptr_t)v_pages % 128) == 0 &&
-                   AYK_DM_TMA;
+                   ((uintptr_t)k_pages % 128) == 0 && ((uintptr_t)v_pages % 128) == 0;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, DM_WARPS, false>,
