@@ -113,6 +113,25 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
+// Two fp32 lanes in one instruction (sm_100): a * b + c and a + b on register pairs.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n.reg .b64 ra, rb, rc, rd;\n"
+      "mov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmov.b64 rc, {%6, %7};\n"
+      "fma.rn.f32x2 rd, ra, rb, rc;\nmov.b64 {%0, %1}, rd;\n}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n.reg .b64 ra, rb, rd;\n"
+      "mov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\n"
+      "add.rn.f32x2 rd, ra, rb;\nmov.b64 {%0, %1}, rd;\n}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
@@ -225,7 +244,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
   pdl_wait_for(q, k_pages, v_pages);
 
   // Which request and which 256-row tile of it: heads along grid.x, tiles along grid.y from
-  // the last one down (the longest first).
+  // the last one down (the longest first). (The tiles ranked by the keys they reach, so that
+  // the order holds across requests too, made the prologue two trips to memory longer and
+  // a step of two prompts of 1,024 tokens 1 % slower.)
   int tile = total_tiles - 1 - (int)blockIdx.y, req = 0, rows_b = 0;
   for (; req < num_requests; ++req) {
     rows_b = row_start[req + 1] - row_start[req];
@@ -316,10 +337,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
         // For K that is harmless (their scores are masked). For V they must be zero (0 * NaN
         // would poison the sum): such a block lands on a barrier of this warp first, which
         // zeroes the rows and then publishes the block.
-        fa_cp_async_wait<0>();
-        fence_proxy_async_shared();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(q_full);
+        // Q is published once the first K or V block of this warp is on its way: the block
+        // does not wait for Q (that order cost a CTA the time of one more trip to memory
+        // before its first product)
+        auto publish_q = [&]() {
+          fa_cp_async_wait<0>();
+          fence_proxy_async_shared();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(q_full);
+        };
+        if (part != 0) publish_q();
         if (part == 0) {
           const CUtensorMap* map = keys ? &map_k : &map_v;
           const int boxes = FA_BN / box_rows;
@@ -348,6 +375,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
               tma_load_2d(tile + (size_t)lane * box_bytes, map, lands, 0,
                           (page * num_kv_heads + kv_head) * page_size + slot);
             }
+            if (jj == 0) publish_q();
             if (fix) {
               if (lane == 0) ok = mbar_wait(v_land, (uint32_t)landed & 1u);
               ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -526,11 +554,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
         float part = 0.f;
         for (int attempt = 0;; ++attempt) {
           const float offset = ref == -INFINITY ? 0.f : ref;
-          float part0 = 0.f, part1 = 0.f, part2 = 0.f, part3 = 0.f;
+          float2 part01 = make_float2(0.f, 0.f), part23 = make_float2(0.f, 0.f);
           float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
           constexpr int CW = 32;  // columns of the row worked on at a time
-          auto process = [&](const uint32_t* raw, int c) {
-            float p[CW];
+          float p[CW];
+          // scale and reference for two scores an instruction
+          const float2 scale_2 = make_float2(scale2, scale2), offset_2 = make_float2(-offset, -offset);
+          // the columns' scores (masked) against the reference, the block's maximum on the way
+          auto select = [&](const uint32_t* raw, int c) {
             if (all_seen) {
 #pragma unroll
               for (int i = 0; i < CW; i += 8) {
@@ -540,8 +571,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
                 t3 = fmax3(t3, __uint_as_float(raw[i + 6]), __uint_as_float(raw[i + 7]));
               }
 #pragma unroll
-              for (int i = 0; i < CW; ++i) {
-                p[i] = fast_exp2(fmaf(__uint_as_float(raw[i]), scale2, -offset));
+              for (int i = 0; i < CW; i += 2) {
+                const float2 x = fma2(
+                    make_float2(__uint_as_float(raw[i]), __uint_as_float(raw[i + 1])), scale_2,
+                    offset_2);
+                p[i] = x.x;
+                p[i + 1] = x.y;
               }
             } else {
               const int key = key0 + c * CW;
@@ -559,18 +594,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
                 t1 = fmaxf(t1, x1);
                 t2 = fmaxf(t2, x2);
                 t3 = fmaxf(t3, x3);
-                p[i] = fast_exp2(fmaf(x0, scale2, -offset));  // exp2(-inf) = 0
-                p[i + 1] = fast_exp2(fmaf(x1, scale2, -offset));
-                p[i + 2] = fast_exp2(fmaf(x2, scale2, -offset));
-                p[i + 3] = fast_exp2(fmaf(x3, scale2, -offset));
+                const float2 x01 = fma2(make_float2(x0, x1), scale_2, offset_2);
+                const float2 x23 = fma2(make_float2(x2, x3), scale_2, offset_2);
+                p[i] = x01.x;  // -inf for a masked key: exp2(-inf) = 0
+                p[i + 1] = x01.y;
+                p[i + 2] = x23.x;
+                p[i + 3] = x23.y;
               }
             }
+          };
+          auto weigh = [&](int c) {
+#pragma unroll
+            for (int i = 0; i < CW; ++i) p[i] = fast_exp2(p[i]);
 #pragma unroll
             for (int i = 0; i < CW; i += 4) {
-              part0 += p[i];
-              part1 += p[i + 1];
-              part2 += p[i + 2];
-              part3 += p[i + 3];
+              part01 = add2(part01, make_float2(p[i], p[i + 1]));
+              part23 = add2(part23, make_float2(p[i + 2], p[i + 3]));
             }
             // 64 keys make a tile of 128-byte rows; eight keys a 16-byte piece of it
             uint8_t* dst = p_row + ((c * CW) >> 6) * FA_TILE;
@@ -589,18 +628,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k,
               *reinterpret_cast<uint4*>(dst + (((piece0 + h) ^ swz) << 4)) = packed;
             }
           };
-          // One load and one copy of the arithmetic: loading the next columns while these
-          // are worked on (two register buffers, the arithmetic twice in the loop) measured
-          // slower, 426 against 408 microseconds at 8,192 tokens; the warps wait for
-          // instructions more than for tensor memory, and the other group's warps fill the gap.
+          // One load and one copy of the arithmetic. Loading the next columns while these are
+          // worked on measured no faster, neither with two register buffers and the arithmetic
+          // twice in the loop (426 against 408 microseconds at 8,192 tokens) nor with the next
+          // load issued once these columns have left its registers (384 against 379): the
+          // other group's warps fill the gap.
           uint32_t raw[CW];
 #pragma unroll 1
           for (int c = 0; c < FA_BN / CW; ++c) {
             tmem_ld_32x32(s_acc + (uint32_t)(c * CW), raw);
             tmem_ld_wait();
-            process(raw, c);
+            select(raw, c);
+            weigh(c);
           }
-          part = (part0 + part1) + (part2 + part3);
+          part = (part01.x + part01.y) + (part23.x + part23.y);
           const float top = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)) * scale2;
           // A row without a reference ran this pass against 0 (see offset): that stands as
           // its reference if its maximum is within FA_LAZY of it, and the first block then
