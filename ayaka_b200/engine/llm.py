@@ -23,7 +23,7 @@ from ayaka_b200.engine.outputs import CompletionOutput, FinishReason, RequestOut
 from ayaka_b200.engine.request import RequestEvent
 from ayaka_b200.engine.runner import StepEntry
 from ayaka_b200.engine.scheduler import Scheduler
-from ayaka_b200.errors import AyakaError, BackendError, EngineError, InvalidRequestError
+from ayaka_b200.errors import AyakaError, EngineError, InvalidRequestError
 from ayaka_b200.sampling.params import SamplingParams
 from ayaka_b200.sampling.sampler import SampleRow, Sampler
 

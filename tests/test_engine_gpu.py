@@ -7,7 +7,6 @@ failure message names the first wrong position with its page and slot."""
 from __future__ import annotations
 
 import pytest
-import torch
 
 import engine_support as es
 from cases import INIT_LOUD, INIT_LOUD_WIDE, TINY_A, TINY_B, TINY_C, TINY_D, random_tokens
