@@ -1580,15 +1580,17 @@ AYK_API int ayk_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, con
     return launch_gemm_stream(a, lda, w, ldw, bias, out, ldo, M, N, K, act, mode, splits,
                               tile_n == -200 ? -1 : (tile_n == -202 ? 1 : 0), s);
   }
-  // 49 to 64 rows of a product so wide that the weight-streaming kernel would run it without
+  // 33 to 64 rows of a product so wide that the weight-streaming kernel would run it without
   // a K split (more than 32 tiles of 128 columns), while its 64-column tiles are still one
   // round: the rows as the 128-row operand and one 64-column tile per CTA, which has twice
   // the CTAs and needs no cluster. Measured, a decode step of 64 requests with and without
-  // this choice: GPT-2 XL 4.22 against 4.58 ms, GPT-2 large 3.02 against 3.18; where the
-  // weight-streaming kernel splits K in four (GPT-2 small and medium: at most 32 tiles) it
-  // stays ahead (0.77 against 0.79 ms, 1.56 against 1.60), and at 48 rows and fewer it is
-  // level or ahead everywhere (its rows operand shrinks with the rows, this one's does not).
-  if (tile_n == 0 && M > 48 && M <= 64 && (N + TC_BM - 1) / TC_BM > 32 &&
+  // this choice: GPT-2 XL 4.22 against 4.58 ms, GPT-2 large 3.02 against 3.18; of 48 requests
+  // 3.78 against 4.18 and 2.40 against 2.54, of 36 requests (GPT-2 XL) 3.38 against 3.69.
+  // Where the weight-streaming kernel splits K in four (GPT-2 small and medium: at most 32
+  // tiles) it stays ahead (0.77 against 0.79 ms, 1.56 against 1.60), and up to 32 rows, where
+  // its rows operand is 32 wide, everywhere (GPT-2 XL's QKV at 32 rows in a chain: 9.9
+  // against 10.6 us, its feed-forward 10.3 against 12.3).
+  if (tile_n == 0 && M > 32 && M <= 64 && (N + TC_BM - 1) / TC_BM > 32 &&
       (N + 63) / 64 <= sm_count()) {
     tile_n = 64;
   }
