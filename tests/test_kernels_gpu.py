@@ -265,6 +265,32 @@ def test_linear_tcgen05_few_rows(m, splits):
     gemm_tc.check_status(a.device)
 
 
+def test_linear_wide_products_of_33_to_64_rows():
+    """Products too wide for a K split (more than 32 tiles of 128 columns) take 64-column
+    tiles with the rows as the 128-row operand from 33 rows on: the library's own choice at
+    the row counts around that border, every epilogue."""
+    from ayaka_b200.kernels import gemm_tc
+    n, k = 4800, 1600
+    w = _randn(n, k, seed=41, dtype=torch.bfloat16, scale=1 / math.sqrt(k))
+    bias = _randn(n, seed=42)
+    for m in (32, 33, 48, 64):
+        a = _randn(m, k, seed=40 + m, dtype=torch.bfloat16)
+        exact = a.double() @ w.double().t() + bias.double()
+        out = torch.full((m + 1, n), float("nan"), device=DEV)
+        gemm_tc.linear_bf16(a, w, bias, out, m, 0, False)
+        torch.testing.assert_close(out[:m].double(), exact, rtol=1e-4, atol=1e-4)
+        assert torch.isnan(out[m:]).all()
+        base = _randn(m, n, seed=43)
+        acc = base.clone()
+        gemm_tc.linear_bf16(a, w, bias, acc, m, 0, True)
+        torch.testing.assert_close(acc.double(), exact + base.double(), rtol=1e-4, atol=1e-4)
+        half = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+        gemm_tc.linear_bf16(a, w, bias, half, m, 1, False)
+        torch.testing.assert_close(half.double(), plain.gelu(exact, "gelu_new"),
+                                   rtol=1e-2, atol=1e-2)
+    gemm_tc.check_status(a.device)
+
+
 @pytest.mark.parametrize("m", [1, 8, 40])
 @pytest.mark.parametrize("n,k", [(300, 96), (136, 840)])
 def test_linear_normed(m, n, k):
